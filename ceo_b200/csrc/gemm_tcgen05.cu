@@ -1,0 +1,417 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with
+// fp32 accumulators in TMEM -> tcgen05.ld epilogue with fused scale / bias /
+// residual / accumulate and bf16 or fp32 store.
+//
+// Persistent kernel, one CTA per SM, warp-specialised:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM allocation + MMA issue (one lane)
+//   warps 2..5  epilogue (each owns one 32-lane TMEM quadrant)
+// Two 128x256 fp32 accumulators (all 512 TMEM columns) are double-buffered so
+// the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Replaces the library GEMM + separate bias / column-sum kernels of the
+// reference (kernels/cuda/gemm.cu:182-234, 50-72) with one fused kernel.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "common/ptx.cuh"
+#include "include/ceo_kernels.h"
+
+namespace ceo {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int PANEL_BYTES = 64 * BK * 2;  // one 64-wide MN-major panel, 8 KB
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 512;
+
+struct GemmParams {
+  void* C;
+  const void* residual;  // same dtype/layout family as C (bf16), optional
+  const float* bias;     // fp32 [N], optional
+  int M, N, K;
+  long long ldc, ldr;
+  long long batch_stride_c, batch_stride_r;
+  int batch;
+  int out_f32;     // 1: C is fp32, 0: C is bf16
+  int accumulate;  // C = alpha*acc + C
+  float alpha;
+  int num_m, num_n;
+  int* status;
+};
+
+enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4 };
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128B swizzle atom (8 rows x 128 B).
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_batch = p.num_m * p.num_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int b = t / tiles_per_batch;
+        const int r = t - b * tiles_per_batch;
+        const int m0 = (r % p.num_m) * BM;
+        const int n0 = (r / p.num_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicCAS(p.status, 0, ST_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_3d(sa, &tmA, &full_bar[s], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sa + j * PANEL_BYTES, &tmA, &full_bar[s], m0 + j * 64, k0, b);
+          }
+          if (B_MN == 0) {
+            tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * PANEL_BYTES, &tmB, &full_bar[s], n0 + j * 64, k0, b);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // let any copy still in flight land before the CTA's shared memory goes away
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1)) {
+          atomicCAS(p.status, 0, ST_MMA_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicCAS(p.status, 0, ST_MMA_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = A_MN ? umma_smem_desc(sa + k * 2048, PANEL_BYTES, 1024)
+                                     : umma_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? umma_smem_desc(sb + k * 2048, PANEL_BYTES, 1024)
+                                     : umma_smem_desc(sb + k * 32, 16, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      const int b = t / tiles_per_batch;
+      const int r = t - b * tiles_per_batch;
+      const int m0 = (r % p.num_m) * BM;
+      const int n0 = (r / p.num_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph)) {
+        if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C);
+      const long long coff = static_cast<long long>(b) * p.batch_stride_c + row * p.ldc;
+      const __nv_bfloat16* rrow =
+          p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) +
+                           static_cast<long long>(b) * p.batch_stride_r + row * p.ldr
+                     : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the masked stores
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int n = n0 + c * 32;
+        if (!row_ok || n >= p.N) continue;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+        const bool full = (n + 32 <= p.N);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full || n + j < p.N) f[j] += p.bias[n + j];
+        }
+        if (rrow) {
+          if (full && ((p.ldr & 7) == 0)) {
+            const uint4* rp = reinterpret_cast<const uint4*>(rrow + n);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u = rp[q];
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 x = __bfloat1622float2(h[j]);
+                f[q * 8 + 2 * j] += x.x;
+                f[q * 8 + 2 * j + 1] += x.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n + j < p.N) f[j] += __bfloat162float(rrow[n + j]);
+          }
+        }
+        if (p.out_f32) {
+          float* crow = reinterpret_cast<float*>(cbase) + coff + n;
+          if (full && ((p.ldc & 3) == 0)) {
+            float4* cp = reinterpret_cast<float4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+              if (p.accumulate) {
+                float4 old = cp[q];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              cp[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n + j < p.N) crow[j] = f[j] + (p.accumulate ? crow[j] : 0.f);
+          }
+        } else {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(cbase) + coff + n;
+          if (full && ((p.ldc & 7) == 0)) {
+            uint4* cp = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (p.accumulate) {
+                uint4 u = cp[q];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 x = __bfloat1622float2(h[j]);
+                  f[q * 8 + 2 * j] += x.x;
+                  f[q * 8 + 2 * j + 1] += x.y;
+                }
+              }
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                oh[j] = __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+              cp[q] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n + j < p.N) {
+                float o = f[j] + (p.accumulate ? __bfloat162float(crow[j]) : 0.f);
+                crow[j] = __float2bfloat16(o);
+              }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// bf16 tensor map over (batch, outer, inner) with a {64, box_outer, 1} box and 128B swizzle.
+static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer,
+                     uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                     uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {ld_elems * 2, (batch > 1 ? batch_stride_elems : ld_elems * outer) * 2};
+  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+static int g_num_sms = 0;
+
+template <int A_MN, int B_MN>
+static cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                          int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<A_MN, B_MN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  gemm_bf16_tcgen05_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace ceo
+
+extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                             long long lda, long long ldb, long long ldc, int a_mn_major,
+                             int b_mn_major, int batch, long long batch_stride_a,
+                             long long batch_stride_b, long long batch_stride_c, int out_f32,
+                             int accumulate, float alpha, const float* bias, const void* residual,
+                             long long ldr, long long batch_stride_r, int* status, int max_ctas,
+                             cudaStream_t stream) {
+  using namespace ceo;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  // TMA needs 16-byte aligned bases and row strides
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (lda & 7) || (ldb & 7) || (batch > 1 && ((batch_stride_a & 7) || (batch_stride_b & 7))))
+    return -2;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn_major == 0)
+    rc = make_tmap(&ta, A, K, M, batch, lda, batch_stride_a, BM);
+  else
+    rc = make_tmap(&ta, A, M, K, batch, lda, batch_stride_a, BK);
+  if (rc) return -3;
+  if (b_mn_major == 0)
+    rc = make_tmap(&tb, B, K, N, batch, ldb, batch_stride_b, BN);
+  else
+    rc = make_tmap(&tb, B, N, K, batch, ldb, batch_stride_b, BK);
+  if (rc) return -4;
+
+  GemmParams p;
+  p.C = C;
+  p.residual = residual;
+  p.bias = bias;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ldr = ldr;
+  p.batch_stride_c = batch_stride_c;
+  p.batch_stride_r = batch_stride_r;
+  p.batch = batch;
+  p.out_f32 = out_f32;
+  p.accumulate = accumulate;
+  p.alpha = alpha;
+  p.num_m = (M + BM - 1) / BM;
+  p.num_n = (N + BN - 1) / BN;
+  p.status = status;
+  long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
+  int cap = g_num_sms;
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  int grid = static_cast<int>(total < cap ? total : cap);
+  cudaError_t e;
+  if (a_mn_major == 0 && b_mn_major == 0) e = launch<0, 0>(ta, tb, p, grid, stream);
+  else if (a_mn_major == 0) e = launch<0, 1>(ta, tb, p, grid, stream);
+  else if (b_mn_major == 0) e = launch<1, 0>(ta, tb, p, grid, stream);
+  else e = launch<1, 1>(ta, tb, p, grid, stream);
+  return static_cast<int>(e);
+}

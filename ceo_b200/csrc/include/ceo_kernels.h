@@ -1,0 +1,122 @@
+/* C ABI of the sm_100a kernel library (libceo_b200.so).
+ *
+ * Every entry point takes raw device pointers and a stream, allocates nothing
+ * (callers pass outputs and scratch), and returns 0 on success, a positive
+ * cudaError_t value when a launch failed, or a negative code for rejected
+ * arguments (-2 alignment, -3/-4 tensor-map encoding, -5 shape/dtype).
+ * bf16 tensors are row-major with the stated leading dimension in elements.
+ *
+ * This plays the role of the reference's kernels/cuda/include/kernels.h:35-421
+ * (26 prototypes); the Python shims in ceo_b200/ops bind it through ctypes the
+ * way src/kernels/*_kernels.zig bind the reference's.
+ */
+#ifndef CEO_KERNELS_H
+#define CEO_KERNELS_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CEO_NORM_BWD_MAX_BLOCKS 592  /* 148 SMs x 4 */
+#define CEO_SUMSQ_MAX_BLOCKS 1184    /* 148 SMs x 8 */
+
+/* ---- GEMM (tcgen05 / TMEM / TMA) -------------------------------------------
+ * C[b] (M x N) = alpha * A[b] (M x K) * B[b]^T (N x K)  (+bias[n]) (+residual) (+C if accumulate)
+ * a_mn_major = 0: A stored (M rows, K contiguous, lda); 1: A stored (K rows, M contiguous, lda)
+ * b_mn_major = 0: B stored (N rows, K contiguous, ldb); 1: B stored (K rows, N contiguous, ldb)
+ * out_f32: C is fp32 (else bf16).  residual is bf16.  `status` is a device int that the
+ * kernel sets non-zero if one of its bounded waits ran out (it then returns normally).
+ * max_ctas > 0 caps the persistent grid (leaves SMs free for a concurrent kernel). */
+int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                  long long ldb, long long ldc, int a_mn_major, int b_mn_major, int batch,
+                  long long batch_stride_a, long long batch_stride_b, long long batch_stride_c,
+                  int out_f32, int accumulate, float alpha, const float* bias,
+                  const void* residual, long long ldr, long long batch_stride_r, int* status,
+                  int max_ctas, cudaStream_t stream);
+
+/* ---- normalisation ---------------------------------------------------------- */
+int ceo_norm_bwd_blocks(int rows); /* rows of the partial scratch the bwd kernels need */
+int ceo_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out,
+                    float* rstd, int rows, int D, float eps, cudaStream_t stream);
+/* partial_scratch: fp32 [ceo_norm_bwd_blocks(rows)][D] */
+int ceo_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                    const void* dres, void* dx, float* dw, int dw_accumulate,
+                    float* partial_scratch, int rows, int D, cudaStream_t stream);
+int ceo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean,
+                      float* rstd, int rows, int D, float eps, cudaStream_t stream);
+/* partial_scratch: fp32 [ceo_norm_bwd_blocks(rows)][2*D] */
+int ceo_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                      const float* rstd, void* dx, float* dw, float* db, int accumulate,
+                      float* partial_scratch, int rows, int D, cudaStream_t stream);
+
+/* ---- activations ------------------------------------------------------------ */
+int ceo_swiglu_fwd(const void* gate_up, void* out, long long rows, int F, cudaStream_t stream);
+int ceo_swiglu_bwd(const void* dout, const void* gate_up, void* dgate_up, long long rows, int F,
+                   cudaStream_t stream);
+/* mode 0 tanh-GELU, 1 erf-GELU, 2 SiLU, 3 ReLU */
+int ceo_act_fwd(const void* x, void* y, long long n, int mode, cudaStream_t stream);
+int ceo_act_bwd(const void* dy, const void* x, void* dx, long long n, int mode,
+                cudaStream_t stream);
+int ceo_softmax_fwd(const float* x, float* y, int rows, int n, cudaStream_t stream);
+
+/* ---- loss ------------------------------------------------------------------- */
+int ceo_cross_entropy(const void* logits, int logits_f32, const long long* targets, float* loss,
+                      void* dlogits_bf16, int rows, int V, long long ld, long long ldd,
+                      float label_smoothing, const float* scale_ptr, float scale,
+                      long long ignore_index, cudaStream_t stream);
+
+/* ---- embedding -------------------------------------------------------------- */
+int ceo_embedding_fwd(const long long* ids, const void* table, void* out, long long n, int D,
+                      long long vocab, int* oob_count, cudaStream_t stream);
+int ceo_embedding_bwd(const long long* ids, const void* dy, float* dtable, long long n, int D,
+                      long long vocab, cudaStream_t stream);
+
+/* ---- optimizers / clipping ---------------------------------------------------- */
+int ceo_sumsq_blocks(long long n); /* floats of partial scratch ceo_sumsq / ceo_muon_momentum need */
+int ceo_sumsq(const void* x, int is_f32, long long n, float* out, int accumulate,
+              float* partial_scratch, cudaStream_t stream);
+int ceo_clip_scale(const float* sumsq, float max_norm, float* scale_out, float* norm_out,
+                   cudaStream_t stream);
+int ceo_scale(void* x, int is_f32, long long n, const float* scale_ptr, float scale,
+              cudaStream_t stream);
+int ceo_clip_value(float* x, long long n, float clip, cudaStream_t stream);
+int ceo_adamw_step(float* master, float* m, float* v, void* grad, int grad_f32, void* shadow_bf16,
+                   long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                   int step, const float* gscale_ptr, float gscale, int zero_grad,
+                   cudaStream_t stream);
+int ceo_lion_step(float* master, float* m, void* grad, int grad_f32, void* shadow_bf16,
+                  long long n, float lr, float beta1, float beta2, float weight_decay,
+                  const float* gscale_ptr, float gscale, int zero_grad, cudaStream_t stream);
+int ceo_muon_momentum(float* m, void* grad, int grad_f32, long long n, float beta,
+                      const float* gscale_ptr, float gscale, int zero_grad, float* sumsq_out,
+                      float* partial_scratch, cudaStream_t stream);
+int ceo_muon_normalize(const float* m, const float* sumsq, void* y_bf16, long long n, float eps,
+                       cudaStream_t stream);
+int ceo_ns_poly(void* g_bf16, const void* g2_bf16, int n, float a, float b, float c,
+                cudaStream_t stream);
+int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long long n, float lr,
+                   float weight_decay, float scale, cudaStream_t stream);
+
+/* ---- fill / cast / copy / reduce / fp8 (dtype: 0 fp32, 1 fp16, 2 bf16) ---------- */
+int ceo_fill(void* x, int dtype, long long n, float value, cudaStream_t stream);
+int ceo_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,
+             cudaStream_t stream);
+int ceo_copy(const void* src, void* dst, long long bytes, cudaStream_t stream);
+int ceo_axpby_f32(float* y, const float* x, long long n, float a, float b, cudaStream_t stream);
+int ceo_reduce_blocks(long long n);
+int ceo_reduce(const void* x, int dtype, long long n, int mode, float* out, float* partial_scratch,
+               cudaStream_t stream);
+int ceo_fp8_quantize(const void* x_bf16, void* q, long long n, const float* scale, float* amax_out,
+                     int kind, cudaStream_t stream);
+int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* scale, int kind,
+                       cudaStream_t stream);
+int ceo_fp8_update_scale(float* history, int hist_len, int* cursor, float* amax, float* scale,
+                         float fp8_max, float margin_pow2, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CEO_KERNELS_H */

@@ -1,0 +1,168 @@
+// Fill / cast / copy / reductions / FP8 quantisation with amax tracking.
+// Counterparts of the reference's fill_cuda, copy_cuda, cast_cuda, sum_reduce_cuda,
+// norm_cuda (kernels/cuda/init.cu:308-444, which reduce through a library device
+// reduction and a stream-ordered allocation) and of the header-only
+// quantize_fp8_cuda / dequantize_fp8_cuda (kernels/cuda/include/kernels.h:378-395).
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "common/util.cuh"
+#include "include/ceo_kernels.h"
+
+namespace ceo {
+
+// dtype codes of the C ABI: 0 fp32, 1 fp16, 2 bf16
+__device__ __forceinline__ float load_as_f32(const void* p, int dt, long long i) {
+  if (dt == 0) return static_cast<const float*>(p)[i];
+  if (dt == 1) return __half2float(static_cast<const __half*>(p)[i]);
+  return __bfloat162float(static_cast<const bf16*>(p)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void* p, int dt, long long i, float v) {
+  if (dt == 0) static_cast<float*>(p)[i] = v;
+  else if (dt == 1) static_cast<__half*>(p)[i] = __float2half_rn(v);
+  else static_cast<bf16*>(p)[i] = __float2bfloat16(v);
+}
+
+#define CEO_GRID_STRIDE(i, n)                                                              \
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; \
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+
+__global__ void fill_kernel(void* x, int dt, long long n, float v) {
+  CEO_GRID_STRIDE(i, n) store_from_f32(x, dt, i, v);
+}
+__global__ void cast_kernel(const void* src, int sdt, void* dst, int ddt, long long n) {
+  CEO_GRID_STRIDE(i, n) store_from_f32(dst, ddt, i, load_as_f32(src, sdt, i));
+}
+__global__ void copy16_kernel(const uint4* src, uint4* dst, long long n16) {
+  CEO_GRID_STRIDE(i, n16) dst[i] = src[i];
+}
+__global__ void copy1_kernel(const uint8_t* src, uint8_t* dst, long long n) {
+  CEO_GRID_STRIDE(i, n) dst[i] = src[i];
+}
+__global__ void axpby_kernel(float* y, const float* x, long long n, float a, float b) {
+  CEO_GRID_STRIDE(i, n) y[i] = (a != 0.f ? a * y[i] : 0.f) + b * x[i];
+}
+
+// partial[blk] = sum (or sum of squares) of this CTA's strided share, in fp32
+__global__ void __launch_bounds__(256)
+reduce_partial_kernel(const void* x, int dt, long long n, int squares, float* partial) {
+  __shared__ float red[33];
+  float s = 0.f;
+  CEO_GRID_STRIDE(i, n) {
+    const float v = load_as_f32(x, dt, i);
+    s += squares ? v * v : v;
+  }
+  s = block_reduce_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(256)
+reduce_final_kernel(const float* partial, int nblk, float* out, int take_sqrt) {
+  __shared__ float red[33];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nblk; i += blockDim.x) s += partial[i];
+  s = block_reduce_sum(s, red);
+  if (threadIdx.x == 0) *out = take_sqrt ? sqrtf(s) : s;
+}
+
+// ---- FP8: q = sat(x * scale); amax_out = max(amax_out, max|x|) ; kind 0 e4m3, 1 e5m2
+__global__ void __launch_bounds__(256)
+fp8_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, long long n,
+                 const float* __restrict__ scale, float* amax_out, int kind) {
+  __shared__ float red[33];
+  const float s = *scale;
+  float am = 0.f;
+  CEO_GRID_STRIDE(i, n) {
+    const float v = __bfloat162float(x[i]);
+    am = fmaxf(am, fabsf(v));
+    q[i] = static_cast<uint8_t>(
+        __nv_cvt_float_to_fp8(v * s, __NV_SATFINITE, kind == 0 ? __NV_E4M3 : __NV_E5M2));
+  }
+  am = block_reduce_max(am, red);
+  if (threadIdx.x == 0 && amax_out) atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(am));
+}
+__global__ void fp8_dequant_kernel(const uint8_t* __restrict__ q, bf16* __restrict__ x,
+                                   long long n, const float* __restrict__ scale, int kind) {
+  const float inv = 1.f / *scale;
+  CEO_GRID_STRIDE(i, n) {
+    const __half_raw h =
+        __nv_cvt_fp8_to_halfraw(q[i], kind == 0 ? __NV_E4M3 : __NV_E5M2);
+    x[i] = __float2bfloat16(__half2float(__half(h)) * inv);
+  }
+}
+// Delayed scaling: push amax into a ring history, scale = fp8_max / (max(history) * 2^margin)
+__global__ void fp8_update_scale_kernel(float* history, int hist_len, int* cursor, float* amax,
+                                        float* scale, float fp8_max, float margin_pow2) {
+  history[*cursor % hist_len] = *amax;
+  *cursor = (*cursor + 1) % hist_len;
+  float m = 0.f;
+  for (int i = 0; i < hist_len; ++i) m = fmaxf(m, history[i]);
+  *scale = (m > 0.f && isfinite(m)) ? fp8_max / (m * margin_pow2) : 1.f;
+  *amax = 0.f;
+}
+
+constexpr int GEN_CAP = 148 * 8;
+
+}  // namespace ceo
+using namespace ceo;
+
+extern "C" int ceo_fill(void* x, int dtype, long long n, float value, cudaStream_t stream) {
+  if (n <= 0 || dtype < 0 || dtype > 2) return -5;
+  fill_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(x, dtype, n, value);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,
+                        cudaStream_t stream) {
+  if (n <= 0 || src_dtype < 0 || src_dtype > 2 || dst_dtype < 0 || dst_dtype > 2) return -5;
+  cast_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(src, src_dtype, dst, dst_dtype, n);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_copy(const void* src, void* dst, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return -5;
+  const bool al = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                    static_cast<uintptr_t>(bytes)) & 15) == 0;
+  if (al)
+    copy16_kernel<<<grid_for(bytes >> 4, 1024, GEN_CAP), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), bytes >> 4);
+  else
+    copy1_kernel<<<grid_for(bytes, 1024, GEN_CAP), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), bytes);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_axpby_f32(float* y, const float* x, long long n, float a, float b,
+                             cudaStream_t stream) {
+  if (n <= 0) return -5;
+  axpby_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(y, x, n, a, b);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_reduce_blocks(long long n) { return grid_for(n, 2048, CEO_SUMSQ_MAX_BLOCKS); }
+// mode 0: sum, 1: sum of squares, 2: L2 norm
+extern "C" int ceo_reduce(const void* x, int dtype, long long n, int mode, float* out,
+                          float* partial_scratch, cudaStream_t stream) {
+  if (n <= 0 || dtype < 0 || dtype > 2 || mode < 0 || mode > 2) return -5;
+  const int nblk = ceo_reduce_blocks(n);
+  reduce_partial_kernel<<<nblk, 256, 0, stream>>>(x, dtype, n, mode != 0, partial_scratch);
+  reduce_final_kernel<<<1, 256, 0, stream>>>(partial_scratch, nblk, out, mode == 2);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_fp8_quantize(const void* x_bf16, void* q, long long n, const float* scale,
+                                float* amax_out, int kind, cudaStream_t stream) {
+  if (n <= 0 || kind < 0 || kind > 1) return -5;
+  fp8_quant_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(
+      static_cast<const bf16*>(x_bf16), static_cast<uint8_t*>(q), n, scale, amax_out, kind);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* scale,
+                                  int kind, cudaStream_t stream) {
+  if (n <= 0 || kind < 0 || kind > 1) return -5;
+  fp8_dequant_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(q), static_cast<bf16*>(x_bf16), n, scale, kind);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_fp8_update_scale(float* history, int hist_len, int* cursor, float* amax,
+                                    float* scale, float fp8_max, float margin_pow2,
+                                    cudaStream_t stream) {
+  if (hist_len <= 0) return -5;
+  fp8_update_scale_kernel<<<1, 1, 0, stream>>>(history, hist_len, cursor, amax, scale, fp8_max,
+                                               margin_pow2);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,329 @@
+// Fused RMSNorm / LayerNorm forward and backward, bf16 in/out, fp32 math.
+//
+// Forward can fold the residual add of a pre-norm block (h = x + r; y = norm(h))
+// and writes h once.  Backward folds the incoming residual gradient and builds
+// the weight gradient from per-CTA fp32 partial sums (a scratch buffer) that a
+// second kernel reduces - the reference adds floats into a bf16 buffer through a
+// reinterpret cast (kernels/cuda/layernorm.cu:121-124) and has no LayerNorm
+// backward at all (layernorm.cu:133-183).
+#include "common/util.cuh"
+#include "include/ceo_kernels.h"
+
+namespace ceo {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 4;  // 8-element vectors per thread -> D <= 8192
+
+// ------------------------------------------------------------- RMSNorm fwd
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                   const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ h_out,
+                   float* __restrict__ rstd, int rows, int D, float eps) {
+  __shared__ float red[33];
+  const int nv = D >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * D);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * D)
+                          : nullptr;
+    float v[NORM_MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        unpack8(xr[c], v[i]);
+        if (rr) {
+          float t[8];
+          unpack8(rr[c], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+          if (h_out) {
+            uint4 hv = pack8(v[i]);
+            reinterpret_cast<uint4*>(h_out + static_cast<size_t>(row) * D)[c] = hv;
+            unpack8(hv, v[i]);  // normalise exactly what was stored
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = block_reduce_sum(ss, red);
+    const float rs = rsqrtf(ss / D + eps);
+    if (threadIdx.x == 0 && rstd) rstd[row] = rs;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float wv[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[c], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rs * wv[j];
+        reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * D)[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------- RMSNorm bwd
+// dx = rs * (dy*w) - x * rs^3 * mean(dy*w*x)   (+ dres when given)
+// dw partial[blk][c] = sum over this CTA's rows of dy * x * rs
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                   const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                   float* __restrict__ partial, int rows, int D) {
+  __shared__ float red[33];
+  const int nv = D >> 3;
+  float dwacc[NORM_MAXV][8];
+  float wv[NORM_MAXV][8];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < nv) unpack8(reinterpret_cast<const uint4*>(w)[c], wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * D;
+    const float rs = rstd[row];
+    float xv[NORM_MAXV][8], gv[NORM_MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        unpack8(reinterpret_cast<const uint4*>(x + off)[c], xv[i]);
+        unpack8(reinterpret_cast<const uint4*>(dy + off)[c], gv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[i][j] += gv[i][j] * xv[i][j] * rs;
+          gv[i][j] *= wv[i][j];
+          dot += gv[i][j] * xv[i][j];
+        }
+      }
+    }
+    dot = block_reduce_sum(dot, red);
+    const float coef = dot * rs * rs * rs / D;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * rs - xv[i][j] * coef;
+        if (dres) {
+          float t[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + off)[c], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += t[j];
+        }
+        reinterpret_cast<uint4*>(dx + off)[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nv) {
+      float* pp = partial + static_cast<size_t>(blockIdx.x) * D + c * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pp[j] = dwacc[i][j];
+    }
+  }
+}
+
+// out[c] (+)= sum_b partial[b][c]
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                       int nblk, int D, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int b = 0; b < nblk; ++b) s += partial[static_cast<size_t>(b) * D + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ----------------------------------------------------------- LayerNorm fwd
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                     const bf16* __restrict__ b, bf16* __restrict__ y, float* __restrict__ mean,
+                     float* __restrict__ rstd, int rows, int D, float eps) {
+  __shared__ float red[33];
+  const int nv = D >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * D;
+    float v[NORM_MAXV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        unpack8(reinterpret_cast<const uint4*>(x + off)[c], v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+      }
+    }
+    const float mu = block_reduce_sum(s, red) / D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[i][j] - mu;
+          q += d * d;
+        }
+      }
+    }
+    const float rs = rsqrtf(block_reduce_sum(q, red) / D + eps);
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float wv[8], bv[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[c], wv);
+        if (b) unpack8(reinterpret_cast<const uint4*>(b)[c], bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mu) * rs * wv[j] + (b ? bv[j] : 0.f);
+        reinterpret_cast<uint4*>(y + off)[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------- LayerNorm bwd
+// xhat = (x-mu)*rs; g = dy*w; dx = rs*(g - mean(g) - xhat*mean(g*xhat))
+// partial rows: [blk][0:D] = dw, [blk][D:2D] = db
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                     const bf16* __restrict__ w, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, bf16* __restrict__ dx,
+                     float* __restrict__ partial, int rows, int D) {
+  __shared__ float red[33];
+  const int nv = D >> 3;
+  float dwacc[NORM_MAXV][8], dbacc[NORM_MAXV][8], wv[NORM_MAXV][8];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = dbacc[i][j] = 0.f;
+    if (c < nv) unpack8(reinterpret_cast<const uint4*>(w)[c], wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * D;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        unpack8(reinterpret_cast<const uint4*>(x + off)[c], xh[i]);
+        unpack8(reinterpret_cast<const uint4*>(dy + off)[c], g[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mu) * rs;
+          dwacc[i][j] += g[i][j] * xh[i][j];
+          dbacc[i][j] += g[i][j];
+          g[i][j] *= wv[i][j];
+          s1 += g[i][j];
+          s2 += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = block_reduce_sum(s1, red) / D;
+    s2 = block_reduce_sum(s2, red) / D;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - s1 - xh[i][j] * s2);
+        reinterpret_cast<uint4*>(dx + off)[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nv) {
+      float* pw = partial + static_cast<size_t>(blockIdx.x) * 2 * D + c * 8;
+      float* pb = pw + D;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        pw[j] = dwacc[i][j];
+        pb[j] = dbacc[i][j];
+      }
+    }
+  }
+}
+
+static bool norm_shape_ok(int rows, int D) {
+  return rows > 0 && D > 0 && (D & 7) == 0 && D <= NORM_THREADS * 8 * NORM_MAXV;
+}
+
+}  // namespace ceo
+
+using namespace ceo;
+
+extern "C" int ceo_norm_bwd_blocks(int rows) {
+  int g = rows < CEO_NORM_BWD_MAX_BLOCKS ? rows : CEO_NORM_BWD_MAX_BLOCKS;
+  return g < 1 ? 1 : g;
+}
+
+extern "C" int ceo_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y,
+                               void* h_out, float* rstd, int rows, int D, float eps,
+                               cudaStream_t stream) {
+  if (!norm_shape_ok(rows, D)) return -5;
+  rmsnorm_fwd_kernel<<<rows, NORM_THREADS, 0, stream>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(residual), static_cast<const bf16*>(w),
+      static_cast<bf16*>(y), static_cast<bf16*>(h_out), rstd, rows, D, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ceo_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                               const void* dres, void* dx, float* dw, int dw_accumulate,
+                               float* partial_scratch, int rows, int D, cudaStream_t stream) {
+  if (!norm_shape_ok(rows, D)) return -5;
+  const int nblk = ceo_norm_bwd_blocks(rows);
+  rmsnorm_bwd_kernel<<<nblk, NORM_THREADS, 0, stream>>>(
+      static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
+      static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial_scratch, rows, D);
+  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial_scratch, dw, nblk, D,
+                                                              dw_accumulate);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ceo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean,
+                                 float* rstd, int rows, int D, float eps, cudaStream_t stream) {
+  if (!norm_shape_ok(rows, D)) return -5;
+  layernorm_fwd_kernel<<<rows, NORM_THREADS, 0, stream>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(w), static_cast<const bf16*>(b),
+      static_cast<bf16*>(y), mean, rstd, rows, D, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ceo_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                                 const float* rstd, void* dx, float* dw, float* db,
+                                 int accumulate, float* partial_scratch, int rows, int D,
+                                 cudaStream_t stream) {
+  if (!norm_shape_ok(rows, D)) return -5;
+  const int nblk = ceo_norm_bwd_blocks(rows);
+  layernorm_bwd_kernel<<<nblk, NORM_THREADS, 0, stream>>>(
+      static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), mean,
+      rstd, static_cast<bf16*>(dx), partial_scratch, rows, D);
+  // the partial buffer interleaves [dw | db] per CTA: reduce with a row stride of 2*D
+  reduce_partials_kernel<<<(2 * D + 255) / 256, 256, 0, stream>>>(partial_scratch,
+                                                                  partial_scratch, nblk, 2 * D, 0);
+  // partial_scratch[0:2D] now holds the totals (row 0 is summed in place: reads of row 0
+  // happen before the single write per column in the same thread)
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return ceo_axpby_f32(dw, partial_scratch, D, accumulate ? 1.f : 0.f, 1.f, stream) |
+         (db ? ceo_axpby_f32(db, partial_scratch + D, D, accumulate ? 1.f : 0.f, 1.f, stream) : 0);
+}

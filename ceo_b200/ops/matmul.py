@@ -1,0 +1,132 @@
+"""bf16 GEMM on tcgen05/TMEM (``csrc/gemm_tcgen05.cu``) and the autograd Linear on top of it.
+
+Layout vocabulary: the kernel computes ``C[M,N] = alpha * A[M,K] @ B[N,K]^T`` and
+each operand may be stored K-major (rows of K) or MN-major (rows of M or N), so
+forward, data-gradient and weight-gradient all read their tensors in place with
+no transpose copy.  Weights are kept ``(out_features, in_features)``; the
+reference stores ``(in, out)`` (src/nn/layers.zig:509,529) - the checkpoint
+writer transposes.
+
+The weight gradient can be accumulated straight into an fp32 ``main_grad``
+buffer by the GEMM epilogue, which is how micro-batch gradient accumulation is
+done without a separate add kernel.  Replaces gemm_forward_cuda /
+gemm_backward_cuda of the reference (kernels/cuda/gemm.cu:303, 400).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _as2d(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dim() == 2 else t.reshape(-1, t.shape[-1])
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """``out = alpha * A @ B^T (+ bias) (+ residual) (+ out if accumulate)``.
+
+    ``a`` is ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b`` is ``(N, K)`` (or ``(K, N)``
+    when ``b_mn``).  A leading batch dimension on both makes it a batched GEMM.
+    """
+    batched = a.dim() == 3
+    if batched:
+        assert b.dim() == 3 and a.shape[0] == b.shape[0]
+        nb = a.shape[0]
+        a2, b2 = a[0], b[0]
+    else:
+        nb = 1
+        a2, b2 = a, b
+    if a_mn:
+        K, M = a2.shape
+    else:
+        M, K = a2.shape
+    if b_mn:
+        Kb, N = b2.shape
+    else:
+        N, Kb = b2.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+
+    if not a.is_cuda:  # fp32 oracle path
+        af = a.float().transpose(-1, -2) if a_mn else a.float()
+        bf = b.float() if b_mn else b.float().transpose(-1, -2)
+        r = alpha * (af @ bf)
+        if bias is not None:
+            r = r + bias.float()
+        if residual is not None:
+            r = r + residual.float()
+        if out is not None:
+            if accumulate:
+                r = r + out.float()
+            out.copy_(r.to(out.dtype))
+            return out
+        return r.to(out_dtype)
+
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a2.stride(-1) == 1 and b2.stride(-1) == 1, "operands must have a unit inner stride"
+    if out is None:
+        shape = (nb, M, N) if batched else (M, N)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+        assert not accumulate
+    assert out.stride(-1) == 1
+    out_f32 = out.dtype == torch.float32
+    assert out_f32 or out.dtype == torch.bfloat16
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.stride(-1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous()
+    rc = _lib.lib().ceo_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+        a2.stride(0), b2.stride(0), out.stride(-2), int(a_mn), int(b_mn), nb,
+        a.stride(0) if batched else 0, b.stride(0) if batched else 0,
+        out.stride(0) if batched else 0, int(out_f32), int(accumulate), float(alpha),
+        _lib.ptr(bias), _lib.ptr(residual),
+        residual.stride(-2) if residual is not None else 0,
+        residual.stride(0) if (residual is not None and batched) else 0,
+        _lib.status_word(a.device).data_ptr(), int(max_ctas), _lib.stream())
+    _lib.check(rc, "ceo_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T (+ residual); dW accumulated into ``weight.main_grad`` when present."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual):
+        x2 = _as2d(x)
+        y = gemm(x2, weight, residual=_as2d(residual) if residual is not None else None)
+        ctx.save_for_backward(x2, weight)
+        ctx.weight_ref = weight  # the Parameter object itself (carries .main_grad)
+        ctx.x_shape = x.shape
+        ctx.has_res = residual is not None
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, _ = ctx.saved_tensors
+        weight = ctx.weight_ref
+        dy2 = _as2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                weight.grad_touched = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        dres = dy if ctx.has_res else None
+        return dx, dw, dres
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ residual)`` with ``weight`` of shape ``(out, in)``."""
+    return _LinearFn.apply(x, weight, residual)

@@ -1,0 +1,107 @@
+"""Per-kernel timings against the measured roofline: ``python -m ceo_b200.utils.kernel_bench``.
+
+Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2
+flush (a write of a buffer larger than L2) before every timed launch, and reported as
+the median of the timed launches.  The denominators are the measured copy bandwidth and
+library bf16 GEMM throughput in ``MEASURED_PEAKS.json`` at the repository root when that
+file exists ("of measured"), else 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+``--torch`` also times the PyTorch/library op of the same shape for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+from ..ops import matmul as G, nn as N
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_flush = None
+
+
+def time_ms(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--d-model", type=int, default=2048)
+    ap.add_argument("--ffn", type=int, default=5632)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--torch", action="store_true")
+    ap.add_argument("--json", type=str, default="")
+    a = ap.parse_args(argv)
+    bw, fl, kind = peaks()
+    dev = "cuda"
+    M, D, Fh = a.tokens, a.d_model, a.ffn
+    rows = []
+
+    def rec(name, ms, flops=0.0, bytes_=0.0, base_ms=None):
+        r = {"kernel": name, "ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r[f"frac_of_{kind}_gemm_peak"] = round(flops / (ms * 1e-3) / fl, 3)
+        if bytes_:
+            r["gbs"] = round(bytes_ / ms / 1e6, 1)
+            r[f"frac_of_{kind}_hbm"] = round(bytes_ / (ms * 1e-3) / bw, 3)
+        if base_ms is not None:
+            r["torch_ms"] = round(base_ms, 4)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+
+    x = torch.randn(M, D, device=dev).bfloat16()
+    for name, n_out, k_in in (("qkv", 3 * D, D), ("gate_up", 2 * Fh, D), ("down", D, Fh),
+                              ("out", D, D)):
+        xin = x if k_in == D else torch.randn(M, k_in, device=dev).bfloat16()
+        w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
+        dy = torch.randn(M, n_out, device=dev).bfloat16()
+        mg = torch.zeros(n_out, k_in, device=dev)
+        fl_ = 2.0 * M * n_out * k_in
+        tb = time_ms(lambda: xin @ w.t()) if a.torch else None
+        rec(f"gemm_fwd_{name} {M}x{n_out}x{k_in}", time_ms(lambda: G.gemm(xin, w)), fl_, 0, tb)
+        tb = time_ms(lambda: dy @ w) if a.torch else None
+        rec(f"gemm_dgrad_{name}", time_ms(lambda: G.gemm(dy, w, b_mn=True)), fl_, 0, tb)
+        tb = time_ms(lambda: mg.addmm_(dy.t().float(), xin.float())) if False else None
+        tb = time_ms(lambda: dy.t() @ xin) if a.torch else None
+        rec(f"gemm_wgrad_{name} (fp32 accumulate)",
+            time_ms(lambda: G.gemm(dy, xin, a_mn=True, b_mn=True, out=mg, accumulate=True)),
+            fl_, 0, tb)
+
+    w = torch.ones(D, device=dev).bfloat16()
+    y, _ = N.rmsnorm(x, w)
+    rec("rmsnorm_fwd", time_ms(lambda: N.rmsnorm(x, w)), 0, 2.0 * M * D * 2,
+        time_ms(lambda: torch.nn.functional.rms_norm(x, (D,), w)) if a.torch else None)
+    gu = torch.randn(M, 2 * Fh, device=dev).bfloat16()
+    rec("swiglu_fwd", time_ms(lambda: N.swiglu(gu)), 0, 3.0 * M * Fh * 2)
+    if a.json:
+        Path(a.json).write_text(json.dumps(rows, indent=1))
+
+
+if __name__ == "__main__":
+    main()
