@@ -330,6 +330,13 @@ static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t 
                      uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
+  // The driver entry point needs a current context; a thread that has made no runtime
+  // call yet (an autograd worker thread, for one) has none until the runtime binds it.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[3] = {inner, outer, batch};
   cuuint64_t strides[2] = {ld_elems * 2, (batch > 1 ? batch_stride_elems : ld_elems * outer) * 2};
   cuuint32_t box[3] = {64, box_outer, 1};
@@ -337,6 +344,13 @@ static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t 
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "ceo: cuTensorMapEncodeTiled failed (%d): ptr=%p dims={%llu,%llu,%llu} strides={%llu,%llu} "
+            "box={64,%u,1}\n",
+            static_cast<int>(r), ptr, (unsigned long long)dims[0], (unsigned long long)dims[1],
+            (unsigned long long)dims[2], (unsigned long long)strides[0],
+            (unsigned long long)strides[1], box_outer);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 

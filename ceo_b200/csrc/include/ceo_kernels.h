@@ -37,6 +37,21 @@ int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
                   const void* residual, long long ldr, long long batch_stride_r, int* status,
                   int max_ctas, cudaStream_t stream);
 
+/* ---- EFLA (chunked delta rule), chunk = 64, D in {64, 128}, T % 64 == 0 -------------
+ * q,k,v: bf16 (B,T,H,D) with a token stride in elements (slices of a fused QKV output are
+ * fine); alpha fp32 (B,T,H); s0 / s_final / ds_final / ds0 fp32 (B,H,D,D) (s0, ds_final may
+ * be NULL).  Saved for backward: w, up (bf16 (B,T,H,D)), states (bf16 (B,H,T/64,D,D)).
+ * Backward workspaces: dloc, dup (bf16 (B,T,H,D)), dstates (bf16 (B,H,T/64,D,D)). */
+int ceo_efla_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* s0,
+                 void* w, void* up, void* states, void* o, float* s_final, int B, int T, int H,
+                 int D, long long q_stride, long long k_stride, long long v_stride, int* status,
+                 cudaStream_t stream);
+int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha, const void* w,
+                 const void* up, const void* states, const void* dO, const float* ds_final,
+                 void* dloc, void* dup, void* dstates, void* dq, void* dk, void* dv, float* dalpha,
+                 float* ds0, int B, int T, int H, int D, long long q_stride, long long k_stride,
+                 long long v_stride, int* status, cudaStream_t stream);
+
 /* ---- normalisation ---------------------------------------------------------- */
 int ceo_norm_bwd_blocks(int rows); /* rows of the partial scratch the bwd kernels need */
 int ceo_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out,

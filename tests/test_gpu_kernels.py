@@ -110,7 +110,7 @@ def test_rmsnorm(rows, D, with_res):
     wr = w.detach().float().requires_grad_()
     hr = xr + rr if with_res else xr
     if with_res:
-        hr = hr.to(torch.bfloat16).float() + (hr - hr.detach())  # stored h is bf16
+        hr = hr + (hr.to(torch.bfloat16).float() - hr).detach()  # stored h is bf16
     yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
     loss = (yr * dy.float()).sum() + ((hr * dh.float()).sum() if with_res else 0)
     loss.backward()
