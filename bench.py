@@ -1,0 +1,230 @@
+"""Headline benchmark: training tokens/s of EFLA-1.3B (configs/efla_1p3b.yaml) on N GPUs
+of one node.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+A step is one optimizer step over the configured global batch (256 sequences of 4096
+tokens = 1M tokens, fixed as N grows: strong scaling), run as micro-batches with fp32
+gradient accumulation, then gradient reduce-scatter, AdamW on the sharded fp32 master
+weights and parameter all-gather.  Tokens are seeded Zipf(1.1) over the vocabulary and the
+weights N(0, 0.02): synthetic data, random initialisation.
+
+Two timed regions, each bracketed by a barrier and a device synchronise, timed with CUDA
+events, max over ranks: (1) `value`: K steps with the step's inputs already on the device;
+(2) `e2e`: K steps through ``TrainEngine.train_step`` with the inputs in pinned host
+memory (copied host->device inside the step) and the loss read back to the host every
+step.  Every micro-batch streams far more than L2 (126 MB) through the device, so no
+explicit L2 flush is needed between timed iterations.
+
+``--impl reference`` reports why the reference cannot be run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+REFERENCE_UNAVAILABLE = (
+    "reference is a Zig project with no setup.py/pyproject.toml: `pip install --no-index "
+    "--target baseline/_ref /root/reference` answers 'not installable', Zig is not in the "
+    "image, and its model forward rejects non-CPU devices (src/model/model.zig:378-380)")
+
+CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(prefix="ceo_clocks_", suffix=".csv")
+        self.proc = None
+        self.idx = gpu_index
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+                power.append(float(p[3]))
+            except ValueError:
+                continue
+            for nme, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        busy = [s for s, w in zip(sm, power) if w > 300] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "power_w_max": max(power) if power else None, "samples": len(sm)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=os.path.join(ROOT, "configs", "efla_1p3b.yaml"))
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch")
+    ap.add_argument("--global-batch", type=int, default=0, help="sequences per step (all GPUs)")
+    ap.add_argument("--seq-len", type=int, default=0)
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--skip-e2e", action="store_true")
+    a = ap.parse_args(argv)
+
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    from ceo_b200.data.synthetic import SyntheticTokens
+    from ceo_b200.ops import _lib
+    from ceo_b200.parallel.comm import Comm, init_distributed
+    from ceo_b200.runtime.engine import TrainEngine
+    from ceo_b200.utils.config import Config
+
+    rank, world, local = init_distributed()
+    if world != a.gpus:
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE is {world}: launch with torchrun")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        if a.comm in ("auto", "fused"):
+            try:
+                from ceo_b200.parallel.fused import FusedComm
+                comm = FusedComm()
+            except Exception as e:  # noqa: BLE001
+                if a.comm == "fused":
+                    raise
+                if rank == 0:
+                    print(f"[bench] fused collectives unavailable ({e}); using NCCL",
+                          file=sys.stderr)
+        if comm is None:
+            comm = Comm()
+
+    cfg = Config.parse_from_file(a.config)
+    cfg.runtime.world_size = world
+    cfg.runtime.tensor_parallel_size = 1
+    seq = a.seq_len or cfg.data.seq_len
+    gbs = a.global_batch or cfg.training.global_batch_size
+    mbs = a.micro_batch or cfg.training.micro_batch_size
+    if gbs % (mbs * world):
+        raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x {world}")
+    n_micro = gbs // (mbs * world)
+    tokens_per_step = gbs * seq
+
+    eng = TrainEngine(cfg, dev, comm)
+    data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
+                           cfg.data.synthetic.s, cfg.data.synthetic.seed, rank)
+    host = [data.batch(mbs, seq, pin=True) for _ in range(n_micro)]
+    on_dev = [(t.to(dev), g.to(dev)) for t, g in host]
+    lr = cfg.training.learning_rate
+
+    def sync():
+        if comm is not None:
+            comm.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        eng.train_step(on_dev, lr)
+    sync()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- region 1: device-resident inputs ---------------------------------------------
+    l0 = _lib.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(a.steps):
+        loss, gnorm = eng.train_step(on_dev, lr)
+    e1.record()
+    sync()
+    launches = _lib.launch_count - l0
+    ms = e0.elapsed_time(e1)
+    ms = comm.max_over_ranks(ms) if comm is not None else ms
+    last_loss = float(loss)
+    # ---- region 2: end to end through the public API ------------------------------------
+    e2e = None
+    if not a.skip_e2e:
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        e2.record()
+        for _ in range(a.steps):
+            loss, gnorm = eng.train_step(host, lr)
+            last_loss = loss.item()  # device -> host read of the step's result
+        e3.record()
+        sync()
+        ms2 = e2.elapsed_time(e3)
+        ms2 = comm.max_over_ranks(ms2) if comm is not None else ms2
+        e2e = {"value": tokens_per_step * a.steps / (ms2 * 1e-3), "unit": "tokens/s",
+               "ms_per_step": ms2 / a.steps,
+               "h2d_bytes_per_step": sum(t.numel() * 8 + g.numel() * 8 for t, g in host) * world,
+               "d2h_bytes_per_step": 4 * world}
+    clocks = sampler.stop() if rank == 0 else None
+    status = _lib.read_status(dev)
+    if rank == 0:
+        value = tokens_per_step * a.steps / (ms * 1e-3)
+        flops = eng.model.flops_per_token(seq) * value
+        out = {
+            "metric": "train tokens/sec (box, device-timed, max over ranks) EFLA-1.3B",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded Zipf(1.1) tokens, N(0,0.02) random-init weights)",
+            "config": {"model": cfg.model.name, "global_batch": gbs, "seq_len": seq,
+                       "tokens_per_step": tokens_per_step, "micro_batch": mbs,
+                       "grad_accum_steps": n_micro, "parallelism": f"fsdp{world}",
+                       "optimizer": cfg.training.optimizer,
+                       "collectives": type(comm).__name__ if comm else "none",
+                       "l2": "inputs larger than L2 (each micro-batch streams >1 GB)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "model_tflops_per_gpu": flops / world / 1e12, "final_loss": last_loss,
+            "wait_status": status, "impl": "ours",
+        }
+        print(json.dumps(out))
+    if comm is not None:
+        comm.barrier()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

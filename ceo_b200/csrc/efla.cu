@@ -294,7 +294,8 @@ __global__ void __launch_bounds__(256)
 efla_bwd_local_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                       const bf16* __restrict__ up, const bf16* __restrict__ states,
                       const bf16* __restrict__ dO, bf16* __restrict__ dq,
-                      bf16* __restrict__ dloc, int T, int H, long long qs, long long ks) {
+                      bf16* __restrict__ dloc, int T, int H, long long qs, long long ks,
+                      long long dqs) {
   constexpr int LD = D + 8, NT = D / 16;
   extern __shared__ __align__(16) uint8_t smem[];
   bf16* Qs = reinterpret_cast<bf16*>(smem);
@@ -346,7 +347,7 @@ efla_bwd_local_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     zero_acc<NT>(acc);
     warp_gemm<NT, D, false, false>(acc, dOs + 16 * r * LD, LD, Sb + c0 * LD, LD);
     warp_gemm<NT, CH, false, true>(acc, dPs + 16 * r * XLD, XLD, Ks + c0, LD);
-    frag_store_bf16<NT>(dq + (tok0 + 16 * r) * HD + h * D + c0, HD, acc);
+    frag_store_bf16<NT>(dq + (tok0 + 16 * r) * dqs + h * D + c0, dqs, acc);
   }
   {
     float acc[NT][4];
@@ -474,7 +475,7 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                       const bf16* __restrict__ dO, const bf16* __restrict__ dup,
                       const bf16* __restrict__ dstates, bf16* __restrict__ dk,
                       bf16* __restrict__ dv, float* __restrict__ dalpha, int T, int H,
-                      long long qs, long long ks, long long vs) {
+                      long long qs, long long ks, long long vs, long long dks, long long dvs) {
   constexpr int LD = D + 8, NT = D / 16;
   extern __shared__ __align__(16) uint8_t smem[];
   bf16* Qs = reinterpret_cast<bf16*>(smem);
@@ -554,7 +555,7 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
         p[hf] += zacc[nt][2 * hf] * (vv.x - racc[nt][2 * hf]) +
                  zacc[nt][2 * hf + 1] * (vv.y - racc[nt][2 * hf + 1]);
         const float a = al[row];
-        *reinterpret_cast<bf162*>(dv + (tok0 + row) * HD + h * D + col) =
+        *reinterpret_cast<bf162*>(dv + (tok0 + row) * dvs + h * D + col) =
             __floats2bfloat162_rn(a * zacc[nt][2 * hf], a * zacc[nt][2 * hf + 1]);
       }
 #pragma unroll
@@ -622,8 +623,139 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
   cp_async_wait<0>();
   __syncthreads();
   warp_gemm<NT, D, false, false>(kacc, Ups + 16 * r * LD, LD, Sb + c0 * LD, LD);
-  frag_store_bf16<NT>(dk + (tok0 + 16 * r) * HD + h * D + c0, HD, kacc);
+  frag_store_bf16<NT>(dk + (tok0 + 16 * r) * dks + h * D + c0, dks, kacc);
   if (threadIdx.x < CH) dalpha[(tok0 + threadIdx.x) * H + h] = dal[threadIdx.x];
+}
+
+// ===================================================== q/k normalisation + coefficient
+// One warp per (token, head).  normalize: qn = q/|q|, kn = k/|k| and lambda = 1, so
+// alpha = 1 - exp(-beta); otherwise qn = q, kn = k and alpha = c(beta, |k|^2) with the
+// small-lambda series of the reference (kernels/cuda/efla.cu:93-115).
+__device__ __forceinline__ float efla_coeff(float beta, float lam) {
+  if (lam <= 1e-6f) {
+    const float bl = beta * lam;
+    return beta * (1.f - bl * (0.5f - bl * (1.f / 6.f - bl * (1.f / 24.f))));
+  }
+  return -expm1f(-beta * lam) / lam;
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+efla_prep_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
+                     const float* __restrict__ beta, int beta_scalar, bf16* __restrict__ qn,
+                     bf16* __restrict__ kn, float* __restrict__ rq, float* __restrict__ rk,
+                     float* __restrict__ alpha, long long rows, int H, long long qs, long long ks,
+                     int normalize) {
+  constexpr int E = D / 32;
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long id = wid; id < rows * H; id += nw) {
+    const long long tok = id / H;
+    const int h = static_cast<int>(id - tok * H);
+    float qv[E], kv[E];
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      const float2 a = __bfloat1622float2(
+          *reinterpret_cast<const bf162*>(q + tok * qs + h * D + lane * E + e));
+      const float2 b = __bfloat1622float2(
+          *reinterpret_cast<const bf162*>(k + tok * ks + h * D + lane * E + e));
+      qv[e] = a.x; qv[e + 1] = a.y; kv[e] = b.x; kv[e + 1] = b.y;
+      sq += a.x * a.x + a.y * a.y;
+      sk += b.x * b.x + b.y * b.y;
+    }
+    sq = warp_reduce_sum(sq);
+    sk = warp_reduce_sum(sk);
+    const float iq = normalize ? rsqrtf(sq + 1e-6f) : 1.f;
+    const float ik = normalize ? rsqrtf(sk + 1e-6f) : 1.f;
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      *reinterpret_cast<bf162*>(qn + id * D + lane * E + e) =
+          __floats2bfloat162_rn(qv[e] * iq, qv[e + 1] * iq);
+      *reinterpret_cast<bf162*>(kn + id * D + lane * E + e) =
+          __floats2bfloat162_rn(kv[e] * ik, kv[e + 1] * ik);
+    }
+    if (lane == 0) {
+      const float b = beta_scalar ? beta[0] : beta[id];
+      rq[id] = iq;
+      rk[id] = ik;
+      alpha[id] = normalize ? -expm1f(-b) : efla_coeff(b, sk);
+    }
+  }
+}
+
+// dq = iq (dqn - qn (qn.dqn)),  same for k (normalize); d(beta) = d(alpha) * exp(-beta*lam);
+// without normalisation dk += d(alpha) * dc/dlam * 2k.
+template <int D>
+__global__ void __launch_bounds__(256)
+efla_prep_bwd_kernel(const bf16* __restrict__ dqn, const bf16* __restrict__ dkn,
+                     const bf16* __restrict__ qn, const bf16* __restrict__ kn,
+                     const float* __restrict__ rq, const float* __restrict__ rk,
+                     const float* __restrict__ beta, int beta_scalar,
+                     const float* __restrict__ dalpha, bf16* __restrict__ dq,
+                     bf16* __restrict__ dk, float* __restrict__ dbeta, long long rows, int H,
+                     long long dqs, long long dks, int normalize) {
+  constexpr int E = D / 32;
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long id = wid; id < rows * H; id += nw) {
+    const long long tok = id / H;
+    const int h = static_cast<int>(id - tok * H);
+    float qv[E], kv[E], gq[E], gk[E];
+    float dq_dot = 0.f, dk_dot = 0.f, sk = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      const long long o = id * D + lane * E + e;
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(qn + o));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(kn + o));
+      const float2 ga = __bfloat1622float2(*reinterpret_cast<const bf162*>(dqn + o));
+      const float2 gb = __bfloat1622float2(*reinterpret_cast<const bf162*>(dkn + o));
+      qv[e] = a.x; qv[e + 1] = a.y; kv[e] = b.x; kv[e + 1] = b.y;
+      gq[e] = ga.x; gq[e + 1] = ga.y; gk[e] = gb.x; gk[e + 1] = gb.y;
+      dq_dot += a.x * ga.x + a.y * ga.y;
+      dk_dot += b.x * gb.x + b.y * gb.y;
+      sk += b.x * b.x + b.y * b.y;
+    }
+    dq_dot = warp_reduce_sum(dq_dot);
+    dk_dot = warp_reduce_sum(dk_dot);
+    sk = warp_reduce_sum(sk);
+    const float b = beta_scalar ? beta[0] : beta[id];
+    const float da = dalpha[id];
+    float kcoef = 0.f, db;
+    if (normalize) {
+      db = da * __expf(-b);
+    } else {
+      const float lam = sk;
+      const float ex = __expf(-b * lam);
+      db = da * ex;
+      float dcdl;
+      if (lam <= 1e-6f) dcdl = -0.5f * b * b + b * b * b * lam * (1.f / 3.f);
+      else dcdl = (b * lam * ex + expm1f(-b * lam)) / (lam * lam);
+      kcoef = 2.f * da * dcdl;
+    }
+    const float iq = rq[id], ik = rk[id];
+#pragma unroll
+    for (int e = 0; e < E; e += 2) {
+      float o0, o1, p0, p1;
+      if (normalize) {
+        o0 = iq * (gq[e] - qv[e] * dq_dot);
+        o1 = iq * (gq[e + 1] - qv[e + 1] * dq_dot);
+        p0 = ik * (gk[e] - kv[e] * dk_dot);
+        p1 = ik * (gk[e + 1] - kv[e + 1] * dk_dot);
+      } else {
+        o0 = gq[e]; o1 = gq[e + 1];
+        p0 = gk[e] + kcoef * kv[e];
+        p1 = gk[e + 1] + kcoef * kv[e + 1];
+      }
+      *reinterpret_cast<bf162*>(dq + tok * dqs + h * D + lane * E + e) =
+          __floats2bfloat162_rn(o0, o1);
+      *reinterpret_cast<bf162*>(dk + tok * dks + h * D + lane * E + e) =
+          __floats2bfloat162_rn(p0, p1);
+    }
+    if (lane == 0) dbeta[id] = db;
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -667,7 +799,8 @@ static int efla_bwd_impl(const bf16* q, const bf16* k, const bf16* v, const floa
                          const bf16* w, const bf16* up, const bf16* states, const bf16* dO,
                          const float* ds_final, bf16* dloc, bf16* dup, bf16* dstates, bf16* dq,
                          bf16* dk, bf16* dv, float* dalpha, float* ds0, int B, int T, int H,
-                         long long qs, long long ks, long long vs, cudaStream_t st) {
+                         long long qs, long long ks, long long vs, long long dqs, long long dks,
+                         long long dvs, cudaStream_t st) {
   static bool cfg = false;
   if (!cfg) {
     cudaError_t e;
@@ -679,11 +812,11 @@ static int efla_bwd_impl(const bf16* q, const bf16* k, const bf16* v, const floa
   const int n = T / CH;
   dim3 gpar(n, B * H), gser(D / BV, B * H);
   efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(q, k, up, states, dO, dq, dloc,
-                                                                    T, H, qs, ks);
+                                                                    T, H, qs, ks, dqs);
   efla_state_bwd_kernel<D><<<gser, 128, smem_state_bwd<D>(), st>>>(q, k, w, dO, dloc, ds_final, dup,
                                                                     dstates, ds0, T, H, qs, ks);
   efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
-      q, k, v, alpha, up, states, dO, dup, dstates, dk, dv, dalpha, T, H, qs, ks, vs);
+      q, k, v, alpha, up, states, dO, dup, dstates, dk, dv, dalpha, T, H, qs, ks, vs, dks, dvs);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -721,9 +854,11 @@ extern "C" int ceo_efla_bwd(const void* q, const void* k, const void* v, const f
                             const float* ds_final, void* dloc, void* dup, void* dstates, void* dq,
                             void* dk, void* dv, float* dalpha, float* ds0, int B, int T, int H,
                             int D, long long q_stride, long long k_stride, long long v_stride,
+                            long long dq_stride, long long dk_stride, long long dv_stride,
                             int* status, cudaStream_t stream) {
   (void)status;
   if (!efla_args_ok(B, T, H, D, q_stride, k_stride, v_stride)) return -5;
+  if ((dq_stride | dk_stride | dv_stride) & 1) return -2;
 #define CEO_EFLA_BWD(DD)                                                                         \
   return efla_bwd_impl<DD>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),             \
                            static_cast<const bf16*>(v), alpha, static_cast<const bf16*>(w),      \
@@ -731,8 +866,48 @@ extern "C" int ceo_efla_bwd(const void* q, const void* k, const void* v, const f
                            static_cast<const bf16*>(dO), ds_final, static_cast<bf16*>(dloc),     \
                            static_cast<bf16*>(dup), static_cast<bf16*>(dstates),                 \
                            static_cast<bf16*>(dq), static_cast<bf16*>(dk), static_cast<bf16*>(dv), \
-                           dalpha, ds0, B, T, H, q_stride, k_stride, v_stride, stream)
+                           dalpha, ds0, B, T, H, q_stride, k_stride, v_stride, dq_stride,   \
+                           dk_stride, dv_stride, stream)
   if (D == 64) CEO_EFLA_BWD(64);
   CEO_EFLA_BWD(128);
 #undef CEO_EFLA_BWD
+}
+
+extern "C" int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta, int beta_scalar,
+                                 void* qn, void* kn, float* rq, float* rk, float* alpha,
+                                 long long rows, int H, int D, long long q_stride,
+                                 long long k_stride, int normalize, cudaStream_t stream) {
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || (q_stride & 1) || (k_stride & 1)) return -5;
+  const int grid = grid_for(rows * H, 8, 148 * 16);
+  if (D == 64)
+    efla_prep_fwd_kernel<64><<<grid, 256, 0, stream>>>(
+        static_cast<const bf16*>(q), static_cast<const bf16*>(k), beta, beta_scalar,
+        static_cast<bf16*>(qn), static_cast<bf16*>(kn), rq, rk, alpha, rows, H, q_stride, k_stride,
+        normalize);
+  else
+    efla_prep_fwd_kernel<128><<<grid, 256, 0, stream>>>(
+        static_cast<const bf16*>(q), static_cast<const bf16*>(k), beta, beta_scalar,
+        static_cast<bf16*>(qn), static_cast<bf16*>(kn), rq, rk, alpha, rows, H, q_stride, k_stride,
+        normalize);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* qn, const void* kn,
+                                 const float* rq, const float* rk, const float* beta,
+                                 int beta_scalar, const float* dalpha, void* dq, void* dk,
+                                 float* dbeta, long long rows, int H, int D, long long dq_stride,
+                                 long long dk_stride, int normalize, cudaStream_t stream) {
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || (dq_stride & 1) || (dk_stride & 1)) return -5;
+  const int grid = grid_for(rows * H, 8, 148 * 16);
+  if (D == 64)
+    efla_prep_bwd_kernel<64><<<grid, 256, 0, stream>>>(
+        static_cast<const bf16*>(dqn), static_cast<const bf16*>(dkn), static_cast<const bf16*>(qn),
+        static_cast<const bf16*>(kn), rq, rk, beta, beta_scalar, dalpha, static_cast<bf16*>(dq),
+        static_cast<bf16*>(dk), dbeta, rows, H, dq_stride, dk_stride, normalize);
+  else
+    efla_prep_bwd_kernel<128><<<grid, 256, 0, stream>>>(
+        static_cast<const bf16*>(dqn), static_cast<const bf16*>(dkn), static_cast<const bf16*>(qn),
+        static_cast<const bf16*>(kn), rq, rk, beta, beta_scalar, dalpha, static_cast<bf16*>(dq),
+        static_cast<bf16*>(dk), dbeta, rows, H, dq_stride, dk_stride, normalize);
+  return static_cast<int>(cudaGetLastError());
 }

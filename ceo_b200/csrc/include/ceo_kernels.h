@@ -50,7 +50,18 @@ int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha
                  const void* up, const void* states, const void* dO, const float* ds_final,
                  void* dloc, void* dup, void* dstates, void* dq, void* dk, void* dv, float* dalpha,
                  float* ds0, int B, int T, int H, int D, long long q_stride, long long k_stride,
-                 long long v_stride, int* status, cudaStream_t stream);
+                 long long v_stride, long long dq_stride, long long dk_stride,
+                 long long dv_stride, int* status, cudaStream_t stream);
+/* q/k L2 normalisation (optional) + alpha = c(beta, |k|^2); one launch each way.
+ * beta: fp32 (rows*H) or one scalar (beta_scalar = 1).  qn, kn: bf16 (rows, H, D) dense. */
+int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta, int beta_scalar, void* qn,
+                      void* kn, float* rq, float* rk, float* alpha, long long rows, int H, int D,
+                      long long q_stride, long long k_stride, int normalize, cudaStream_t stream);
+int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* qn, const void* kn,
+                      const float* rq, const float* rk, const float* beta, int beta_scalar,
+                      const float* dalpha, void* dq, void* dk, float* dbeta, long long rows, int H,
+                      int D, long long dq_stride, long long dk_stride, int normalize,
+                      cudaStream_t stream);
 
 /* ---- normalisation ---------------------------------------------------------- */
 int ceo_norm_bwd_blocks(int rows); /* rows of the partial scratch the bwd kernels need */
@@ -76,6 +87,14 @@ int ceo_act_fwd(const void* x, void* y, long long n, int mode, cudaStream_t stre
 int ceo_act_bwd(const void* dy, const void* x, void* dx, long long n, int mode,
                 cudaStream_t stream);
 int ceo_softmax_fwd(const float* x, float* y, int rows, int n, cudaStream_t stream);
+
+/* ---- causal depthwise short convolution: x,y (B,T,D) bf16, weight (D,Wn) bf16 ------- */
+int ceo_shortconv_fwd(const void* x, const void* weight, void* y, int B, int T, int D, int Wn,
+                      cudaStream_t stream);
+int ceo_shortconv_bwd_input(const void* dy, const void* weight, void* dx, int B, int T, int D,
+                            int Wn, cudaStream_t stream);
+int ceo_shortconv_bwd_weight(const void* dy, const void* x, float* dw, int B, int T, int D, int Wn,
+                             int accumulate, cudaStream_t stream);
 
 /* ---- loss ------------------------------------------------------------------- */
 int ceo_cross_entropy(const void* logits, int logits_f32, const long long* targets, float* loss,

@@ -1,0 +1,307 @@
+"""EFLA decoder language model.
+
+Block (pre-norm, residual), following the reference's TransformerBlock
+(src/model/model.zig:152-204) with the generalisations its configs name:
+
+    h += W_o . EFLA(qkv(norm1 h))            [+ PRISM refinement when enabled]
+    h += W_down . act(W_up norm2 h)          (SwiGLU when activation = swiglu)
+
+The residual adds ride in the epilogue of the out-proj / down-proj GEMMs; q/k/v (and the
+gate/up pair) come from one fused projection each.  Parameter names on disk follow the
+reference (model.zig:494-521: ``embed_tokens.weight``, ``blocks.{i}.ln1.weight``,
+``blocks.{i}.efla.{w_k,w_v,w_o,beta_param}``, ``blocks.{i}.mlp_up.weight`` ...) with the
+additions ``efla.w_q``, ``efla.w_beta`` and ``mlp_gate.weight``; ``state_dict_reference()``
+/ ``load_reference_state()`` translate between the fused (out, in) tensors kept here and
+the per-matrix (in, out) tensors of the checkpoint format (src/nn/layers.zig:509,529).
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+
+import torch
+import torch.nn as nn
+
+from ..ops import efla as efla_ops
+from ..ops import nn as K
+from ..ops.matmul import linear
+from ..utils.config import ModelConfig
+from .prism import PrismLayer
+
+
+def _param(shape, std, device, dtype, gen):
+    t = torch.empty(shape, device=device, dtype=torch.float32)
+    if std == 0.0:
+        t.zero_()
+    else:
+        t.normal_(0.0, std, generator=gen)
+    return nn.Parameter(t.to(dtype))
+
+
+class Norm(nn.Module):
+    def __init__(self, dim, kind, device, dtype):
+        super().__init__()
+        self.kind = kind
+        self.eps = 1e-6 if kind == "rmsnorm" else 1e-5
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(dim, device=device, dtype=dtype)) \
+            if kind == "layernorm" else None
+
+    def forward(self, x):
+        if self.kind == "rmsnorm":
+            return K.rmsnorm(x, self.weight, self.eps)[0]
+        return K.layernorm(x, self.weight, self.bias, self.eps)
+
+
+class EflaLayer(nn.Module):
+    """Projections + EFLA attention (reference: src/model/efla.zig:110-249)."""
+
+    def __init__(self, cfg: ModelConfig, device, dtype, gen, std):
+        super().__init__()
+        e = cfg.efla
+        self.H, self.d, self.D = cfg.num_heads, cfg.head_dim, cfg.hidden_dim
+        self.P = 3 if e.use_query else 2
+        self.normalize = e.normalize_qk
+        self.per_token_beta = e.per_token_beta
+        hd = self.H * self.d
+        self.w_qkv = _param((self.P * hd, self.D), std, device, dtype, gen)
+        self.w_o = _param((self.D, hd), std, device, dtype, gen)
+        if self.per_token_beta:
+            self.w_beta = _param((self.H, self.D), std, device, dtype, gen)
+            self.beta_param = None
+        else:
+            self.w_beta = None
+            self.beta_param = nn.Parameter(torch.full((1,), float(e.initial_beta), device=device,
+                                                      dtype=torch.float32),
+                                           requires_grad=e.learned_beta)
+
+    def forward(self, x_norm, residual, state=None):
+        B, T, _ = x_norm.shape
+        qkv = linear(x_norm, self.w_qkv).view(B, T, self.P, self.H, self.d)
+        if self.per_token_beta:
+            beta = torch.sigmoid(linear(x_norm, self.w_beta).float())
+        else:
+            beta = self.beta_param
+        pad = (-T) % efla_ops.CHUNK
+        if pad and qkv.is_cuda:
+            raise ValueError(f"sequence length {T} must be a multiple of {efla_ops.CHUNK} on GPU")
+        o, s_final = efla_ops.efla_qkv(qkv, beta, self.normalize, state)
+        return o.reshape(B, T, self.H * self.d), s_final
+
+    def decode_step(self, x_norm, state):
+        """One token (B, D) with carried state (B,H,d,d) fp32; returns the (B, H*d) output."""
+        B = x_norm.shape[0]
+        qkv = linear(x_norm, self.w_qkv).view(B, self.P, self.H, self.d)
+        q = qkv[:, 0]
+        k = qkv[:, 1] if self.P == 3 else qkv[:, 0]
+        v = qkv[:, self.P - 1]
+        if self.per_token_beta:
+            beta = torch.sigmoid(linear(x_norm, self.w_beta).float())
+        else:
+            beta = self.beta_param.expand(B, self.H)
+        if self.normalize:
+            q, k = efla_ops.l2norm(q), efla_ops.l2norm(k)
+            alpha = -torch.expm1(-beta)
+        else:
+            alpha = efla_ops.ref.efla_coefficient(beta, k.float().pow(2).sum(-1))
+        o = efla_ops.delta_rule_decode_step(q, k, v, alpha, state)
+        return o.reshape(B, self.H * self.d)
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, dtype, gen, std):
+        super().__init__()
+        self.act = cfg.activation
+        D, F = cfg.hidden_dim, cfg.intermediate_dim
+        self.F = F
+        n_up = 2 * F if self.act == "swiglu" else F
+        self.w_up = _param((n_up, D), std, device, dtype, gen)  # [gate | up] rows when swiglu
+        self.w_down = _param((D, F), std, device, dtype, gen)
+
+    def forward(self, x_norm, residual):
+        u = linear(x_norm, self.w_up)
+        a = K.swiglu(u) if self.act == "swiglu" else K.activation(u, self.act)
+        return linear(a, self.w_down, residual)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, dtype, gen, std):
+        super().__init__()
+        self.ln1 = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
+        self.efla = EflaLayer(cfg, device, dtype, gen, std)
+        self.prism = PrismLayer(cfg, device, dtype, gen, std) if cfg.prism.enabled else None
+        self.ln2 = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
+        self.mlp = MLP(cfg, device, dtype, gen, std)
+
+    def forward(self, h, state=None):
+        n1 = self.ln1(h)
+        o, s_final = self.efla(n1, h, state)
+        if self.prism is not None:
+            a = linear(o, self.efla.w_o)
+            h = h + self.prism(n1, a)
+        else:
+            h = linear(o, self.efla.w_o, h)
+        h = self.mlp(self.ln2(h), h)
+        return h, s_final
+
+    def decode_step(self, h, state):
+        n1 = self.ln1(h)
+        o = self.efla.decode_step(n1, state)
+        h = linear(o, self.efla.w_o, h)
+        return self.mlp(self.ln2(h), h)
+
+
+class EflaLM(nn.Module):
+    """embed -> blocks -> final norm -> LM head (reference: src/model/model.zig:271-441)."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0,
+                 init_std: float = 0.02):
+        super().__init__()
+        self.cfg = cfg
+        if dtype is None:
+            dtype = {"fp32": torch.float32, "fp16": torch.float16}.get(cfg.dtype, torch.bfloat16)
+        device = torch.device(device)
+        if device.type == "cuda" and dtype != torch.bfloat16:
+            raise ValueError("the CUDA kernels are bf16; use dtype bf16 on GPU")
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.embed_tokens = _param((cfg.vocab_size, cfg.hidden_dim), init_std, device, dtype, gen)
+        self.blocks = nn.ModuleList(Block(cfg, device, dtype, gen, init_std)
+                                    for _ in range(cfg.num_layers))
+        self.final_norm = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
+        self.lm_head = None if cfg.tie_embeddings else \
+            _param((cfg.vocab_size, cfg.hidden_dim), init_std, device, dtype, gen)
+
+    # ------------------------------------------------------------------ forward paths
+    def head_weight(self):
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    def hidden(self, tokens, states=None):
+        h = K.embedding(tokens, self.embed_tokens)
+        finals = []
+        for i, blk in enumerate(self.blocks):
+            h, s = blk(h, None if states is None else states[i])
+            finals.append(s)
+        return self.final_norm(h), finals
+
+    def forward(self, tokens, targets=None, label_smoothing: float = 0.0, states=None,
+                return_states: bool = False):
+        """With ``targets``: mean next-token cross-entropy (the LM head and the loss are fused,
+        logits are never materialised).  Without: logits (B,T,V) in fp32."""
+        hn, finals = self.hidden(tokens, states)
+        if targets is not None:
+            out = K.linear_cross_entropy(hn, self.head_weight(), targets, label_smoothing)
+        else:
+            from ..ops.matmul import gemm
+            w = self.head_weight()
+            if hn.is_cuda:
+                out = gemm(hn.reshape(-1, hn.shape[-1]), w, out_dtype=torch.float32)
+            else:
+                out = hn.reshape(-1, hn.shape[-1]).float() @ w.float().t()
+            out = out.view(*tokens.shape, -1)
+        return (out, finals) if return_states else out
+
+    def new_states(self, batch, device=None):
+        device = device or self.embed_tokens.device
+        c = self.cfg
+        return [torch.zeros(batch, c.num_heads, c.head_dim, c.head_dim, dtype=torch.float32,
+                            device=device) for _ in self.blocks]
+
+    @torch.no_grad()
+    def decode_step(self, token, states):
+        """token: (B,) ids; states: list of (B,H,d,d) fp32 updated in place -> logits (B,V)."""
+        h = K.embedding(token, self.embed_tokens)
+        for blk, st in zip(self.blocks, states):
+            h = blk.decode_step(h, st)
+        hn = self.final_norm(h)
+        return hn.float() @ self.head_weight().float().t()
+
+    # ------------------------------------------------------------ checkpoint name mapping
+    def count_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def state_dict_reference(self) -> "OrderedDict[str, torch.Tensor]":
+        """Tensors under the reference's names and (in, out) orientation."""
+        out = OrderedDict()
+        hd = self.cfg.num_heads * self.cfg.head_dim
+        out["embed_tokens.weight"] = self.embed_tokens.detach()
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            out[p + "ln1.weight"] = b.ln1.weight.detach()
+            if b.ln1.bias is not None:
+                out[p + "ln1.bias"] = b.ln1.bias.detach()
+            parts = b.efla.w_qkv.detach().split(hd, dim=0)
+            names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
+            for nme, w in zip(names, parts):
+                out[p + "efla." + nme] = w.t().contiguous()
+            out[p + "efla.w_o"] = b.efla.w_o.detach().t().contiguous()
+            if b.efla.w_beta is not None:
+                out[p + "efla.w_beta"] = b.efla.w_beta.detach().t().contiguous()
+            else:
+                out[p + "efla.beta_param"] = b.efla.beta_param.detach()
+            if b.prism is not None:
+                for nme, t in b.prism.reference_tensors().items():
+                    out[p + "prism." + nme] = t
+            out[p + "ln2.weight"] = b.ln2.weight.detach()
+            if b.ln2.bias is not None:
+                out[p + "ln2.bias"] = b.ln2.bias.detach()
+            if b.mlp.act == "swiglu":
+                g, u = b.mlp.w_up.detach().split(b.mlp.F, dim=0)
+                out[p + "mlp_gate.weight"] = g.t().contiguous()
+                out[p + "mlp_up.weight"] = u.t().contiguous()
+            else:
+                out[p + "mlp_up.weight"] = b.mlp.w_up.detach().t().contiguous()
+            out[p + "mlp_down.weight"] = b.mlp.w_down.detach().t().contiguous()
+        out["final_norm.weight"] = self.final_norm.weight.detach()
+        if self.final_norm.bias is not None:
+            out["final_norm.bias"] = self.final_norm.bias.detach()
+        if self.lm_head is not None:
+            out["lm_head.weight"] = self.lm_head.detach().t().contiguous()
+        return out
+
+    @torch.no_grad()
+    def load_reference_state(self, tensors: dict) -> None:
+        """Inverse of ``state_dict_reference`` (raises KeyError on a missing tensor)."""
+        def put(dst, src):
+            dst.copy_(src.to(dst.device, dst.dtype))
+        hd = self.cfg.num_heads * self.cfg.head_dim
+        put(self.embed_tokens, tensors["embed_tokens.weight"])
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            put(b.ln1.weight, tensors[p + "ln1.weight"])
+            if b.ln1.bias is not None:
+                put(b.ln1.bias, tensors[p + "ln1.bias"])
+            names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
+            for j, nme in enumerate(names):
+                put(b.efla.w_qkv[j * hd:(j + 1) * hd], tensors[p + "efla." + nme].t())
+            put(b.efla.w_o, tensors[p + "efla.w_o"].t())
+            if b.efla.w_beta is not None:
+                put(b.efla.w_beta, tensors[p + "efla.w_beta"].t())
+            else:
+                put(b.efla.beta_param, tensors[p + "efla.beta_param"].reshape(1))
+            if b.prism is not None:
+                b.prism.load_reference_tensors({k[len(p + "prism."):]: v for k, v in tensors.items()
+                                                if k.startswith(p + "prism.")})
+            put(b.ln2.weight, tensors[p + "ln2.weight"])
+            if b.ln2.bias is not None:
+                put(b.ln2.bias, tensors[p + "ln2.bias"])
+            if b.mlp.act == "swiglu":
+                put(b.mlp.w_up[:b.mlp.F], tensors[p + "mlp_gate.weight"].t())
+                put(b.mlp.w_up[b.mlp.F:], tensors[p + "mlp_up.weight"].t())
+            else:
+                put(b.mlp.w_up, tensors[p + "mlp_up.weight"].t())
+            put(b.mlp.w_down, tensors[p + "mlp_down.weight"].t())
+        put(self.final_norm.weight, tensors["final_norm.weight"])
+        if self.final_norm.bias is not None:
+            put(self.final_norm.bias, tensors["final_norm.bias"])
+        if self.lm_head is not None:
+            put(self.lm_head, tensors["lm_head.weight"].t())
+
+    def flops_per_token(self, seq_len: int | None = None) -> float:
+        """Model FLOPs per token for one forward+backward (6 x matmul parameters + EFLA)."""
+        c = self.cfg
+        mat = sum(p.numel() for n, p in self.named_parameters() if p.dim() == 2
+                  and "embed_tokens" not in n)
+        if self.lm_head is None:
+            mat += self.embed_tokens.numel()
+        efla = c.num_layers * c.num_heads * (4 * c.head_dim * c.head_dim + 8 * 64 * c.head_dim)
+        return 6.0 * mat + 3.0 * efla

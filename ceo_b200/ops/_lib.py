@@ -26,6 +26,29 @@ _lib = None
 _status = {}
 _scratch = {}
 
+# kernels launched per entry point (everything not listed launches exactly one)
+_LAUNCHES = {"ceo_efla_fwd": 3, "ceo_efla_bwd": 3, "ceo_rmsnorm_bwd": 2, "ceo_layernorm_bwd": 4,
+             "ceo_sumsq": 2, "ceo_reduce": 2, "ceo_muon_momentum": 2, "ceo_norm_bwd_blocks": 0,
+             "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0}
+launch_count = 0
+
+
+class _Counted:
+    """Wraps a ctypes entry point and counts the kernels it launches."""
+    __slots__ = ("fn", "n")
+
+    def __init__(self, fn, n):
+        self.fn, self.n = fn, n
+
+    def __call__(self, *a):
+        global launch_count
+        launch_count += self.n
+        return self.fn(*a)
+
+
+class _Lib:
+    pass
+
 _CTYPE = {
     "int": ctypes.c_int,
     "float": ctypes.c_float,
@@ -59,7 +82,7 @@ def available() -> bool:
     return LIB_PATH.exists()
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     """The loaded kernel library (raises if it has not been built)."""
     global _lib
     if _lib is None:
@@ -67,13 +90,17 @@ def lib() -> ctypes.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python -m ceo_b200.build` "
                 "(CUDA tensors are never routed to a PyTorch fallback)")
-        _lib = ctypes.CDLL(str(LIB_PATH))
+        cdll = ctypes.CDLL(str(LIB_PATH))
+        wrapped = _Lib()
+        wrapped.cdll = cdll
         for name, argtypes in _parse_header(HEADER_PATH.read_text()).items():
-            fn = getattr(_lib, name, None)
+            fn = getattr(cdll, name, None)
             if fn is None:
                 raise RuntimeError(f"{name} is declared in ceo_kernels.h but not exported")
             fn.argtypes = argtypes
             fn.restype = ctypes.c_int
+            setattr(wrapped, name, _Counted(fn, _LAUNCHES.get(name, 1)))
+        _lib = wrapped
     return _lib
 
 

@@ -77,9 +77,113 @@ class _DeltaRuleFn(torch.autograd.Function):
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                   dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, _tok_stride(q),
-                                  _tok_stride(k), _tok_stride(v), st, _lib.stream()),
+                                  _tok_stride(k), _tok_stride(v), H * d, H * d, H * d, st,
+                                  _lib.stream()),
                    "ceo_efla_bwd")
         return dq, dk, dv, dalpha, (ds0 if ctx.has_s0 else None)
+
+
+class _EflaQKVFn(torch.autograd.Function):
+    """EFLA attention straight off a fused projection output ``qkv`` of shape
+    (B, T, P, H, d) with P = 3 (q, k, v) or P = 2 (k, v; q = k as in the reference).
+    One kernel normalises q/k and computes alpha; the chunked kernels follow; backward
+    writes dq, dk, dv into one (B, T, P, H, d) buffer so the projection's gradient GEMMs
+    read it in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, beta, normalize, s0):
+        B, T, P, H, d = qkv.shape
+        assert qkv.is_contiguous() and P in (2, 3) and T % CHUNK == 0
+        dev = qkv.device
+        n = T // CHUNK
+        ts = P * H * d
+        q_raw = qkv[:, :, 0] if P == 3 else qkv[:, :, 0]
+        k_raw = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
+        v = qkv[:, :, P - 1]
+        beta = beta.float().contiguous()
+        scalar = beta.numel() == 1
+        rows = B * T
+        L = _lib.lib()
+        qn = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        kn = torch.empty_like(qn) if P == 3 else qn
+        rq = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        rk = torch.empty_like(rq)
+        alpha = torch.empty_like(rq)
+        _lib.check(L.ceo_efla_prep_fwd(q_raw.data_ptr(), k_raw.data_ptr(), beta.data_ptr(),
+                                       int(scalar), qn.data_ptr(), kn.data_ptr(), rq.data_ptr(),
+                                       rk.data_ptr(), alpha.data_ptr(), rows, H, d, ts, ts,
+                                       int(normalize), _lib.stream()), "ceo_efla_prep_fwd")
+        w = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        up = torch.empty_like(w)
+        o = torch.empty_like(w)
+        states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        s_final = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        st = _lib.status_word(dev).data_ptr()
+        _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), alpha.data_ptr(),
+                                  _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
+                                  o.data_ptr(), s_final.data_ptr(), B, T, H, d, H * d, H * d, ts,
+                                  st, _lib.stream()), "ceo_efla_fwd")
+        ctx.save_for_backward(qkv, beta, qn, kn, rq, rk, alpha, w, up, states)
+        ctx.cfg = (normalize, scalar, s0 is not None)
+        return o, s_final
+
+    @staticmethod
+    def backward(ctx, do, ds_final):
+        qkv, beta, qn, kn, rq, rk, alpha, w, up, states = ctx.saved_tensors
+        normalize, scalar, has_s0 = ctx.cfg
+        B, T, P, H, d = qkv.shape
+        n = T // CHUNK
+        dev = qkv.device
+        ts = P * H * d
+        do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dqn = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        dkn = torch.empty_like(dqn)
+        dalpha = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        dloc = torch.empty_like(dqn)
+        dup = torch.empty_like(dqn)
+        dstates = torch.empty_like(states)
+        ds0 = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        if ds_final is not None:
+            ds_final = ds_final.contiguous().float()
+        v = qkv[:, :, P - 1]
+        dv = dqkv[:, :, P - 1]
+        L = _lib.lib()
+        st = _lib.status_word(dev).data_ptr()
+        _lib.check(L.ceo_efla_bwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), alpha.data_ptr(),
+                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), do.data_ptr(),
+                                  _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
+                                  dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(),
+                                  dv.data_ptr(), dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d,
+                                  H * d, H * d, ts, H * d, H * d, ts, st, _lib.stream()),
+                   "ceo_efla_bwd")
+        dbeta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        if P == 3:
+            dq_out, dk_out = dqkv[:, :, 0], dqkv[:, :, 1]
+        else:  # q = k: both gradients land on the one projection
+            dkn.add_(dqn)
+            dq_out = dloc  # scratch: the q-side output of the kernel is unused
+            dk_out = dqkv[:, :, 0]
+        _lib.check(L.ceo_efla_prep_bwd(dqn.data_ptr(), dkn.data_ptr(), qn.data_ptr(),
+                                       kn.data_ptr(), rq.data_ptr(), rk.data_ptr(),
+                                       beta.data_ptr(), int(scalar), dalpha.data_ptr(),
+                                       dq_out.data_ptr(), dk_out.data_ptr(), dbeta.data_ptr(),
+                                       B * T, H, d, (ts if P == 3 else H * d), ts,
+                                       int(normalize), _lib.stream()), "ceo_efla_prep_bwd")
+        if scalar:
+            dbeta = dbeta.sum().reshape(beta.shape)
+        return dqkv, dbeta, None, (ds0 if has_s0 else None)
+
+
+def efla_qkv(qkv, beta, normalize: bool = True, s0=None):
+    """EFLA attention on a fused projection output.  qkv: (B,T,P,H,d), P = 3 (q,k,v) or 2
+    (k,v with q = k); beta: (B,T,H) or a one-element tensor.  Returns (o (B,T,H,d), S_T)."""
+    if not qkv.is_cuda:
+        P = qkv.shape[2]
+        q = qkv[:, :, 0]
+        k = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
+        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0)
+    return _EflaQKVFn.apply(qkv, beta, normalize, s0)
 
 
 def delta_rule(q, k, v, alpha, s0=None, impl: str = "auto"):

@@ -87,3 +87,37 @@ def test_efla_attention_reference_form():
     o, s = efla.efla_attention(k, k, v, torch.tensor(1.0, device=DEV), normalize_qk=False)
     o_ref, s_ref = ref.efla_reference_form(k, v, 1.0)
     assert _rel(o, o_ref) < 1.5e-2 and _rel(s, s_ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("P,normalize,scalar_beta", [(3, True, False), (2, False, True),
+                                                     (3, False, False), (2, True, False)])
+def test_efla_qkv_fused(P, normalize, scalar_beta):
+    B, T, H, d = 2, 128, 2, 128
+    g = torch.Generator(device=DEV).manual_seed(7)
+    qkv = (0.5 * torch.randn(B, T, P, H, d, device=DEV, generator=g)).to(torch.bfloat16)
+    if not normalize:
+        qkv[:, :, :P - 1] *= 0.15
+    beta0 = torch.tensor([0.8], device=DEV) if scalar_beta else \
+        torch.sigmoid(torch.randn(B, T, H, device=DEV, generator=g))
+    do = torch.randn(B, T, H, d, device=DEV, generator=g).to(torch.bfloat16)
+
+    a = qkv.clone().requires_grad_()
+    ba = beta0.clone().requires_grad_()
+    o, _ = efla.efla_qkv(a, ba, normalize)
+    (o.float() * do.float()).sum().backward()
+
+    b = qkv.float().requires_grad_()
+    bb = beta0.clone().requires_grad_()
+    q = b[:, :, 0]
+    k = b[:, :, 1] if P == 3 else b[:, :, 0]
+    if normalize:
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        alpha = -torch.expm1(-bb.expand(B, T, H))
+    else:
+        alpha = ref.efla_coefficient(bb.expand(B, T, H), k.pow(2).sum(-1))
+    o_r, _ = ref.delta_rule_chunked(q, k, b[:, :, P - 1], alpha)
+    (o_r * do.float()).sum().backward()
+    assert _rel(o, o_r) < 2e-2
+    assert _rel(a.grad, b.grad) < 4e-2, _rel(a.grad, b.grad)
+    assert _rel(ba.grad, bb.grad) < 4e-2, _rel(ba.grad, bb.grad)
