@@ -132,6 +132,77 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   }
 }
 
+// Warp-per-row variant for D = NV*256 <= 2048: no block barriers inside the row loop, the
+// row stays in registers as packed bf16, and 8 warps per CTA keep 8 rows of loads in flight.
+template <int NV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                        const bf16* __restrict__ w, const float* __restrict__ rstd,
+                        const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ partial, int rows) {
+  constexpr int D = NV * 256;
+  __shared__ float dws[D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) dws[i] = 0.f;
+  __syncthreads();
+  float dwacc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const size_t off = static_cast<size_t>(row) * D;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
+    uint4 xp[NV], gp[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xp[i] = xr[lane + 32 * i];
+      gp[i] = gr[lane + 32 * i];
+    }
+    const float rs = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float xv[8], gv[8], ww[8];
+      unpack8(xp[i], xv);
+      unpack8(gp[i], gv);
+      unpack8(wv[lane + 32 * i], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dwacc[i][j] += gv[j] * xv[j] * rs;
+        dot += gv[j] * ww[j] * xv[j];
+      }
+    }
+    dot = warp_reduce_sum(dot);
+    const float coef = dot * rs * rs * rs / D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float xv[8], gv[8], ww[8], o[8];
+      unpack8(xp[i], xv);
+      unpack8(gp[i], gv);
+      unpack8(wv[lane + 32 * i], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = gv[j] * ww[j] * rs - xv[j] * coef;
+      if (dres) {
+        float t[8];
+        unpack8(reinterpret_cast<const uint4*>(dres + off)[lane + 32 * i], t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += t[j];
+      }
+      reinterpret_cast<uint4*>(dx + off)[lane + 32 * i] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&dws[(lane + 32 * i) * 8 + j], dwacc[i][j]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS)
+    partial[static_cast<size_t>(blockIdx.x) * D + i] = dws[i];
+}
+
 // out[c] (+)= sum_b partial[b][c]
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                        int nblk, int D, int accumulate) {
@@ -290,10 +361,30 @@ extern "C" int ceo_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                const void* dres, void* dx, float* dw, int dw_accumulate,
                                float* partial_scratch, int rows, int D, cudaStream_t stream) {
   if (!norm_shape_ok(rows, D)) return -5;
-  const int nblk = ceo_norm_bwd_blocks(rows);
-  rmsnorm_bwd_kernel<<<nblk, NORM_THREADS, 0, stream>>>(
-      static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
-      static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial_scratch, rows, D);
+  int nblk = ceo_norm_bwd_blocks(rows);
+  const bf16* dyp = static_cast<const bf16*>(dy);
+  const bf16* xp = static_cast<const bf16*>(x);
+  const bf16* wp = static_cast<const bf16*>(w);
+  const bf16* rp = static_cast<const bf16*>(dres);
+  bf16* dxp = static_cast<bf16*>(dx);
+  if ((D & 255) == 0 && D <= 2048) {
+    int g = (rows + 7) / 8;
+    if (g > 296) g = 296;
+    nblk = g;
+#define CEO_RMS_BWD(NV)                                                                    \
+  case NV:                                                                                 \
+    rmsnorm_bwd_warp_kernel<NV><<<g, NORM_THREADS, 0, stream>>>(dyp, xp, wp, rstd, rp, dxp, \
+                                                                partial_scratch, rows);    \
+    break;
+    switch (D / 256) {
+      CEO_RMS_BWD(1) CEO_RMS_BWD(2) CEO_RMS_BWD(3) CEO_RMS_BWD(4)
+      CEO_RMS_BWD(5) CEO_RMS_BWD(6) CEO_RMS_BWD(7) CEO_RMS_BWD(8)
+    }
+#undef CEO_RMS_BWD
+  } else {
+    rmsnorm_bwd_kernel<<<nblk, NORM_THREADS, 0, stream>>>(dyp, xp, wp, rstd, rp, dxp,
+                                                          partial_scratch, rows, D);
+  }
   reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial_scratch, dw, nblk, D,
                                                               dw_accumulate);
   return static_cast<int>(cudaGetLastError());
