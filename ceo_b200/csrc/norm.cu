@@ -418,3 +418,45 @@ extern "C" int ceo_layernorm_bwd(const void* dy, const void* x, const void* w, c
   return ceo_axpby_f32(dw, partial_scratch, D, accumulate ? 1.f : 0.f, 1.f, stream) |
          (db ? ceo_axpby_f32(db, partial_scratch + D, D, accumulate ? 1.f : 0.f, 1.f, stream) : 0);
 }
+
+// ------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate: the partial-sum scratch lives in this
+// file-scope device array instead of a caller buffer (see include/ceo_noalloc.h for who
+// needs this and for the rules: size limit, first-call set-up, shared contents, races).
+#include <stdio.h>
+
+#include "include/ceo_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_partial[CEO_NORM_BWD_MAX_BLOCKS *
+                                                         CEO_NOALLOC_MAX_D];
+
+// In host code `g_noalloc_partial` is only a handle for the runtime, not an address the GPU
+// can use, so the device address is looked up once per device and cached here.
+static float* g_noalloc_ptr[64] = {nullptr};
+
+extern "C" int ceo_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w,
+                                       const float* rstd, const void* dres, void* dx, float* dw,
+                                       int dw_accumulate, int rows, int D, cudaStream_t stream) {
+  if (D > CEO_NOALLOC_MAX_D) {
+    fprintf(stderr,
+            "ceo_rmsnorm_bwd_noalloc: D = %d exceeds the built-in scratch (max D = %d); use "
+            "ceo_rmsnorm_bwd with a caller-provided scratch buffer\n",
+            D, CEO_NOALLOC_MAX_D);
+    return CEO_ERR_NOALLOC_TOO_LARGE;
+  }
+  if (rows <= 0 || D <= 0 || (D & 7)) return -5;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -5;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partial);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = p;
+  }
+  // Every partial row that the reduction reads is fully written by the first kernel of this
+  // same call, so stale contents from an earlier call are never observed.
+  return ceo_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, dw_accumulate, g_noalloc_ptr[dev], rows,
+                         D, stream);
+}
