@@ -150,6 +150,31 @@ int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* sc
 int ceo_fp8_update_scale(float* history, int hist_len, int* cursor, float* amax, float* scale,
                          float fp8_max, float margin_pow2, cudaStream_t stream);
 
+/* ---- peer-memory collectives (NVLink), fused with their compute --------------------------
+ * Buffers are plain cudaMalloc allocations mapped into every rank through CUDA IPC; the
+ * `void* const*` arguments are host arrays of `world` device pointers indexed by rank (this
+ * rank's own entry is its local pointer).  flags: 4 slots x 8 unsigned per rank, zeroed once;
+ * `epoch` must grow by at least 2 between uses of the same slot set.  world <= 8. */
+int ceo_dev_malloc(void** out, long long bytes);
+int ceo_dev_free(void* p);
+int ceo_dev_memset(void* p, int value, long long bytes, cudaStream_t stream);
+int ceo_ipc_get_handle(void* p, void* handle64);
+int ceo_ipc_open(const void* handle64, void** out);
+int ceo_ipc_close(void* p);
+int ceo_symm_barrier(void* const* flags, int rank, int world, int slot, unsigned int epoch,
+                     int* status, cudaStream_t stream);
+int ceo_symm_allreduce(void* const* bufs, void* const* flags, float* out, int n, int rank,
+                       int world, unsigned int epoch, int* status, cudaStream_t stream);
+/* One cooperative launch per rank: reduce-scatter of the fp32 gradients (peer loads) ->
+ * global-norm clip -> AdamW on the rank's fp32 master slice [lo, lo+n) -> bf16 parameters
+ * stored into every rank's buffer -> this rank's gradient buffer zeroed. */
+int ceo_zero_step(void* const* grads, void* const* params, void* const* flags, void* const* slots,
+                  float* master, float* m, float* v, float* local_acc, float* norm_out,
+                  int* status, long long lo, long long n, long long total, long long decay_end,
+                  int rank, int world, unsigned int epoch, float lr, float beta1, float beta2,
+                  float eps, float weight_decay, int step, float gscale, float max_norm,
+                  cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,7 +32,9 @@ class Segment:
 
 class FlatParams:
     def __init__(self, model: torch.nn.Module, world: int = 1, rank: int = 0,
-                 grad_dtype: torch.dtype = torch.float32):
+                 grad_dtype: torch.dtype = torch.float32, alloc=None):
+        """``alloc(numel, dtype) -> (tensor, handle)`` places the parameter and gradient
+        buffers in peer-mapped memory (``FusedComm.alloc``); default: ordinary tensors."""
         self.world, self.rank = world, rank
         named = [(n, p) for n, p in model.named_parameters()]
         flat_named = [(n, p) for n, p in named if p.dtype in (torch.bfloat16, torch.float32)
@@ -58,8 +60,13 @@ class FlatParams:
         unit = ALIGN * world
         self.total = (off + unit - 1) // unit * unit
         self.shard = self.total // world
-        self.params = torch.zeros(self.total, dtype=self.param_dtype, device=dev)
-        self.grads = torch.zeros(self.total, dtype=grad_dtype, device=dev)
+        self.params_symm = self.grads_symm = None
+        if alloc is not None:
+            self.params, self.params_symm = alloc(self.total, self.param_dtype)
+            self.grads, self.grads_symm = alloc(self.total, grad_dtype)
+        else:
+            self.params = torch.zeros(self.total, dtype=self.param_dtype, device=dev)
+            self.grads = torch.zeros(self.total, dtype=grad_dtype, device=dev)
         self._by_name = {}
         for seg, i in zip(self.segments, order):
             n, p = flat_named[i]

@@ -280,6 +280,20 @@ class ShardedOptimizer:
         gradient norm as a device scalar (no host synchronisation)."""
         f = self.flat
         self.step_count += 1
+        if (self.kind == "adamw" and self._world() > 1 and getattr(self.comm, "fused", False)
+                and f.grads_symm is not None and f.param_dtype == torch.bfloat16
+                and f.grads.dtype == torch.float32):
+            # one kernel: reduce-scatter + clip + AdamW + all-gather + zero-grad over NVLink
+            side = self._side_grads()
+            norm = self.comm.zero_step(f, f.buffer("exp_avg"), f.buffer("exp_avg_sq"), lr=lr,
+                                       betas=self.betas, eps=self.eps, weight_decay=self.wd,
+                                       step=self.step_count, grad_scale=grad_scale,
+                                       max_norm=self.max_norm)
+            self._scale.fill_(1.0)
+            self._side_update(side, lr, grad_scale)
+            for _, p in f.side:
+                p.grad = None
+            return norm
         g = self._reduce_grads()
         side = self._side_grads()
         self._global_norm(g, side, grad_scale)

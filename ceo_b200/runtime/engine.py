@@ -28,7 +28,8 @@ class TrainEngine:
         if self.device.type == "cuda":
             dtype = torch.bfloat16
         self.model = EflaLM(cfg.model, self.device, dtype=dtype, seed=seed)
-        self.flat = FlatParams(self.model, self.world, self.rank)
+        self.flat = FlatParams(self.model, self.world, self.rank,
+                               alloc=getattr(comm, "alloc", None))
         self.optimizer = build_optimizer(self.flat, cfg.training, comm)
         t = cfg.training
         self.scheduler = LRScheduler(t.learning_rate, t.min_learning_rate, t.warmup_steps,

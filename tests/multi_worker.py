@@ -1,0 +1,77 @@
+"""Worker for the multi-GPU tests (launched with torchrun, one process per GPU)."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ceo_b200.data.synthetic import SyntheticTokens  # noqa: E402
+from ceo_b200.ops import _lib  # noqa: E402
+from ceo_b200.parallel.comm import Comm, init_distributed  # noqa: E402
+from ceo_b200.runtime.engine import TrainEngine  # noqa: E402
+from ceo_b200.utils.config import Config  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def small_cfg(world):
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "efla_340m.yaml"))
+    cfg.model.num_layers = 2
+    cfg.model.vocab_size = 2048
+    cfg.model.hidden_dim = 512
+    cfg.model.num_heads = 8
+    cfg.model.intermediate_dim = 1024
+    cfg.runtime.world_size = world
+    return cfg
+
+
+def run_engine(comm, cfg, rank, steps=3):
+    eng = TrainEngine(cfg, torch.device("cuda", torch.cuda.current_device()), comm, seed=0)
+    data = SyntheticTokens(cfg.model.vocab_size, "zipf", 1.1, 0, rank)
+    losses = []
+    for _ in range(steps):
+        tok, tgt = data.batch(2, 256)
+        loss, gn = eng.train_step([(tok.cuda(), tgt.cuda())], lr=1e-3)
+        losses.append((float(loss), float(gn)))
+    torch.cuda.synchronize()
+    return eng, losses
+
+
+def main():
+    what = sys.argv[1]
+    rank, world, local = init_distributed()
+    torch.cuda.set_device(local)
+    if what == "fused_vs_nccl":
+        from ceo_b200.parallel.fused import FusedComm
+        cfg = small_cfg(world)
+        e_ref, l_ref = run_engine(Comm(), cfg, rank)
+        fc = FusedComm()
+        x = torch.arange(5, dtype=torch.float32, device="cuda") + rank
+        got = fc.all_reduce_small(x)
+        want = sum(torch.arange(5, dtype=torch.float32) + r for r in range(world))
+        assert torch.allclose(got.cpu(), want), (got, want)
+        fc.device_barrier()
+        e_fus, l_fus = run_engine(fc, cfg, rank)
+        for (a, ga), (b, gb) in zip(l_ref, l_fus):
+            assert abs(a - b) < 2e-2 * abs(a) + 1e-3, (l_ref, l_fus)
+            assert abs(ga - gb) < 2e-2 * abs(ga) + 1e-3, (l_ref, l_fus)
+        pa, pb = e_ref.flat.params.float(), e_fus.flat.params.float()
+        rel = ((pa - pb).norm() / pa.norm()).item()
+        assert rel < 2e-3, rel
+        # every rank must hold identical parameters after the fused all-gather
+        chk = e_fus.flat.params.float().sum().reshape(1)
+        allc = Comm().all_gather_cat(chk)
+        assert torch.all(allc == allc[0]), allc
+        assert float(e_fus.flat.grads.abs().max()) == 0.0
+        assert _lib.read_status() == 0
+        fc.close()
+        if rank == 0:
+            print("OK fused_vs_nccl", l_ref, l_fus, rel)
+    else:
+        raise SystemExit(f"unknown test {what}")
+    Comm().barrier()
+
+
+if __name__ == "__main__":
+    main()

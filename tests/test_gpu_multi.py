@@ -1,0 +1,40 @@
+"""Multi-GPU tests: child processes under torchrun, one per GPU (skipped with < 2 GPUs).
+NVLS is switched off in NCCL for these runs and the kernels under test use plain peer loads
+and stores."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(what, nproc, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+           f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1", "--master-port",
+           str(_free_port()), os.path.join(HERE, "multi_worker.py"), what]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_zero_step_matches_nccl():
+    n = 4 if _ngpu() >= 4 else 2
+    out = _run("fused_vs_nccl", n)
+    assert "OK fused_vs_nccl" in out
