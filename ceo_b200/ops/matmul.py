@@ -24,7 +24,7 @@ def _as2d(t: torch.Tensor) -> torch.Tensor:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
-         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
          accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
     """``out = alpha * A @ B^T (+ bias) (+ residual) (+ out if accumulate)``.
@@ -63,13 +63,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                 r = r + out.float()
             out.copy_(r.to(out.dtype))
             return out
-        return r.to(out_dtype)
+        return r.to(out_dtype or a.dtype)
 
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a2.stride(-1) == 1 and b2.stride(-1) == 1, "operands must have a unit inner stride"
     if out is None:
         shape = (nb, M, N) if batched else (M, N)
-        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+        out = torch.empty(shape, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert not accumulate
     assert out.stride(-1) == 1
     out_f32 = out.dtype == torch.float32

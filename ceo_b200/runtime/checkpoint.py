@@ -1,0 +1,249 @@
+"""Checkpoint manager: ``{dir}/step_{step:08d}/`` with ``metadata.json``, ``tensors.bin``,
+``optimizer.bin`` / ``optimizer.rank{r}.bin``, ``rng.bin`` and ``config.yaml``.
+
+Directory layout, metadata fields and the tensor-file format are the reference's
+(src/checkpoint/manager.zig:67-246; formats in ``utils/formats.py``); ``evaluate`` and
+``generate`` expect ``{ckpt}/config.yaml`` (src/main.zig:185,232), which the reference never
+writes and this manager does.  Where the reference stops short this one goes on: the reader
+works (the reference seeks to a relative offset as if absolute: manager.zig:372-375), real
+per-tensor SHA-256, optimizer state (fp32 master + moments, one file per rank so a sharded
+run writes in parallel), RNG, loader cursor and scheduler step, retention of the newest
+``keep_last_n`` directories (manager.zig:382-423), asynchronous save from a host snapshot
+(``checkpoint.async_save``), ``convert`` to safetensors / torch, and re-sharding of the
+optimizer state when the world size changes between save and load.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import shutil
+import struct
+import threading
+import time
+
+import torch
+
+from ..utils import formats
+
+_STEP_RE = re.compile(r"^step_(\d{8})$")
+
+
+def parse_step(name: str):
+    m = _STEP_RE.match(name)
+    return int(m.group(1)) if m else None
+
+
+class CheckpointManager:
+    def __init__(self, directory, keep_last_n: int = 5, save_optimizer: bool = True,
+                 async_save: bool = False, rank: int = 0, world: int = 1):
+        self.dir = str(directory)
+        self.keep_last_n, self.save_optimizer = keep_last_n, save_optimizer
+        self.async_save, self.rank, self.world = async_save, rank, world
+        self._thread = None
+        self._error = None
+
+    # ------------------------------------------------------------------------- listing
+    def path_for(self, step: int) -> str:
+        return os.path.join(self.dir, f"step_{step:08d}")
+
+    def list_checkpoints(self) -> list[int]:
+        if not os.path.isdir(self.dir):
+            return []
+        steps = [parse_step(n) for n in os.listdir(self.dir)]
+        return sorted(s for s in steps if s is not None
+                      and os.path.exists(os.path.join(self.path_for(s), "metadata.json")))
+
+    def latest(self):
+        steps = self.list_checkpoints()
+        return self.path_for(steps[-1]) if steps else None
+
+    # --------------------------------------------------------------------------- save
+    def save(self, step: int, tensors: dict, metadata: dict, optimizer_state: dict | None = None,
+             rng_state: bytes | None = None, config_yaml: str | None = None,
+             extra: dict | None = None) -> str:
+        """``tensors``: name -> tensor (reference names/orientation), written by rank 0.
+        ``optimizer_state``: name -> tensor, this rank's slice, written by every rank."""
+        self.wait()
+        path = self.path_for(step)
+        host_tensors = {k: v.detach().to("cpu", copy=True) for k, v in tensors.items()} \
+            if self.rank == 0 else {}
+        host_opt = None
+        if optimizer_state is not None and self.save_optimizer:
+            host_opt = {k: v.detach().to("cpu", copy=True) for k, v in optimizer_state.items()}
+
+        def work():
+            try:
+                os.makedirs(path, exist_ok=True)
+                if host_opt is not None:
+                    name = "optimizer.bin" if self.world == 1 else f"optimizer.rank{self.rank}.bin"
+                    formats.write_tensor_file(os.path.join(path, name), host_opt,
+                                              formats.MAGIC_OPTIMIZER)
+                if self.rank == 0:
+                    formats.write_tensor_file(os.path.join(path, "tensors.bin"), host_tensors)
+                    if rng_state is not None:
+                        with open(os.path.join(path, "rng.bin"), "wb") as f:
+                            f.write(rng_state)
+                    if config_yaml is not None:
+                        with open(os.path.join(path, "config.yaml"), "w") as f:
+                            f.write(config_yaml)
+                    md = {"step": int(step), "epoch": 0, "tokens_seen": 0, "loss": 0.0,
+                          "learning_rate": 0.0, "timestamp": int(time.time()),
+                          "git_revision": "0" * 40, "config_hash": "0" * 64,
+                          "world_size": self.world}
+                    md.update(metadata)
+                    if extra:
+                        md["extra"] = extra
+                    tmp = os.path.join(path, "metadata.json.tmp")
+                    with open(tmp, "w") as f:
+                        json.dump(md, f, indent=1)
+                    os.replace(tmp, os.path.join(path, "metadata.json"))  # commit point
+                    self.cleanup_old()
+            except BaseException as e:  # noqa: BLE001
+                self._error = e
+
+        if self.async_save:
+            self._thread = threading.Thread(target=work, daemon=True)
+            self._thread.start()
+        else:
+            work()
+            self._raise()
+        return path
+
+    def wait(self):
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        self._raise()
+
+    def _raise(self):
+        if self._error is not None:
+            e, self._error = self._error, None
+            raise e
+
+    def cleanup_old(self):
+        steps = self.list_checkpoints()
+        if self.keep_last_n > 0:
+            for s in steps[:-self.keep_last_n]:
+                shutil.rmtree(self.path_for(s), ignore_errors=True)
+
+    # --------------------------------------------------------------------------- load
+    @staticmethod
+    def read_metadata(path) -> dict:
+        with open(os.path.join(path, "metadata.json")) as f:
+            return json.load(f)
+
+    @staticmethod
+    def load_tensors(path, verify: bool = True) -> dict:
+        return formats.read_tensor_file(os.path.join(path, "tensors.bin"), verify=verify)
+
+    def load_optimizer(self, path, shard_numel: int | None = None) -> dict | None:
+        """This rank's optimizer slice.  If the checkpoint was written with another world size
+        the per-rank files are concatenated and re-split evenly (flat buffers only)."""
+        single = os.path.join(path, "optimizer.bin")
+        mine = os.path.join(path, f"optimizer.rank{self.rank}.bin")
+        saved_world = self.read_metadata(path).get("world_size", 1)
+        if saved_world == self.world:
+            p = single if self.world == 1 else mine
+            if not os.path.exists(p):
+                return None
+            return formats.read_tensor_file(p, formats.MAGIC_OPTIMIZER)
+        files = [single] if saved_world == 1 else \
+            [os.path.join(path, f"optimizer.rank{r}.bin") for r in range(saved_world)]
+        if not all(os.path.exists(p) for p in files):
+            return None
+        parts = [formats.read_tensor_file(p, formats.MAGIC_OPTIMIZER) for p in files]
+        out = {}
+        for k in parts[0]:
+            full = torch.cat([p[k].reshape(-1) for p in parts])
+            if shard_numel is None:
+                shard_numel = -(-full.numel() // self.world)
+            need = shard_numel * self.world
+            if full.numel() < need:
+                full = torch.cat([full, full.new_zeros(need - full.numel())])
+            out[k] = full[self.rank * shard_numel:(self.rank + 1) * shard_numel].clone()
+        return out
+
+    @staticmethod
+    def load_rng(path):
+        p = os.path.join(path, "rng.bin")
+        if not os.path.exists(p):
+            return None
+        with open(p, "rb") as f:
+            return f.read()
+
+    # ----------------------------------------------------------------- validate / convert
+    @staticmethod
+    def validate(path) -> list[str]:
+        """Returns a list of problems (empty = valid): files present, index parses, sizes
+        consistent, every checksum matches."""
+        problems = []
+        for need in ("metadata.json", "tensors.bin"):
+            if not os.path.exists(os.path.join(path, need)):
+                problems.append(f"missing {need}")
+        if problems:
+            return problems
+        try:
+            json.load(open(os.path.join(path, "metadata.json")))
+        except Exception as e:  # noqa: BLE001
+            problems.append(f"metadata.json: {e}")
+        try:
+            formats.read_tensor_file(os.path.join(path, "tensors.bin"), verify=True)
+        except Exception as e:  # noqa: BLE001
+            problems.append(f"tensors.bin: {e}")
+        return problems
+
+    @staticmethod
+    def convert(input_path, output_path, fmt: str) -> None:
+        """``efla_native`` (re-write), ``pytorch`` (torch.save of the dict) or ``safetensors``."""
+        src = input_path
+        if os.path.isdir(src):
+            src = os.path.join(src, "tensors.bin")
+        tensors = formats.read_tensor_file(src)
+        if fmt == "efla_native":
+            formats.write_tensor_file(output_path, tensors)
+        elif fmt == "pytorch":
+            torch.save(tensors, output_path)
+        elif fmt == "safetensors":
+            write_safetensors(output_path, tensors)
+        else:
+            raise ValueError(f"unknown format {fmt!r} (efla_native | safetensors | pytorch)")
+
+
+_ST_DTYPES = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16",
+              torch.int64: "I64", torch.int32: "I32", torch.int8: "I8", torch.bool: "BOOL",
+              torch.float8_e4m3fn: "F8_E4M3", torch.float8_e5m2: "F8_E5M2"}
+
+
+def write_safetensors(path, tensors: dict) -> None:
+    """Minimal safetensors writer: u64 header length, JSON header, raw little-endian data."""
+    header, blobs, off = {}, [], 0
+    for name, t in tensors.items():
+        b = formats.tensor_bytes(t)
+        header[name] = {"dtype": _ST_DTYPES[t.dtype], "shape": list(t.shape),
+                        "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def read_safetensors(path) -> dict:
+    inv = {v: k for k, v in _ST_DTYPES.items()}
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = e["data_offsets"]
+        raw = torch.frombuffer(bytearray(data[a:b]), dtype=torch.uint8)
+        out[name] = raw.view(inv[e["dtype"]]).reshape(e["shape"]).clone()
+    return out

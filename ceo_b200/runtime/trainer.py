@@ -1,0 +1,228 @@
+"""Trainer: config -> engine -> data -> loop with logging, checkpointing and resume.
+
+Public surface of the reference's Trainer (src/runtime/trainer.zig): ``init`` (38-115),
+``run`` (124-188), ``smoke_test`` (191-223: 3 iterations, B=1, T=16), ``resume`` (226-242),
+``save_checkpoint`` (331-362).  Where the reference logs a constant loss of 10.0
+(trainer.zig:269-272), passes the parameters as gradients (src/model/model.zig:527-529) and
+never saves optimizer or RNG state (trainer.zig:356-357), this one trains: the loss is the
+model's cross-entropy, checkpoints carry fp32 master weights, moments, RNG, the loader cursor
+and the scheduler step, and ``resume`` restores all of them.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+
+import torch
+
+from ..data.dataset import BinaryDataset, DataLoader, Prefetcher
+from ..data.synthetic import SyntheticTokens
+from ..utils import errors
+from ..utils.config import Config
+from ..utils.telemetry import HealthStatus, Telemetry
+from .checkpoint import CheckpointManager
+from .engine import TrainEngine
+
+
+def _git_revision() -> str:
+    try:
+        import subprocess
+        r = subprocess.run(["git", "rev-parse", "HEAD"], capture_output=True, text=True, timeout=5,
+                           cwd=os.path.dirname(os.path.abspath(__file__)))
+        rev = r.stdout.strip()
+        return rev if len(rev) == 40 else "0" * 40
+    except Exception:  # noqa: BLE001
+        return "0" * 40
+
+
+class Trainer:
+    def __init__(self, cfg: Config, device=None, comm=None, telemetry: Telemetry | None = None,
+                 data_path: str | None = None, checkpoint_dir: str | None = None):
+        self.cfg = cfg
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.comm = comm
+        self.rank = comm.rank if comm is not None else 0
+        self.world = comm.world if comm is not None else 1
+        self.engine = TrainEngine(cfg, self.device, comm)
+        self.telemetry = telemetry or Telemetry(rank=self.rank, log_file=None,
+                                                log_level=cfg.telemetry.log_level)
+        ck = cfg.checkpoint
+        self.ckpt = CheckpointManager(checkpoint_dir or ck.dir, ck.keep_last_n, ck.save_optimizer,
+                                      ck.async_save, self.rank, self.world)
+        self.data_path = data_path or cfg.data.path
+        self.loader = None
+        self.epoch = 0
+        self.last_loss = float("nan")
+        t = cfg.training
+        dp = max(1, self.world)
+        self.micro_batch = t.micro_batch_size
+        self.n_micro = max(1, t.global_batch_size // (t.micro_batch_size * dp))
+
+    # ------------------------------------------------------------------------- data
+    def _open_data(self):
+        d = self.cfg.data
+        if d.synthetic.kind:
+            self._synth = SyntheticTokens(self.cfg.model.vocab_size, d.synthetic.kind,
+                                          d.synthetic.s, d.synthetic.seed, self.rank)
+            return
+        self._synth = None
+        ds = BinaryDataset.open(self.data_path)
+        self.loader = DataLoader(ds, d.seq_len, self.micro_batch, shuffle=True, drop_last=True,
+                                 seed=self.cfg.runtime.seed, dp_rank=self.rank, dp_world=self.world,
+                                 pin=self.device.type == "cuda")
+        if len(self.loader) == 0:
+            raise errors.DataExhausted(
+                f"{self.data_path}: not enough tokens for one batch of {self.micro_batch} x "
+                f"{d.seq_len + 1}")
+
+    def _next_micro_batches(self):
+        out = []
+        if self._synth is not None:
+            for _ in range(self.n_micro):
+                out.append(self._synth.batch(self.micro_batch, self.cfg.data.seq_len,
+                                             pin=self.device.type == "cuda"))
+            return out
+        while len(out) < self.n_micro:
+            b = self.loader.next()
+            if b is None:
+                self.loader.reset()
+                self.epoch += 1
+                continue
+            out.append((b.input, b.target))
+        return out
+
+    # ------------------------------------------------------------------------- loop
+    def run(self, max_steps: int | None = None) -> dict:
+        cfg, eng, tel = self.cfg, self.engine, self.telemetry
+        self._open_data()
+        total = cfg.training.total_steps if max_steps is None else \
+            min(cfg.training.total_steps, eng.step_count + max_steps)
+        tokens_per_step = self.micro_batch * self.n_micro * cfg.data.seq_len * self.world
+        flops_tok = eng.model.flops_per_token(cfg.data.seq_len)
+        tel.log("info", "trainer", f"training {cfg.model.name}: {eng.model.count_parameters()} "
+                f"parameters, {tokens_per_step} tokens/step, {self.world} rank(s)")
+        use_events = self.device.type == "cuda"
+        while eng.step_count < total:
+            batches = self._next_micro_batches()
+            lr = eng.scheduler.get_lr()
+            if use_events:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            t0 = time.time()
+            loss, gnorm = eng.train_step(batches, lr)
+            step = eng.step_count
+            log_now = step % max(1, cfg.telemetry.metrics_interval) == 0 or step == total
+            if log_now:
+                if use_events:
+                    e1.record()
+                    e1.synchronize()
+                    secs = e0.elapsed_time(e1) * 1e-3
+                    if self.comm is not None:
+                        secs = self.comm.max_over_ranks(secs)
+                else:
+                    secs = time.time() - t0
+                lv, gv = float(loss), float(gnorm)
+                self.last_loss = lv
+                if not math.isfinite(lv):
+                    tel.log_health_check(HealthStatus(nan_inf=True))
+                    raise errors.NaNDetected(f"loss is {lv} at step {step}")
+                tel.stats.update(lv, tokens_per_step, secs)
+                tps = tokens_per_step / secs if secs > 0 else 0.0
+                mfu = None
+                if use_events:
+                    from ..utils.kernel_bench import peaks
+                    mfu = tps * flops_tok / self.world / peaks()[1]
+                tel.log_step(step, eng.tokens_seen, lr, gv)
+                tel.log_metrics(step, lv, lr, eng.tokens_seen, tps, mfu)
+            if cfg.checkpoint.save_interval > 0 and step % cfg.checkpoint.save_interval == 0:
+                self.save_checkpoint()
+        self.ckpt.wait()
+        return {"step": eng.step_count, "loss": self.last_loss, "tokens_seen": eng.tokens_seen}
+
+    def smoke_test(self, iterations: int = 3) -> list[float]:
+        """3 optimizer steps on a B=1, T=16 batch (64 on a GPU, the kernels' chunk length)."""
+        T = 16 if self.device.type != "cuda" else 64
+        g = torch.Generator().manual_seed(self.cfg.runtime.seed)
+        x = torch.randint(0, self.cfg.model.vocab_size, (1, T + 1), generator=g)
+        losses = []
+        for _ in range(iterations):
+            loss, _ = self.engine.train_step([(x[:, :-1].contiguous(), x[:, 1:].contiguous())])
+            losses.append(float(loss))
+            self.telemetry.log("info", "smoke", f"iteration {len(losses)} loss {losses[-1]:.4f}")
+        return losses
+
+    # ------------------------------------------------------------------ checkpointing
+    def save_checkpoint(self) -> str:
+        eng = self.engine
+        md = {"step": eng.step_count, "epoch": self.epoch, "tokens_seen": eng.tokens_seen,
+              "loss": self.last_loss if math.isfinite(self.last_loss) else 0.0,
+              "learning_rate": eng.scheduler.get_lr(), "git_revision": _git_revision(),
+              "config_hash": self.cfg.config_hash().hex()}
+        opt = {"master": eng.flat.master}
+        opt.update({k: v for k, v in eng.flat.state.items()})
+        for name, st in eng.optimizer._muon_state.items():
+            for k, v in st.items():
+                opt[f"muon.{name}.{k}"] = v
+        for name, st in eng.optimizer._side_state.items():
+            for k, v in st.items():
+                opt[f"side.{name}.{k}"] = v
+        opt["step_count"] = torch.tensor([eng.optimizer.step_count], dtype=torch.int64)
+        rng = torch.get_rng_state().numpy().tobytes()
+        extra = {"scheduler": eng.scheduler.state_dict(),
+                 "loader": self.loader.state_dict() if self.loader is not None else None}
+        path = self.ckpt.save(eng.step_count, eng.model.state_dict_reference(), md, opt, rng,
+                              self.cfg.to_yaml(), extra)
+        self.telemetry.log("info", "checkpoint", f"saved {path}")
+        return path
+
+    def resume(self, path: str | None = None) -> dict:
+        path = path or self.ckpt.latest()
+        if path is None or not os.path.isdir(path):
+            raise errors.CheckpointNotFound(f"no checkpoint at {path or self.ckpt.dir}")
+        eng = self.engine
+        md = self.ckpt.read_metadata(path)
+        try:
+            tensors = self.ckpt.load_tensors(path)
+        except Exception as e:  # noqa: BLE001
+            raise errors.CheckpointCorrupted(str(e)) from e
+        eng.model.load_reference_state(tensors)
+        eng.flat.refresh_master()
+        opt = self.ckpt.load_optimizer(path, eng.flat.shard)
+        if opt is not None:
+            eng.flat.master.copy_(opt["master"].to(eng.flat.master))
+            for k, v in opt.items():
+                if k in ("master", "step_count"):
+                    continue
+                if k.startswith("muon."):
+                    _, rest = k.split(".", 1)
+                    name, key = rest.rsplit(".", 1)
+                    eng.optimizer._muon_state.setdefault(name, {})[key] = v.to(eng.flat.device)
+                elif k.startswith("side."):
+                    _, rest = k.split(".", 1)
+                    name, key = rest.rsplit(".", 1)
+                    eng.optimizer._side_state.setdefault(name, {})[key] = v.to(eng.flat.device)
+                else:
+                    eng.flat.buffer(k).copy_(v.to(eng.flat.device))
+            eng.optimizer.step_count = int(opt["step_count"][0]) if "step_count" in opt \
+                else int(md["step"])
+        rng = self.ckpt.load_rng(path)
+        if rng is not None:
+            torch.set_rng_state(torch.frombuffer(bytearray(rng), dtype=torch.uint8))
+        eng.step_count = int(md["step"])
+        eng.tokens_seen = int(md.get("tokens_seen", 0))
+        self.epoch = int(md.get("epoch", 0))
+        extra = md.get("extra") or {}
+        if extra.get("scheduler"):
+            eng.scheduler.load_state_dict(extra["scheduler"])
+        else:
+            eng.scheduler.current_step = eng.step_count
+        self._resume_loader = extra.get("loader")
+        if self._resume_loader and not self.cfg.data.synthetic.kind:
+            self._open_data()
+            self.loader.load_state_dict(self._resume_loader)
+            self._open_data = lambda: None  # keep the restored cursor
+        self.telemetry.log("info", "checkpoint", f"resumed {path} at step {eng.step_count}")
+        return md

@@ -197,7 +197,15 @@ def dumps(obj: Any, indent: int = 0) -> str:
                 lines.append(f"{pad}{k}: {_scalar_str(v)}")
         return "\n".join(lines)
     if isinstance(obj, list):
-        return "\n".join(f"{pad}- {_scalar_str(v)}" for v in obj)
+        lines = []
+        for v in obj:
+            if isinstance(v, dict) and v:
+                body = dumps(v, indent + 2).split("\n")
+                lines.append(f"{pad}- {body[0].lstrip()}")
+                lines.extend(body[1:])
+            else:
+                lines.append(f"{pad}- {_scalar_str(v)}")
+        return "\n".join(lines)
     return pad + _scalar_str(obj)
 
 

@@ -1,0 +1,81 @@
+"""Worker for the multi-process CPU (gloo) tests: python dist_worker.py <what> <rank> <world> <port> <dir>."""
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ceo_b200.parallel.comm import Comm  # noqa: E402
+from ceo_b200.runtime.engine import TrainEngine  # noqa: E402
+from ceo_b200.runtime.fault import Heartbeat  # noqa: E402
+from ceo_b200.utils import errors  # noqa: E402
+from ceo_b200.utils.config import Config  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def main():
+    what, rank, world, port, out = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), \
+        int(sys.argv[4]), sys.argv[5]
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=__import__("datetime")
+                          .timedelta(seconds=60))
+    if what == "heartbeat":
+        hb = Heartbeat(store, rank, world, interval=0.1, timeout=1.0).start()
+        time.sleep(0.5)
+        assert hb.dead_ranks() == []
+        if rank == 1:       # rank 1 stops beating, then leaves between "steps"
+            hb.pause()
+            time.sleep(3.0)
+            return
+        t0 = time.time()
+        while time.time() - t0 < 5:
+            try:
+                hb.check()
+            except errors.RankFailure as e:
+                open(os.path.join(out, f"detected{rank}"), "w").write(str(e))
+                return
+            time.sleep(0.1)
+        raise SystemExit("failure not detected")
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world)
+    comm = Comm()
+    if what == "collectives":
+        t = torch.arange(8, dtype=torch.float32) + rank
+        buf = t.clone()
+        sl = comm.reduce_scatter(buf, rank * (8 // world), (rank + 1) * (8 // world))
+        want = sum(torch.arange(8, dtype=torch.float32) + r for r in range(world))
+        assert torch.equal(sl, want[rank * (8 // world):(rank + 1) * (8 // world)])
+        full = torch.zeros(8)
+        full[rank * (8 // world):(rank + 1) * (8 // world)] = rank + 1.0
+        comm.all_gather(full, rank * (8 // world), (rank + 1) * (8 // world))
+        assert full.tolist() == [float(i // (8 // world) + 1) for i in range(8)]
+        a2a_in = torch.arange(world * 2, dtype=torch.float32) + 100 * rank
+        a2a_out = torch.empty_like(a2a_in)
+        comm.all_to_all(a2a_out, a2a_in)
+        assert a2a_out.tolist() == [100.0 * r + 2 * rank + j for r in range(world) for j in range(2)]
+        b = torch.tensor([float(rank)])
+        comm.broadcast(b, src=world - 1)
+        assert b.item() == world - 1
+        assert comm.max_over_ranks(float(rank), device="cpu") == world - 1
+        comm.barrier()
+    elif what in ("zero_adamw", "zero_lion_muon"):
+        cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+        cfg.training.optimizer = "adamw" if what == "zero_adamw" else "lion_muon"
+        cfg.training.muon_iterations = 3
+        cfg.runtime.world_size = world
+        eng = TrainEngine(cfg, "cpu", comm, seed=0)
+        g = torch.Generator().manual_seed(0)
+        x = torch.randint(0, 256, (world * 2, 65), generator=g)
+        mine = x[rank * 2:(rank + 1) * 2]
+        for _ in range(3):
+            loss, gn = eng.train_step([(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())], lr=1e-3)
+        torch.save({"params": eng.flat.params.clone(), "loss": float(loss), "gn": float(gn)},
+                   os.path.join(out, f"{what}_{rank}.pt"))
+    comm.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,129 @@
+"""Multi-process CPU tests (gloo, world_size 2): collectives, ZeRO-sharded optimizers equal
+to the single-process result, heartbeat-based failure detection, recovery driver."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from ceo_b200.runtime import fault
+from ceo_b200.runtime.engine import TrainEngine
+from ceo_b200.utils import errors
+from ceo_b200.utils.config import Config
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _spawn(what, world, out, timeout=240):
+    port = _port()
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "dist_worker.py"), what, str(r),
+                               str(world), str(port), str(out)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append((p.returncode, o))
+    for rc, o in outs:
+        assert rc == 0, o[-3000:]
+
+
+def test_gloo_collectives(tmp_path):
+    _spawn("collectives", 2, tmp_path)
+
+
+@pytest.mark.parametrize("kind", ["zero_adamw", "zero_lion_muon"])
+def test_sharded_optimizer_matches_single_process(tmp_path, kind):
+    world = 2
+    _spawn(kind, world, tmp_path)
+    res = [torch.load(tmp_path / f"{kind}_{r}.pt") for r in range(world)]
+    assert torch.equal(res[0]["params"][:1000], res[1]["params"][:1000])
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    cfg.training.optimizer = "adamw" if kind == "zero_adamw" else "lion_muon"
+    cfg.training.muon_iterations = 3
+    eng = TrainEngine(cfg, "cpu", None, seed=0)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randint(0, 256, (world * 2, 65), generator=g)
+    for _ in range(3):
+        # one process, the two ranks' micro-batches as gradient accumulation: with the
+        # optimizer's 1/n_micro scale the summed gradient matches sum-over-ranks / world
+        batches = [(x[r * 2:(r + 1) * 2, :-1].contiguous(), x[r * 2:(r + 1) * 2, 1:].contiguous())
+                   for r in range(world)]
+        loss, gn = eng.train_step(batches, lr=1e-3)
+    n = eng.flat.numel()
+    # the distributed run sums gradients over ranks (no 1/world): compare against that
+    eng2 = TrainEngine(cfg, "cpu", None, seed=0)
+    for _ in range(3):
+        for tok, tgt in batches:
+            eng2.model(tok, tgt).backward()
+        eng2.optimizer.step(1e-3, grad_scale=1.0)
+    ref_params = eng2.flat.params[:n]
+    assert torch.allclose(res[0]["params"][:n], ref_params, atol=2e-5), \
+        (res[0]["params"][:n] - ref_params).abs().max()
+
+
+def test_heartbeat_detects_silent_rank(tmp_path):
+    _spawn("heartbeat", 2, tmp_path, timeout=60)
+    msg = (tmp_path / "detected0").read_text()
+    assert "rank(s) [1]" in msg
+
+
+def test_kernel_watch_and_step_guard():
+    state = {"code": 0}
+    kw = fault.KernelWatch(lambda: state["code"], lambda: state.update(code=0))
+    kw.check()
+    state["code"] = 112
+    with pytest.raises(errors.KernelWaitTimeout, match="peer barrier 1: no signal from rank 2"):
+        kw.check()
+    assert state["code"] == 0
+    assert "MMA waiting for data" in fault.describe_status(2)
+    g = fault.StepGuard(None, kw)
+    assert g.run(lambda: (1.5, 0.1)) == (1.5, 0.1)
+    with pytest.raises(errors.NaNDetected):
+        g.run(lambda: (float("nan"), 0.0))
+    with pytest.raises(errors.CommunicationError):
+        g.run(lambda: (_ for _ in ()).throw(RuntimeError("NCCL communicator was aborted")))
+    with pytest.raises(RuntimeError, match="other"):
+        g.run(lambda: (_ for _ in ()).throw(RuntimeError("other")))
+
+
+def test_run_with_recovery_resumes_after_injected_failure(tmp_path):
+    from ceo_b200.runtime.trainer import Trainer
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    cfg.data.seq_len = 32
+    cfg.training.global_batch_size = cfg.training.micro_batch_size = 2
+    cfg.checkpoint.save_interval = 2
+    cfg.checkpoint.async_save = False
+    inj = fault.FaultInjector()
+    inj.fail_at_step = 5
+    restarts = []
+
+    def make(attempt):
+        tr = Trainer(cfg, "cpu", checkpoint_dir=str(tmp_path / "ck"))
+        orig = tr.engine.train_step
+
+        def guarded(batches, lr=None):
+            inj.maybe_raise(tr.engine.step_count + 1)
+            return orig(batches, lr)
+        tr.engine.train_step = guarded
+        return tr
+    tr = fault.run_with_recovery(make, total_steps=8, on_restart=lambda a, e: restarts.append(str(e)))
+    assert tr.engine.step_count == 8 and restarts == ["injected failure"]
+    assert tr.ckpt.list_checkpoints()[-1] == 8
+    # a corrupted newest checkpoint falls back to the one before it
+    fault.FaultInjector.corrupt_file(os.path.join(tr.ckpt.path_for(8), "tensors.bin"))
+    tr2 = fault.run_with_recovery(lambda a: Trainer(cfg, "cpu", checkpoint_dir=str(tmp_path / "ck")),
+                                  total_steps=8)
+    assert tr2.engine.step_count == 8
