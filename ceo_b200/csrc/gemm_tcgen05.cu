@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "common/ptx.cuh"
 #include "include/ceo_kernels.h"
@@ -47,9 +48,35 @@ struct GemmParams {
   float alpha;
   int num_m, num_n;
   int* status;
+  // ---- collectives fused into the kernel (all zero for a plain GEMM) --------------------
+  int m_rot, n_rot;        // tile traversal starts at this m / n block (local data first)
+  // all-gather of one operand: the first `ag_ctas` CTAs pull the peers' row-shards into
+  // the local gathered buffer (which the tensor map reads) and publish one flag per block
+  // of BM (A) or BN (B) rows; the TMA producer waits for a block's flag before loading it.
+  int ag_operand;          // 0 none, 1 A, 2 B
+  int ag_ctas;
+  int ag_rows_per_shard;   // rows of the gathered operand owned by each rank
+  long long ag_row_bytes;  // bytes per row (dense rows)
+  const void* ag_src[8];   // rank r's shard, as mapped on this rank (entry `rank` unused)
+  void* ag_dst;            // local gathered buffer
+  unsigned* ag_flags;      // local, one per row block, counts up by 1 per call
+  unsigned ag_target;
+  // reduce-scatter of C over M: the epilogue stores each partial tile into the staging
+  // area of the rank that owns those rows and bumps a counter there; after its last tile a
+  // CTA reduces its share of this rank's own rows from the staged partials of all ranks.
+  int rs_on;
+  int rs_rows_per_rank;
+  void* rs_stage[8];       // rank j's staging: [world][rows_per_rank][N] bf16
+  unsigned* rs_count[8];   // rank j's counters: [world][rows_per_rank / BM]
+  unsigned rs_target;      // counter value that means "all tiles of this call arrived"
+  void* rs_out;            // bf16 [rows_per_rank][N], ld = rs_ldo
+  const void* rs_residual; // optional bf16, same shape/ld as rs_out
+  long long rs_ldo;
+  int rank, world;
 };
 
-enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4 };
+enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4, ST_AG_WAIT = 5,
+             ST_RS_WAIT = 6, ST_COPY = 7 };
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -94,6 +121,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int tiles_per_batch = p.num_m * p.num_n;
   const int total_tiles = tiles_per_batch * p.batch;
   const int num_kb = (p.K + BK - 1) / BK;
+  // the first ag_ctas CTAs only copy (all-gather); the others walk the output tiles
+  const bool copy_cta = static_cast<int>(blockIdx.x) < p.ag_ctas;
+  const int tile_step = static_cast<int>(gridDim.x) - p.ag_ctas;
+  const int first_tile = copy_cta ? total_tiles : static_cast<int>(blockIdx.x) - p.ag_ctas;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -101,11 +132,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
-        const int m0 = (r % p.num_m) * BM;
-        const int n0 = (r / p.num_m) * BN;
+        const int m0 = ((r % p.num_m + p.m_rot) % p.num_m) * BM;
+        const int n0 = ((r / p.num_m + p.n_rot) % p.num_n) * BN;
+        if (p.ag_operand) {
+          // rows pulled from a peer become loadable once the copy CTAs have published them
+          const int row0 = p.ag_operand == 1 ? m0 : n0;
+          const int blk = p.ag_operand == 1 ? m0 / BM : n0 / BN;
+          if (row0 / p.ag_rows_per_shard != p.rank) {
+            if (!flag_wait_ge<false>(p.ag_flags + blk, p.ag_target)) {
+              atomicCAS(p.status, 0, ST_AG_WAIT);
+              ok = false;
+              break;
+            }
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
             atomicCAS(p.status, 0, ST_PRODUCER);
@@ -137,6 +181,74 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         // let any copy still in flight land before the CTA's shared memory goes away
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
       }
+      if (copy_cta) {
+        // ---------------------------------------------------- all-gather copy CTA
+        // Pulls row blocks of the peers' shards through a ring of shared-memory buffers with
+        // bulk async copies (peer -> smem -> local gathered buffer), nearest peer first, and
+        // publishes a block's flag once its bytes have landed in local memory.
+        const int blk_rows = p.ag_operand == 1 ? BM : BN;
+        const int blks_per_shard = p.ag_rows_per_shard / blk_rows;
+        const long long blk_bytes = p.ag_row_bytes * blk_rows;
+        constexpr uint32_t CHUNK = 32768;
+        constexpr int RING = (STAGES * STAGE_BYTES) / CHUNK;  // 6 buffers of 32 KB
+        const int cpb = static_cast<int>((blk_bytes + CHUNK - 1) / CHUNK);  // chunks per block
+        const int my_blks = static_cast<int>(blockIdx.x) < blks_per_shard
+                                ? (blks_per_shard - static_cast<int>(blockIdx.x) + p.ag_ctas - 1) /
+                                      p.ag_ctas
+                                : 0;
+        const int per_peer = my_blks * cpb;
+        const int total = (p.world - 1) * per_peer;
+        uint32_t ring_ph = 0;  // bit i = phase of ring barrier i (bars[0..RING) are count-1)
+        // chunk idx -> peer (nearest first), block, byte offset
+        auto locate = [&](int idx, const uint8_t*& src, uint8_t*& dst, uint32_t& nb, int& flag,
+                          bool& last) {
+          const int peer = (p.rank + 1 + idx / per_peer) % p.world;
+          const int rem = idx % per_peer;
+          const int bi = static_cast<int>(blockIdx.x) + (rem / cpb) * p.ag_ctas;
+          const long long off = static_cast<long long>(bi) * blk_bytes +
+                                static_cast<long long>(rem % cpb) * CHUNK;
+          const long long left = static_cast<long long>(bi + 1) * blk_bytes - off;
+          nb = static_cast<uint32_t>(left < CHUNK ? left : CHUNK);
+          src = reinterpret_cast<const uint8_t*>(p.ag_src[peer]) + off;
+          dst = reinterpret_cast<uint8_t*>(p.ag_dst) +
+                static_cast<long long>(peer) * p.ag_rows_per_shard * p.ag_row_bytes + off;
+          flag = peer * blks_per_shard + bi;
+          last = (rem % cpb) == cpb - 1;
+        };
+        int issued = 0;
+        bool cok = true;
+        for (int done = 0; done < total && cok; ++done) {
+          while (issued < total && issued < done + RING) {
+            if (issued >= RING) bulk_wait_read<0>();  // the ring slot's last store has read it
+            const uint8_t* src; uint8_t* dst; uint32_t nb; int flag; bool last;
+            locate(issued, src, dst, nb, flag, last);
+            const int slot = issued % RING;
+            mbar_arrive_expect_tx(&bars[slot], nb);
+            bulk_load(smem + slot * CHUNK, src, nb, &bars[slot]);
+            ++issued;
+          }
+          const uint8_t* src; uint8_t* dst; uint32_t nb; int flag; bool last;
+          locate(done, src, dst, nb, flag, last);
+          const int slot = done % RING;
+          if (!mbar_wait(&bars[slot], (ring_ph >> slot) & 1)) {
+            atomicCAS(p.status, 0, ST_COPY);
+            cok = false;
+            break;
+          }
+          ring_ph ^= 1u << slot;
+          fence_proxy_async_smem();
+          bulk_store(dst, smem + slot * CHUNK, nb);
+          bulk_commit();
+          if (last) {
+            bulk_wait<0>();  // every byte of this block is in local memory
+            fence_proxy_async_all();
+            __threadfence();
+            st_release_gpu(p.ag_flags + flag, p.ag_target);
+          }
+        }
+        if (!cok) for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        bulk_wait<0>();
+      }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
@@ -146,7 +258,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1)) {
@@ -184,13 +296,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
-      const int m0 = (r % p.num_m) * BM;
-      const int n0 = (r / p.num_m) * BN;
+      const int m0 = ((r % p.num_m + p.m_rot) % p.num_m) * BM;
+      const int n0 = ((r / p.num_m + p.n_rot) % p.num_n) * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_ph)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE);
         ok = false;
@@ -201,7 +313,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C);
-      const long long coff = static_cast<long long>(b) * p.batch_stride_c + row * p.ldc;
+      long long coff = static_cast<long long>(b) * p.batch_stride_c + row * p.ldc;
+      int rs_owner = 0;
+      if (p.rs_on) {
+        // partial tile -> staging area of the rank that owns these rows (peer store)
+        rs_owner = m0 / p.rs_rows_per_rank;
+        cbase = reinterpret_cast<uint8_t*>(p.rs_stage[rs_owner]);
+        coff = (static_cast<long long>(p.rank) * p.rs_rows_per_rank +
+                (row - rs_owner * p.rs_rows_per_rank)) * p.ldc;
+      }
       const __nv_bfloat16* rrow =
           p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) +
                            static_cast<long long>(b) * p.batch_stride_r + row * p.ldr
@@ -294,6 +414,69 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (p.rs_on) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          red_release_sys_add(p.rs_count[rs_owner] + p.rank * (p.rs_rows_per_rank / BM) +
+                                  (m0 - rs_owner * p.rs_rows_per_rank) / BM,
+                              1u);
+      }
+    }
+    if (p.rs_on && ok && !copy_cta) {
+      // ---------------------------------------------------- reduce this rank's own rows
+      // Work item = one (row block, 256-column block) of the rows this rank owns; a block is
+      // complete when every source rank's counter for it has reached the target.
+      const int bpr = p.rs_rows_per_rank / BM;
+      const int items = bpr * p.num_n;
+      const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
+      const unsigned* cnt = p.rs_count[p.rank];
+      for (int item = first_tile; item < items && ok; item += tile_step) {
+        const int lb = item % bpr, nb = item / bpr;
+        for (int src = 0; src < p.world; ++src) {
+          if (!flag_wait_ge<true>(cnt + src * bpr + lb, p.rs_target)) {
+            if (lane == 0) atomicCAS(p.status, 0, ST_RS_WAIT);
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) break;
+        const int ncols = min(BN, p.N - nb * BN);
+        const int c = lane * 8;  // a warp covers one 256-column row segment per iteration
+        for (int rr = 0; rr < 32 && c < ncols; ++rr) {
+          const int row = lb * BM + quad * 32 + rr;  // row within this rank's slice
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int src = 0; src < p.world; ++src) {
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
+                stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row) * p.ldc +
+                nb * BN + c));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 x = __bfloat1622float2(h[j]);
+              acc8[2 * j] += x.x;
+              acc8[2 * j + 1] += x.y;
+            }
+          }
+          if (p.rs_residual) {
+            const uint4 u = *reinterpret_cast<const uint4*>(
+                reinterpret_cast<const __nv_bfloat16*>(p.rs_residual) + row * p.rs_ldo + nb * BN + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 x = __bfloat1622float2(h[j]);
+              acc8[2 * j] += x.x;
+              acc8[2 * j + 1] += x.y;
+            }
+          }
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo +
+                                    nb * BN + c) = o;
+        }
+      }
     }
   }
 
@@ -372,13 +555,26 @@ static cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
 
 }  // namespace ceo
 
-extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
-                             long long lda, long long ldb, long long ldc, int a_mn_major,
-                             int b_mn_major, int batch, long long batch_stride_a,
-                             long long batch_stride_b, long long batch_stride_c, int out_f32,
-                             int accumulate, float alpha, const float* bias, const void* residual,
-                             long long ldr, long long batch_stride_r, int* status, int max_ctas,
-                             cudaStream_t stream) {
+// Host-side description of the collective fused into a GEMM launch (see GemmParams).
+struct FusedDesc {
+  int kind = 0;  // 0 plain, 1 all-gather of A, 2 all-gather of B, 3 reduce-scatter of C
+  int rank = 0, world = 1;
+  int copy_ctas = 0;
+  void* const* peers = nullptr;    // AG: gathered buffers per rank; RS: staging per rank
+  void* const* counters = nullptr; // RS: counters per rank
+  unsigned* flags = nullptr;       // AG: local flags
+  unsigned target = 0;
+  void* rs_out = nullptr;
+  const void* rs_residual = nullptr;
+  long long rs_ldo = 0;
+};
+
+static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int a_mn_major, int b_mn_major, int batch,
+                    long long batch_stride_a, long long batch_stride_b, long long batch_stride_c,
+                    int out_f32, int accumulate, float alpha, const float* bias,
+                    const void* residual, long long ldr, long long batch_stride_r, int* status,
+                    int max_ctas, const FusedDesc& fz, cudaStream_t stream) {
   using namespace ceo;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA needs 16-byte aligned bases and row strides
@@ -404,6 +600,7 @@ extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (rc) return -4;
 
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.C = C;
   p.residual = residual;
   p.bias = bias;
@@ -418,14 +615,119 @@ extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.num_m = (M + BM - 1) / BM;
   p.num_n = (N + BN - 1) / BN;
   p.status = status;
-  long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
+  p.rank = fz.rank;
+  p.world = fz.world;
   int cap = g_num_sms;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
-  int grid = static_cast<int>(total < cap ? total : cap);
+  if (fz.kind == 1 || fz.kind == 2) {
+    // gathered operand: K-major rows only, shards of whole row blocks, dense rows
+    const int rows = fz.kind == 1 ? M : N;
+    const int blk = fz.kind == 1 ? BM : BN;
+    const long long ld = fz.kind == 1 ? lda : ldb;
+    if ((fz.kind == 1 ? a_mn_major : b_mn_major) || batch != 1 || ld != K ||
+        rows % fz.world || (rows / fz.world) % blk || fz.world < 2 || fz.world > 8)
+      return -5;
+    p.ag_operand = fz.kind;
+    p.ag_ctas = fz.copy_ctas > 0 ? fz.copy_ctas : 8;
+    if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
+    p.ag_rows_per_shard = rows / fz.world;
+    p.ag_row_bytes = static_cast<long long>(K) * 2;
+    for (int r = 0; r < fz.world; ++r)
+      p.ag_src[r] = static_cast<const uint8_t*>(fz.peers[r]) +
+                    static_cast<long long>(r) * p.ag_rows_per_shard * p.ag_row_bytes;
+    p.ag_dst = const_cast<void*>(fz.kind == 1 ? A : B);
+    p.ag_flags = fz.flags;
+    p.ag_target = fz.target;
+    const int rot = fz.rank * (p.ag_rows_per_shard / blk);
+    if (fz.kind == 1) p.m_rot = rot; else p.n_rot = rot;
+  } else if (fz.kind == 3) {
+    if (batch != 1 || out_f32 || accumulate || bias || residual || M % fz.world ||
+        (M / fz.world) % BM || (N & 7) || fz.world < 2 || fz.world > 8)
+      return -5;
+    p.rs_on = 1;
+    p.rs_rows_per_rank = M / fz.world;
+    for (int r = 0; r < fz.world; ++r) {
+      p.rs_stage[r] = fz.peers[r];
+      p.rs_count[r] = static_cast<unsigned*>(fz.counters[r]);
+    }
+    p.rs_target = fz.target;
+    p.rs_out = fz.rs_out;
+    p.rs_residual = fz.rs_residual;
+    p.rs_ldo = fz.rs_ldo;
+    p.ldc = N;  // staging rows are dense
+    // other ranks' rows first, this rank's own rows last
+    p.m_rot = ((fz.rank + 1) % fz.world) * (p.rs_rows_per_rank / BM);
+  }
+  long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
+  int grid = static_cast<int>(total + p.ag_ctas < cap ? total + p.ag_ctas : cap);
   cudaError_t e;
   if (a_mn_major == 0 && b_mn_major == 0) e = launch<0, 0>(ta, tb, p, grid, stream);
   else if (a_mn_major == 0) e = launch<0, 1>(ta, tb, p, grid, stream);
   else if (b_mn_major == 0) e = launch<1, 0>(ta, tb, p, grid, stream);
   else e = launch<1, 1>(ta, tb, p, grid, stream);
   return static_cast<int>(e);
+}
+
+extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                             long long lda, long long ldb, long long ldc, int a_mn_major,
+                             int b_mn_major, int batch, long long batch_stride_a,
+                             long long batch_stride_b, long long batch_stride_c, int out_f32,
+                             int accumulate, float alpha, const float* bias, const void* residual,
+                             long long ldr, long long batch_stride_r, int* status, int max_ctas,
+                             cudaStream_t stream) {
+  FusedDesc fz;
+  return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, batch, batch_stride_a,
+                  batch_stride_b, batch_stride_c, out_f32, accumulate, alpha, bias, residual, ldr,
+                  batch_stride_r, status, max_ctas, fz, stream);
+}
+
+// All-gather fused into the GEMM that consumes the gathered operand.  `gathered` is the table
+// of every rank's gathered buffer (rows x K bf16, dense); rank r's own shard already sits in
+// rows [r*rows/world, (r+1)*rows/world) of ITS buffer, and copy CTAs of this launch pull the
+// other shards from the peers while the remaining CTAs compute, local rows first.
+// operand: 1 = A (M rows gathered), 2 = B (N rows gathered).  The non-gathered operand and C
+// are ordinary local tensors.  `flags`: local unsigned[rows/block]; target grows by 1 per call.
+extern "C" int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void* C,
+                                int M, int N, int K, long long ld_other, long long ldc,
+                                int other_mn_major, int out_f32, int accumulate, float alpha,
+                                const void* residual, long long ldr, void* flags,
+                                unsigned int target, int rank, int world, int copy_ctas,
+                                int* status, cudaStream_t stream) {
+  if (operand != 1 && operand != 2) return -5;
+  FusedDesc fz;
+  fz.kind = operand;
+  fz.rank = rank;
+  fz.world = world;
+  fz.copy_ctas = copy_ctas;
+  fz.peers = gathered;
+  fz.flags = static_cast<unsigned*>(flags);
+  fz.target = target;
+  const void* A = operand == 1 ? gathered[rank] : other;
+  const void* B = operand == 2 ? gathered[rank] : other;
+  return gemm_run(A, B, C, M, N, K, operand == 1 ? K : ld_other, operand == 2 ? K : ld_other, ldc,
+                  operand == 1 ? 0 : other_mn_major, operand == 2 ? 0 : other_mn_major, 1, 0, 0, 0,
+                  out_f32, accumulate, alpha, nullptr, residual, ldr, 0, status, 0, fz, stream);
+}
+
+// GEMM fused with the reduce-scatter of its output over M: every rank computes the partial
+// product of its K-slice; out (M/world x N bf16, this rank's rows) = sum over ranks (+residual).
+// `stage`: table of per-rank staging buffers [world][M/world][N] bf16; `counters`: table of
+// per-rank unsigned[world][M/world/128]; target = 4 * ceil(N/256) * (number of calls so far).
+extern "C" int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
+                                long long ldb, int a_mn_major, int b_mn_major, float alpha,
+                                void* const* stage, void* const* counters, unsigned int target,
+                                void* out, const void* residual, long long ldo, int rank,
+                                int world, int* status, cudaStream_t stream) {
+  FusedDesc fz;
+  fz.kind = 3;
+  fz.rank = rank;
+  fz.world = world;
+  fz.peers = stage;
+  fz.counters = counters;
+  fz.target = target;
+  fz.rs_out = out;
+  fz.rs_residual = residual;
+  fz.rs_ldo = ldo;
+  return gemm_run(A, B, stage[rank], M, N, K, lda, ldb, N, a_mn_major, b_mn_major, 1, 0, 0, 0, 0,
+                  0, alpha, nullptr, nullptr, 0, 0, status, 0, fz, stream);
 }

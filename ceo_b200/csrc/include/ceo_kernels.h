@@ -165,6 +165,27 @@ int ceo_symm_barrier(void* const* flags, int rank, int world, int slot, unsigned
                      int* status, cudaStream_t stream);
 int ceo_symm_allreduce(void* const* bufs, void* const* flags, float* out, int n, int rank,
                        int world, unsigned int epoch, int* status, cudaStream_t stream);
+/* All-gather fused into the consuming GEMM (copy CTAs pull peer shards through shared memory
+ * with bulk async copies while the other CTAs compute, local rows first; the TMA producer
+ * waits on per-row-block flags).  gathered[r] = rank r's (rows x K) bf16 buffer whose own
+ * shard is already in place; operand 1 = A (M rows), 2 = B (N rows).  flags: local
+ * unsigned[rows / (128 for A, 256 for B)], zeroed once; target grows by 1 per call.
+ * Call ceo_symm_barrier first so every rank's shard is complete. */
+int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void* C, int M, int N,
+                     int K, long long ld_other, long long ldc, int other_mn_major, int out_f32,
+                     int accumulate, float alpha, const void* residual, long long ldr, void* flags,
+                     unsigned int target, int rank, int world, int copy_ctas, int* status,
+                     cudaStream_t stream);
+/* GEMM fused with the reduce-scatter of its output over M (epilogue stores partial tiles
+ * into the owner's staging area over NVLink and bumps its counters; each rank then reduces
+ * its own rows, adding an optional bf16 residual).  stage[r]: [world][M/world][N] bf16;
+ * counters[r]: unsigned[world][M/world/128], zeroed once; target = 4*ceil(N/256)*calls.
+ * Call ceo_symm_barrier first so no rank is still reducing the previous call. */
+int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
+                     long long ldb, int a_mn_major, int b_mn_major, float alpha,
+                     void* const* stage, void* const* counters, unsigned int target, void* out,
+                     const void* residual, long long ldo, int rank, int world, int* status,
+                     cudaStream_t stream);
 /* One cooperative launch per rank: reduce-scatter of the fp32 gradients (peer loads) ->
  * global-norm clip -> AdamW on the rank's fp32 master slice [lo, lo+n) -> bf16 parameters
  * stored into every rank's buffer -> this rank's gradient buffer zeroed. */

@@ -38,3 +38,10 @@ def test_fused_zero_step_matches_nccl():
     n = 4 if _ngpu() >= 4 else 2
     out = _run("fused_vs_nccl", n)
     assert "OK fused_vs_nccl" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_ag_gemm_and_gemm_rs():
+    n = 4 if _ngpu() >= 4 else 2
+    out = _run("tp_fused", n)
+    assert "OK tp_fused" in out
