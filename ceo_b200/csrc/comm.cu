@@ -286,3 +286,47 @@ extern "C" int ceo_zero_step(void* const* grads, void* const* params, void* cons
   return static_cast<int>(cudaLaunchCooperativeKernel(
       reinterpret_cast<void*>(zero_step_kernel), dim3(grid), dim3(512), kargs, 0, stream));
 }
+
+// ---------------------------------------------------------------------------------------
+// Context-parallel state exchange: every rank stores its block of `n` floats (the affine map
+// (P_r, R_r) of its sequence span, or (Q_r) in backward) into slot `rank` of every peer's
+// gather buffer and then joins a flag barrier, all in one launch: when the kernel ends, slot
+// s of the local buffer holds rank s's block.  The last CTA to finish its stores runs the
+// barrier (a device-wide counter elects it), so no second launch and no host round trip.
+namespace ceo {
+__global__ void __launch_bounds__(256)
+cp_exchange_kernel(const float* __restrict__ src, PeerPtrs dst, PeerPtrs flags, long long n,
+                   int rank, int world, unsigned epoch, unsigned* done_counter, int* status) {
+  const long long n4 = n >> 2;
+  const float4* s4 = reinterpret_cast<const float4*>(src);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = s4[i];
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<float4*>(reinterpret_cast<float*>(dst.p[r]) + rank * n)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {  // every CTA of this rank has issued and fenced its stores
+      *done_counter = 0;
+      peer_barrier(flags, rank, world, 2, epoch, status);
+    }
+  }
+}
+}  // namespace ceo
+
+extern "C" int ceo_cp_exchange(const float* src, void* const* gather, void* const* flags,
+                               long long n, int rank, int world, unsigned int epoch,
+                               unsigned int* done_counter, int* status, cudaStream_t stream) {
+  if (world < 1 || world > MAXR || n <= 0 || (n & 3)) return -5;
+  PeerPtrs d, f;
+  fill_peers(d, gather, world);
+  fill_peers(f, flags, world);
+  int grid = static_cast<int>((n / 4 + 255) / 256);
+  if (grid > 64) grid = 64;
+  cp_exchange_kernel<<<grid, 256, 0, stream>>>(src, d, f, n, rank, world, epoch, done_counter,
+                                               status);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -911,3 +911,72 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
         static_cast<bf16*>(dk), dbeta, rows, H, dq_stride, dk_stride, normalize);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------
+// Stage-by-stage access to the six kernels, for callers that interleave them with other work
+// (context parallelism runs the state recurrences more than once around a state exchange).
+// ptrs: 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u, 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO,
+//       12 dloc, 13 dup, 14 dstates, 15 ds_final, 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha
+// strides (elements per token): 0 q, 1 k, 2 v, 3 dq, 4 dk, 5 dv
+// stage: 0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd, 5 bwd_final
+namespace ceo {
+template <int D>
+static int efla_stage_impl(int stage, void* const* P, const long long* S, int B, int T, int H,
+                           cudaStream_t st) {
+  static bool cfg = false;
+  if (!cfg) {
+    cudaError_t e;
+    if ((e = set_smem(efla_wy_kernel<D>, smem_wy<D>())) != cudaSuccess) return e;
+    if ((e = set_smem(efla_state_fwd_kernel<D>, smem_state_fwd<D>())) != cudaSuccess) return e;
+    if ((e = set_smem(efla_out_kernel<D>, smem_out<D>())) != cudaSuccess) return e;
+    if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
+    if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
+    if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
+    cfg = true;
+  }
+  const int n = T / CH;
+  dim3 gpar(n, B * H), gser(D / BV, B * H);
+  auto b16 = [&](int i) { return static_cast<bf16*>(P[i]); };
+  auto f32 = [&](int i) { return static_cast<float*>(P[i]); };
+  switch (stage) {
+    case 0:
+      efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(b16(1), b16(2), f32(3), b16(4), b16(5), T,
+                                                         H, S[1], S[2]);
+      break;
+    case 1:
+      efla_state_fwd_kernel<D><<<gser, 128, smem_state_fwd<D>(), st>>>(
+          b16(1), b16(4), b16(5), f32(9), b16(6), b16(7), f32(10), T, H, S[1]);
+      break;
+    case 2:
+      efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(b16(0), b16(1), b16(6), b16(7), b16(8),
+                                                           T, H, S[0], S[1]);
+      break;
+    case 3:
+      efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(
+          b16(0), b16(1), b16(6), b16(7), b16(11), b16(17), b16(12), T, H, S[0], S[1], S[3]);
+      break;
+    case 4:
+      efla_state_bwd_kernel<D><<<gser, 128, smem_state_bwd<D>(), st>>>(
+          b16(0), b16(1), b16(4), b16(11), b16(12), f32(15), b16(13), b16(14), f32(16), T, H, S[0],
+          S[1]);
+      break;
+    case 5:
+      efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
+          b16(0), b16(1), b16(2), f32(3), b16(6), b16(7), b16(11), b16(13), b16(14), b16(18),
+          b16(19), f32(20), T, H, S[0], S[1], S[2], S[4], S[5]);
+      break;
+    default:
+      return -5;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+}  // namespace ceo
+
+extern "C" int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T,
+                              int H, int D, cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || H <= 0 || (T % ceo::CH) || (D != 64 && D != 128)) return -5;
+  for (int i = 0; i < 6; ++i)
+    if (strides[i] & 7) return -2;
+  return D == 64 ? ceo::efla_stage_impl<64>(stage, ptrs, strides, B, T, H, stream)
+                 : ceo::efla_stage_impl<128>(stage, ptrs, strides, B, T, H, stream);
+}

@@ -52,6 +52,12 @@ int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha
                  float* ds0, int B, int T, int H, int D, long long q_stride, long long k_stride,
                  long long v_stride, long long dq_stride, long long dk_stride,
                  long long dv_stride, int* status, cudaStream_t stream);
+/* One of the six EFLA kernels at a time (0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd,
+ * 5 bwd_final).  ptrs (host array of 21 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
+ * 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO, 12 dloc, 13 dup, 14 dstates, 15 ds_final,
+ * 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha; strides (host array of 6): q, k, v, dq, dk, dv. */
+int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T, int H,
+                   int D, cudaStream_t stream);
 /* q/k L2 normalisation (optional) + alpha = c(beta, |k|^2); one launch each way.
  * beta: fp32 (rows*H) or one scalar (beta_scalar = 1).  qn, kn: bf16 (rows, H, D) dense. */
 int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta, int beta_scalar, void* qn,
@@ -186,6 +192,11 @@ int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long lon
                      void* const* stage, void* const* counters, unsigned int target, void* out,
                      const void* residual, long long ldo, int rank, int world, int* status,
                      cudaStream_t stream);
+/* Context-parallel exchange: store `n` floats into slot `rank` of every rank's gather buffer
+ * (n floats per slot) and barrier, in one launch.  done_counter: local unsigned, zero. */
+int ceo_cp_exchange(const float* src, void* const* gather, void* const* flags, long long n,
+                    int rank, int world, unsigned int epoch, unsigned int* done_counter,
+                    int* status, cudaStream_t stream);
 /* One cooperative launch per rank: reduce-scatter of the fp32 gradients (peer loads) ->
  * global-norm clip -> AdamW on the rank's fp32 master slice [lo, lo+n) -> bf16 parameters
  * stored into every rank's buffer -> this rank's gradient buffer zeroed. */

@@ -1,0 +1,93 @@
+"""Fused compute+collective kernels against their NCCL compositions, with roofline fractions:
+``torchrun --nproc-per-node N -m ceo_b200.parallel.comm_bench``.
+
+For each op the target time is the slower of FLOPs / measured GEMM peak and bytes that must
+cross NVLink / 770 GB/s (the measured per-direction peer-copy rate; nominal 900); the table
+reports achieved / target for the fused kernel and the time of the NCCL composition.  Timed
+with CUDA events after warm-up, max over ranks, an L2 flush before every timed launch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from ..utils.kernel_bench import peaks
+from .comm import Comm, init_distributed
+from .fused import FusedComm
+from .tp import TPContext
+
+NVLINK_BPS = 770e9
+
+
+def timed(fn, comm, iters=8, warmup=3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        comm.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(comm.max_over_ranks(e0.elapsed_time(e1)))
+    return statistics.median(ts)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--d-model", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--json", default="")
+    a = ap.parse_args(argv)
+    rank, world, local = init_distributed()
+    torch.cuda.set_device(local)
+    fc = FusedComm()
+    _, flops_peak, kind = peaks()
+    M, D = a.tokens, a.d_model
+    rows = M // world
+    out = []
+
+    def rec(name, fused_ms, nccl_ms, flops, link_bytes):
+        target = max(flops / flops_peak, link_bytes / NVLINK_BPS) * 1e3
+        r = {"op": name, "world": world, "fused_ms": round(fused_ms, 4),
+             "nccl_ms": round(nccl_ms, 4), "speedup_vs_nccl": round(nccl_ms / fused_ms, 3),
+             "roofline_ms": round(target, 4),
+             f"frac_of_roofline_{kind}": round(target / fused_ms, 3)}
+        out.append(r)
+        if rank == 0:
+            print(json.dumps(r), flush=True)
+
+    ncol = max(3 * D // world, 256)
+    ffn_loc = (a.ffn // world + 255) // 256 * 256
+    tp = TPContext(fc, M, max(D, ncol, ffn_loc, 2 * ffn_loc), copy_ctas=8)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    xs = torch.randn(rows, D, device="cuda", generator=g).bfloat16()
+    for name, n_loc in (("ag_gemm qkv", ncol), ("ag_gemm gate_up", 2 * ffn_loc)):
+        w = (torch.randn(n_loc, D, device="cuda", generator=g) * 0.02).bfloat16()
+        f = timed(lambda: tp.ag_gemm(xs, w), fc)
+        n = timed(lambda: tp.ag_gemm_nccl(xs, w), fc)
+        rec(f"{name} {M}x{n_loc}x{D}", f, n, 2.0 * M * n_loc * D,
+            (world - 1) / world * M * D * 2)
+    for name, k_loc in (("gemm_rs out", max(D // world, 256)), ("gemm_rs down", ffn_loc)):
+        x = torch.randn(M, k_loc, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(D, k_loc, device="cuda", generator=g) * 0.02).bfloat16()
+        f = timed(lambda: tp.gemm_rs(x, w), fc)
+        n = timed(lambda: tp.gemm_rs_nccl(x, w), fc)
+        rec(f"{name} {M}x{D}x{k_loc}", f, n, 2.0 * M * D * k_loc, (world - 1) / world * M * D * 2)
+    tp.close()
+    fc.close()
+    if a.json and rank == 0:
+        open(a.json, "w").write(json.dumps(out, indent=1))
+    Comm().barrier()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,156 @@
+"""Context parallelism for EFLA: the sequence is split over the ranks of a group and the
+recurrent state crosses rank boundaries as an affine map.
+
+Over one rank's span the delta-rule recurrence is ``S_out = P_r S_in + R_r`` with
+``P_r = prod_c (I - K_c^T W_c)`` (so is its adjoint: ``dS_in = P_r^T dS_out + Q_r``).  Forward:
+
+  A. every rank, in parallel: W, U of its chunks; R_r (state pass from zero) and P_r (state
+     pass on the identity with U = 0);
+  X. ``ceo_cp_exchange``: each rank stores (P_r, R_r) into every peer's gather buffer over
+     NVLink and joins a flag barrier, in one kernel; every rank then folds the maps of the
+     ranks before it into its true incoming state (G-1 tiny fp32 matmuls per head);
+  B. the real state pass from that state, and the output kernel.
+
+Backward mirrors it with Q_r and the transposed maps, folding from the last rank down.
+The reference has only the flag ``use_ring_attention`` and an additive "chunked scan" stub
+(src/tensor/sharding.zig:229, kernels/cuda/efla.cu:711-748, src/model/efla.zig:473-484).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _lib, efla as efla_ops
+from .symm import SymmetricBuffer
+
+_IDX = {"q": 0, "k": 1, "v": 2, "alpha": 3, "w": 4, "u": 5, "up": 6, "states": 7, "o": 8,
+        "s0": 9, "s_final": 10, "dO": 11, "dloc": 12, "dup": 13, "dstates": 14, "ds_final": 15,
+        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20}
+
+
+def _stage(stage: int, tensors: dict, strides, B, T, H, d):
+    ptrs = (ctypes.c_void_p * 21)()
+    for k, t in tensors.items():
+        ptrs[_IDX[k]] = None if t is None else t.data_ptr()
+    st = (ctypes.c_longlong * 6)(*strides)
+    _lib.check(_lib.lib().ceo_efla_stage(stage, ptrs, st, B, T, H, d, _lib.stream()),
+               f"ceo_efla_stage({stage})")
+
+
+class CPContext:
+    """Exchange buffers of one context-parallel group for up to ``max_bh`` (batch x heads)
+    states of size d x d."""
+
+    def __init__(self, comm, max_bh: int, d: int):
+        self.comm, self.rank, self.world = comm, comm.rank, comm.world
+        self.d, self.max_bh = d, max_bh
+        self.slot_floats = 2 * max_bh * d * d
+        self.gather = SymmetricBuffer(self.world * self.slot_floats * 4, comm.group)
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.done = torch.zeros(1, dtype=torch.int32, device=self.dev)
+
+    def exchange(self, block: torch.Tensor) -> torch.Tensor:
+        """block: fp32 tensor (same numel on every rank).  Returns (world, *block.shape): slot s
+        = rank s's block."""
+        n = block.numel()
+        assert n % 4 == 0 and n <= self.slot_floats and block.dtype == torch.float32
+        block = block.contiguous()
+        # slots are n floats apart for this call; nobody may still be reading the previous one
+        self.comm.device_barrier()
+        L = _lib.lib()
+        _lib.check(L.ceo_cp_exchange(block.data_ptr(), self.gather.table(),
+                                     self.comm.ctrl.table(), n, self.rank, self.world,
+                                     self.comm._next_epoch(), self.done.data_ptr(),
+                                     _lib.status_word(self.dev).data_ptr(), _lib.stream()),
+                   "ceo_cp_exchange")
+        return self.gather.view(torch.float32, self.world * n).view(self.world, *block.shape).clone()
+
+    def close(self):
+        self.gather.close()
+
+
+class _CPDeltaRule(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, alpha, cp):
+        B, T, H, d = k.shape
+        n = T // efla_ops.CHUNK
+        dev = k.device
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        alpha = alpha.contiguous().float()
+        hd = H * d
+        strides = (hd, hd, hd, hd, hd, hd)
+        new = lambda: torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        w, u, up, o = new(), new(), new(), new()
+        states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        R = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        P = torch.empty_like(R)
+        base = {"q": q, "k": k, "v": v, "alpha": alpha, "w": w, "u": u, "up": up,
+                "states": states, "o": o}
+        _stage(0, base, strides, B, T, H, d)
+        # R_r: state pass from zero;  P_r: the homogeneous pass on the identity (U = 0)
+        _stage(1, dict(base, s0=None, s_final=R), strides, B, T, H, d)
+        eye = torch.eye(d, device=dev, dtype=torch.float32).expand(B, H, d, d).contiguous()
+        zero_u = torch.zeros_like(u)
+        _stage(1, dict(base, u=zero_u, s0=eye, s_final=P), strides, B, T, H, d)
+        allmaps = cp.exchange(torch.stack([P, R]))          # (G, 2, B, H, d, d)
+        s_in = torch.zeros_like(R)
+        for j in range(cp.rank):                            # fold the maps of earlier ranks
+            s_in = torch.matmul(allmaps[j, 0], s_in) + allmaps[j, 1]
+        s_out = torch.empty_like(R)
+        _stage(1, dict(base, s0=s_in, s_final=s_out), strides, B, T, H, d)
+        _stage(2, base, strides, B, T, H, d)
+        ctx.save_for_backward(q, k, v, alpha, w, up, states, allmaps[:, 0].contiguous())
+        ctx.cp = cp
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, alpha, w, up, states, Pall = ctx.saved_tensors
+        cp = ctx.cp
+        B, T, H, d = k.shape
+        n = T // efla_ops.CHUNK
+        dev = k.device
+        hd = H * d
+        strides = (hd, hd, hd, hd, hd, hd)
+        do = do.contiguous()
+        new = lambda: torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        dq, dk, dv, dloc, dup = new(), new(), new(), new(), new()
+        dstates = torch.empty_like(states)
+        dalpha = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        Q = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        base = {"q": q, "k": k, "v": v, "alpha": alpha, "w": w, "up": up, "states": states,
+                "dO": do, "dloc": dloc, "dup": dup, "dstates": dstates, "dq": dq, "dk": dk,
+                "dv": dv, "dalpha": dalpha}
+        _stage(3, base, strides, B, T, H, d)
+        _stage(4, dict(base, ds_final=None, ds0=Q), strides, B, T, H, d)   # Q_r
+        allq = cp.exchange(Q)                                              # (G, B, H, d, d)
+        ds_out = torch.zeros_like(Q)
+        for j in range(cp.world - 1, cp.rank, -1):                          # fold from the end
+            ds_out = torch.matmul(Pall[j].transpose(-1, -2), ds_out) + allq[j]
+        ds0 = torch.empty_like(Q)
+        _stage(4, dict(base, ds_final=ds_out, ds0=ds0), strides, B, T, H, d)
+        _stage(5, base, strides, B, T, H, d)
+        return dq, dk, dv, dalpha, None
+
+
+def cp_delta_rule(q, k, v, alpha, cp: CPContext):
+    """Delta-rule attention over a sequence split across ``cp``'s ranks (rank r holds the r-th
+    contiguous span).  q, k, v: (B, T_local, H, d) bf16; alpha: (B, T_local, H)."""
+    return _CPDeltaRule.apply(q, k, v, alpha, cp)
+
+
+def efla_flops(B, T, H, d, backward: bool = True) -> float:
+    """Matmul FLOPs of the chunked kernels per call (forward, plus backward when asked)."""
+    C = efla_ops.CHUNK
+    per_chunk_fwd = 2 * (C * C * d            # K K^T
+                         + 2 * C * C * d      # W, U
+                         + 2 * C * d * d      # W S, K^T U'
+                         + C * C * d          # Q K^T
+                         + C * d * d          # Q S
+                         + C * C * d)         # P U'
+    per_chunk_bwd = 2 * (4 * C * C * d + 4 * C * d * d + 5 * C * C * d   # final
+                         + 2 * C * C * d + C * d * d + 2 * C * C * d     # local
+                         + 3 * C * d * d)                                # state bwd
+    chunks = B * H * (T // C)
+    return chunks * (per_chunk_fwd + (per_chunk_bwd if backward else 0))

@@ -113,6 +113,39 @@ def main():
         fc.close()
         if rank == 0:
             print("OK tp_fused", e1, e2)
+    elif what == "cp":
+        from ceo_b200.ops import efla, reference as ref
+        from ceo_b200.parallel.cp import CPContext, cp_delta_rule
+        from ceo_b200.parallel.fused import FusedComm
+        fc = FusedComm()
+        B, Tl, H, d = 2, 128, 2, 128
+        T = Tl * world
+        cp = CPContext(fc, B * H, d)
+        g = torch.Generator(device="cuda").manual_seed(3)     # same on all ranks: full tensors
+        q = torch.randn(B, T, H, d, device="cuda", generator=g)
+        k = torch.randn(B, T, H, d, device="cuda", generator=g)
+        q = (q / q.norm(dim=-1, keepdim=True)).bfloat16()
+        k = (k / k.norm(dim=-1, keepdim=True)).bfloat16()
+        v = torch.randn(B, T, H, d, device="cuda", generator=g).bfloat16()
+        alpha = -torch.expm1(-torch.sigmoid(torch.randn(B, T, H, device="cuda", generator=g)))
+        do = torch.randn(B, T, H, d, device="cuda", generator=g).bfloat16()
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        for rep in range(2):
+            loc = [t[:, sl].detach().clone().requires_grad_() for t in (q, k, v, alpha)]
+            o = cp_delta_rule(*loc, cp)
+            (o.float() * do[:, sl].float()).sum().backward()
+            full = [t.detach().clone().requires_grad_() for t in (q, k, v, alpha)]
+            of, _ = efla.delta_rule(*full)
+            (of.float() * do.float()).sum().backward()
+            rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
+            errs = [rel(o, of[:, sl])] + [rel(a.grad, b.grad[:, sl]) for a, b in zip(loc, full)]
+            assert max(errs) < 2e-2, errs
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        cp.close()
+        fc.close()
+        if rank == 0:
+            print("OK cp", errs)
     else:
         raise SystemExit(f"unknown test {what}")
     Comm().barrier()

@@ -45,3 +45,10 @@ def test_fused_ag_gemm_and_gemm_rs():
     n = 4 if _ngpu() >= 4 else 2
     out = _run("tp_fused", n)
     assert "OK tp_fused" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_context_parallel_efla_matches_single_gpu():
+    n = 4 if _ngpu() >= 4 else 2
+    out = _run("cp", n)
+    assert "OK cp" in out
