@@ -32,7 +32,10 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int PANEL_BYTES = 64 * BK * 2;  // one 64-wide MN-major panel, 8 KB
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_ROW_BYTES = 144;  // 64 bf16 + 16 B pad: conflict-free 16-byte accesses
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
+                          4 * EPI_WARP_BYTES /*reduce-scatter store staging*/;
 constexpr uint32_t TMEM_COLS = 512;
 
 struct GemmParams {
@@ -50,6 +53,7 @@ struct GemmParams {
   int* status;
   // ---- collectives fused into the kernel (all zero for a plain GEMM) --------------------
   int m_rot, n_rot;        // tile traversal starts at this m / n block (local data first)
+  int grp_m;               // row blocks per traversal group (see tile_coords)
   // all-gather of one operand: the first `ag_ctas` CTAs pull the peers' row-shards into
   // the local gathered buffer (which the tensor map reads) and publish one flag per block
   // of BM (A) or BN (B) rows; the TMA producer waits for a block's flag before loading it.
@@ -77,6 +81,18 @@ struct GemmParams {
 
 enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4, ST_AG_WAIT = 5,
              ST_RS_WAIT = 6, ST_COPY = 7 };
+
+// Tile r of a batch -> (m block, n block).  m runs fastest inside a group of `grp_m` row
+// blocks and a group is finished (all n blocks) before the next one starts; groups and n
+// blocks are visited starting at m_rot / n_rot.  With grp_m = num_m this is plain m-fastest
+// order; with grp_m = row blocks per rank the kernel works through one rank's rows at a time
+// (local rows first for an all-gathered A, the other ranks' rows first for a reduce-scatter).
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int r, int& m_blk, int& n_blk) {
+  const int per_group = p.grp_m * p.num_n;
+  const int g = r / per_group, rem = r - g * per_group;
+  m_blk = (g * p.grp_m + rem % p.grp_m + p.m_rot) % p.num_m;
+  n_blk = (rem / p.grp_m + p.n_rot) % p.num_n;
+}
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -135,8 +151,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
-        const int m0 = ((r % p.num_m + p.m_rot) % p.num_m) * BM;
-        const int n0 = ((r / p.num_m + p.n_rot) % p.num_n) * BN;
+        int mb_, nb_;
+        tile_coords(p, r, mb_, nb_);
+        const int m0 = mb_ * BM, n0 = nb_ * BN;
         if (p.ag_operand) {
           // rows pulled from a peer become loadable once the copy CTAs have published them
           const int row0 = p.ag_operand == 1 ? m0 : n0;
@@ -301,8 +318,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t acc_ph = (it >> 1) & 1;
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
-      const int m0 = ((r % p.num_m + p.m_rot) % p.num_m) * BM;
-      const int n0 = ((r / p.num_m + p.n_rot) % p.num_n) * BN;
+      int mb_, nb_;
+      tile_coords(p, r, mb_, nb_);
+      const int m0 = mb_ * BM, n0 = nb_ * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_ph)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE);
         ok = false;
@@ -326,6 +344,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) +
                            static_cast<long long>(b) * p.batch_stride_r + row * p.ldr
                      : nullptr;
+      if (p.rs_on) {
+        // Peer stores want whole 128-byte lines: transpose 64 columns at a time through a
+        // per-warp shared-memory tile so that 8 lanes write one row's 128 contiguous bytes.
+        uint8_t* sb = smem + STAGES * STAGE_BYTES + 256 + quad * EPI_WARP_BYTES;
+        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(cbase) +
+                               (coff - static_cast<long long>(lane) * p.ldc);  // row of lane 0
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c2 * 64 + hc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                oh[j] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * j]) * p.alpha,
+                                              __uint_as_float(v[q4 * 8 + 2 * j + 1]) * p.alpha);
+              *reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16) = o;
+            }
+          }
+          __syncwarp();
+          const int ncol = n0 + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            if (m0 + quad * 32 + rl < p.M && ncol < p.N)
+              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol) = o;
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -415,7 +469,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (p.rs_on) {
-        __threadfence_system();
+        // the warp barrier orders every lane's stores before lane 0's system-scope release
         __syncwarp();
         if (lane == 0)
           red_release_sys_add(p.rs_count[rs_owner] + p.rank * (p.rs_rows_per_rank / BM) +
@@ -442,39 +496,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         if (!ok) break;
         const int ncols = min(BN, p.N - nb * BN);
-        const int c = lane * 8;  // a warp covers one 256-column row segment per iteration
-        for (int rr = 0; rr < 32 && c < ncols; ++rr) {
-          const int row = lb * BM + quad * 32 + rr;  // row within this rank's slice
-          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int src = 0; src < p.world; ++src) {
-            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
-                stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row) * p.ldc +
-                nb * BN + c));
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const int c = lane * 8;  // a warp covers one 256-column row segment per row
+        constexpr int RU = 4;    // rows in flight per warp: all their loads are issued first
+        for (int rr = 0; rr < 32 && c < ncols; rr += RU) {
+          const int row0 = lb * BM + quad * 32 + rr;  // rows within this rank's slice
+          uint4 part[RU][8];
+          uint4 resv[RU];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 x = __bfloat1622float2(h[j]);
-              acc8[2 * j] += x.x;
-              acc8[2 * j + 1] += x.y;
-            }
+          for (int u = 0; u < RU; ++u) {
+#pragma unroll
+            for (int src = 0; src < 8; ++src)
+              if (src < p.world)
+                part[u][src] = __ldcg(reinterpret_cast<const uint4*>(
+                    stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row0 + u) * p.ldc +
+                    nb * BN + c));
+            if (p.rs_residual)
+              resv[u] = *reinterpret_cast<const uint4*>(
+                  reinterpret_cast<const __nv_bfloat16*>(p.rs_residual) + (row0 + u) * p.rs_ldo +
+                  nb * BN + c);
           }
-          if (p.rs_residual) {
-            const uint4 u = *reinterpret_cast<const uint4*>(
-                reinterpret_cast<const __nv_bfloat16*>(p.rs_residual) + row * p.rs_ldo + nb * BN + c);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 x = __bfloat1622float2(h[j]);
-              acc8[2 * j] += x.x;
-              acc8[2 * j + 1] += x.y;
+          for (int u = 0; u < RU; ++u) {
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int src = 0; src < 8; ++src)
+              if (src < p.world) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[u][src]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(h[j]);
+                  acc8[2 * j] += x.x;
+                  acc8[2 * j + 1] += x.y;
+                }
+              }
+            if (p.rs_residual) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&resv[u]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(h[j]);
+                acc8[2 * j] += x.x;
+                acc8[2 * j + 1] += x.y;
+              }
             }
-          }
-          uint4 o;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) + row * p.rs_ldo +
-                                    nb * BN + c) = o;
+            for (int j = 0; j < 4; ++j)
+              oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) +
+                                      (row0 + u) * p.rs_ldo + nb * BN + c) = o;
+          }
         }
       }
     }
@@ -617,6 +688,7 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   p.status = status;
   p.rank = fz.rank;
   p.world = fz.world;
+  p.grp_m = p.num_m;
   int cap = g_num_sms;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (fz.kind == 1 || fz.kind == 2) {
@@ -639,7 +711,7 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
     p.ag_flags = fz.flags;
     p.ag_target = fz.target;
     const int rot = fz.rank * (p.ag_rows_per_shard / blk);
-    if (fz.kind == 1) p.m_rot = rot; else p.n_rot = rot;
+    if (fz.kind == 1) { p.m_rot = rot; p.grp_m = p.ag_rows_per_shard / blk; } else p.n_rot = rot;
   } else if (fz.kind == 3) {
     if (batch != 1 || out_f32 || accumulate || bias || residual || M % fz.world ||
         (M / fz.world) % BM || (N & 7) || fz.world < 2 || fz.world > 8)
@@ -656,7 +728,10 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
     p.rs_ldo = fz.rs_ldo;
     p.ldc = N;  // staging rows are dense
     // other ranks' rows first, this rank's own rows last
+    // plain m-fastest order interleaves the owners, which spreads the peer stores evenly over
+    // the kernel instead of saturating NVLink during the first (world-1)/world of it
     p.m_rot = ((fz.rank + 1) % fz.world) * (p.rs_rows_per_rank / BM);
+    p.grp_m = p.num_m;
   }
   long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
   int grid = static_cast<int>(total + p.ag_ctas < cap ? total + p.ag_ctas : cap);

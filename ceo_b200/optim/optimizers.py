@@ -109,6 +109,11 @@ class ShardedOptimizer:
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._side_state = {}
         self._muon_state = {}
+        # Tensor parallelism: the squared norm is also summed over `extra_norm_group`, and the
+        # parameters every rank of that group holds in full (`replicated_names`) count once.
+        self.extra_norm_group = None
+        self.replicated_names: set = set()
+        self.use_fused_step = True
         self.uses_matrices = kind in ("muon", "lion_muon")
         if self.uses_matrices:
             self._matrix_segs = [s for s in flat.segments if len(s.shape) == 2 and s.decay]
@@ -150,6 +155,23 @@ class ShardedOptimizer:
                 self.comm.all_reduce(self._sumsq)
             for g in side:
                 self._sumsq += g.float().pow(2).sum()
+            if self.extra_norm_group is not None:
+                import torch.distributed as dist
+                tpw = dist.get_world_size(self.extra_norm_group)
+                f = self.flat
+                rep = torch.zeros_like(self._sumsq)
+                for seg in f.segments:
+                    if seg.name in self.replicated_names:
+                        a = max(seg.offset, f.lo) - f.lo
+                        b = min(seg.offset + seg.numel, f.hi) - f.lo
+                        if b > a:
+                            rep += gshard[a:b].float().pow(2).sum()
+                if self._world() > 1:
+                    self.comm.all_reduce(rep)
+                for g in side:
+                    rep += g.float().pow(2).sum()
+                self._sumsq -= rep * (1.0 - 1.0 / tpw)
+                dist.all_reduce(self._sumsq, group=self.extra_norm_group)
             self._sumsq *= gscale * gscale
             _lib.check(L.ceo_clip_scale(self._sumsq.data_ptr(), float(self.max_norm),
                                         self._scale.data_ptr(), self._norm.data_ptr(),
@@ -280,7 +302,8 @@ class ShardedOptimizer:
         gradient norm as a device scalar (no host synchronisation)."""
         f = self.flat
         self.step_count += 1
-        if (self.kind == "adamw" and self._world() > 1 and getattr(self.comm, "fused", False)
+        if (self.use_fused_step and self.kind == "adamw" and self._world() > 1
+                and getattr(self.comm, "fused", False)
                 and f.grads_symm is not None and f.param_dtype == torch.bfloat16
                 and f.grads.dtype == torch.float32):
             # one kernel: reduce-scatter + clip + AdamW + all-gather + zero-grad over NVLink

@@ -70,18 +70,32 @@ def main(argv=None):
     tp = TPContext(fc, M, max(D, ncol, ffn_loc, 2 * ffn_loc), copy_ctas=8)
     g = torch.Generator(device="cuda").manual_seed(rank)
     xs = torch.randn(rows, D, device="cuda", generator=g).bfloat16()
+    from ..ops.matmul import gemm as plain_gemm
+    t_bar = timed(lambda: fc.device_barrier(), fc)
+    if rank == 0:
+        print(json.dumps({"op": "device barrier (flag kernel)", "world": world,
+                          "ms": round(t_bar, 4)}), flush=True)
     for name, n_loc in (("ag_gemm qkv", ncol), ("ag_gemm gate_up", 2 * ffn_loc)):
         w = (torch.randn(n_loc, D, device="cuda", generator=g) * 0.02).bfloat16()
         f = timed(lambda: tp.ag_gemm(xs, w), fc)
         n = timed(lambda: tp.ag_gemm_nccl(xs, w), fc)
+        xf = torch.randn(M, D, device="cuda", generator=g).bfloat16()
+        loc = timed(lambda: plain_gemm(xf, w), fc)
         rec(f"{name} {M}x{n_loc}x{D}", f, n, 2.0 * M * n_loc * D,
             (world - 1) / world * M * D * 2)
+        out[-1]["local_gemm_ms"] = round(loc, 4)
+        if rank == 0:
+            print(json.dumps({"local_gemm_ms": round(loc, 4)}), flush=True)
     for name, k_loc in (("gemm_rs out", max(D // world, 256)), ("gemm_rs down", ffn_loc)):
         x = torch.randn(M, k_loc, device="cuda", generator=g).bfloat16()
         w = (torch.randn(D, k_loc, device="cuda", generator=g) * 0.02).bfloat16()
         f = timed(lambda: tp.gemm_rs(x, w), fc)
         n = timed(lambda: tp.gemm_rs_nccl(x, w), fc)
+        loc = timed(lambda: plain_gemm(x, w), fc)
         rec(f"{name} {M}x{D}x{k_loc}", f, n, 2.0 * M * D * k_loc, (world - 1) / world * M * D * 2)
+        out[-1]["local_gemm_ms"] = round(loc, 4)
+        if rank == 0:
+            print(json.dumps({"local_gemm_ms": round(loc, 4)}), flush=True)
     tp.close()
     fc.close()
     if a.json and rank == 0:

@@ -72,7 +72,8 @@ class TrainEngine:
             loss.backward()
             total += loss.detach().float()
             self.tokens_seen += tok.numel() * self.world
-        gnorm = self.optimizer.step(lr, grad_scale=1.0 / n)
+        # mean over micro-batches and data-parallel ranks (the collectives sum)
+        gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.world))
         self.scheduler.step()
         self.step_count += 1
         mean = total / n

@@ -146,6 +146,32 @@ def main():
         fc.close()
         if rank == 0:
             print("OK cp", errs)
+    elif what in ("tp_model", "cp_model"):
+        from ceo_b200.runtime.parallel_engine import ParallelEngine
+        cfg = small_cfg(world)
+        cfg.model.num_heads = 4
+        cfg.model.head_dim = 128
+        cfg.data.seq_len = 256
+        cfg.training.micro_batch_size = 2
+        cfg.runtime.tensor_parallel_size = world if what == "tp_model" else 1
+        cfg.runtime.context_parallel_size = world if what == "cp_model" else 1
+        data = SyntheticTokens(cfg.model.vocab_size, "zipf", 1.1, 0, 0)   # same data on all ranks
+        batches = [data.batch(2, 256) for _ in range(3)]
+        par = ParallelEngine(cfg, torch.device("cuda", torch.cuda.current_device()))
+        lp = [tuple(float(x) for x in par.train_step([b], lr=1e-3)) for b in batches]
+        cfg1 = small_cfg(1)
+        cfg1.model.num_heads, cfg1.model.head_dim = 4, 128
+        single = TrainEngine(cfg1, torch.device("cuda", torch.cuda.current_device()), None, seed=0)
+        ls = [tuple(float(x) for x in single.train_step([(t.cuda(), g.cuda())], lr=1e-3))
+              for t, g in batches]
+        for (a, ga), (b, gb) in zip(lp, ls):
+            assert abs(a - b) < 3e-2 * abs(b), (lp, ls)
+            assert abs(ga - gb) < 6e-2 * abs(gb), (lp, ls)
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        par.close()
+        if rank == 0:
+            print(f"OK {what}", lp, ls)
     else:
         raise SystemExit(f"unknown test {what}")
     Comm().barrier()

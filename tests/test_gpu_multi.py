@@ -52,3 +52,10 @@ def test_context_parallel_efla_matches_single_gpu():
     n = 4 if _ngpu() >= 4 else 2
     out = _run("cp", n)
     assert "OK cp" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("what", ["tp_model", "cp_model"])
+def test_parallel_model_matches_single_gpu(what):
+    out = _run(what, 2)
+    assert f"OK {what}" in out
