@@ -64,39 +64,43 @@ class EflaLayer(nn.Module):
         self.normalize = e.normalize_qk
         self.per_token_beta = e.per_token_beta
         hd = self.H * self.d
-        self.w_qkv = _param((self.P * hd, self.D), std, device, dtype, gen)
+        self.hd = hd
+        w_qkv = _param((self.P * hd, self.D), std, device, dtype, gen).data
         self.w_o = _param((self.D, hd), std, device, dtype, gen)
         if self.per_token_beta:
-            self.w_beta = _param((self.H, self.D), std, device, dtype, gen)
+            # the beta logits ride in the same projection: rows [q | k | v | beta (H) | zero pad]
+            w_beta = _param((self.H, self.D), std, device, dtype, gen).data
+            pad = (-self.H) % 8
+            w_qkv = torch.cat([w_qkv, w_beta, torch.zeros(pad, self.D, device=device, dtype=dtype)])
             self.beta_param = None
         else:
-            self.w_beta = None
             self.beta_param = nn.Parameter(torch.full((1,), float(e.initial_beta), device=device,
                                                       dtype=torch.float32),
                                            requires_grad=e.learned_beta)
+        self.w_qkv = nn.Parameter(w_qkv)
 
     def forward(self, x_norm, residual, state=None):
         B, T, _ = x_norm.shape
-        qkv = linear(x_norm, self.w_qkv).view(B, T, self.P, self.H, self.d)
-        if self.per_token_beta:
-            beta = torch.sigmoid(linear(x_norm, self.w_beta).float())
-        else:
-            beta = self.beta_param
-        pad = (-T) % efla_ops.CHUNK
-        if pad and qkv.is_cuda:
+        if (-T) % efla_ops.CHUNK and x_norm.is_cuda:
             raise ValueError(f"sequence length {T} must be a multiple of {efla_ops.CHUNK} on GPU")
-        o, s_final = efla_ops.efla_qkv(qkv, beta, self.normalize, state)
+        proj = linear(x_norm, self.w_qkv)
+        if self.per_token_beta:
+            o, s_final = efla_ops.efla_proj(proj, self.P, self.H, self.d, self.normalize, state)
+        else:
+            o, s_final = efla_ops.efla_qkv(proj.view(B, T, self.P, self.H, self.d),
+                                           self.beta_param, self.normalize, state)
         return o.reshape(B, T, self.H * self.d), s_final
 
     def decode_step(self, x_norm, state):
         """One token (B, D) with carried state (B,H,d,d) fp32; returns the (B, H*d) output."""
         B = x_norm.shape[0]
-        qkv = linear(x_norm, self.w_qkv).view(B, self.P, self.H, self.d)
+        proj = linear(x_norm, self.w_qkv)
+        qkv = proj[:, :self.P * self.hd].reshape(B, self.P, self.H, self.d)
         q = qkv[:, 0]
         k = qkv[:, 1] if self.P == 3 else qkv[:, 0]
         v = qkv[:, self.P - 1]
         if self.per_token_beta:
-            beta = torch.sigmoid(linear(x_norm, self.w_beta).float())
+            beta = torch.sigmoid(proj[:, self.P * self.hd:self.P * self.hd + self.H].float())
         else:
             beta = self.beta_param.expand(B, self.H)
         if self.normalize:
@@ -229,13 +233,14 @@ class EflaLM(nn.Module):
             out[p + "ln1.weight"] = b.ln1.weight.detach()
             if b.ln1.bias is not None:
                 out[p + "ln1.bias"] = b.ln1.bias.detach()
-            parts = b.efla.w_qkv.detach().split(hd, dim=0)
             names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
+            parts = b.efla.w_qkv.detach()[:len(names) * hd].split(hd, dim=0)
             for nme, w in zip(names, parts):
                 out[p + "efla." + nme] = w.t().contiguous()
             out[p + "efla.w_o"] = b.efla.w_o.detach().t().contiguous()
-            if b.efla.w_beta is not None:
-                out[p + "efla.w_beta"] = b.efla.w_beta.detach().t().contiguous()
+            if b.efla.per_token_beta:
+                nb = len(names) * hd
+                out[p + "efla.w_beta"] = b.efla.w_qkv.detach()[nb:nb + b.efla.H].t().contiguous()
             else:
                 out[p + "efla.beta_param"] = b.efla.beta_param.detach()
             if b.prism is not None:
@@ -274,8 +279,9 @@ class EflaLM(nn.Module):
             for j, nme in enumerate(names):
                 put(b.efla.w_qkv[j * hd:(j + 1) * hd], tensors[p + "efla." + nme].t())
             put(b.efla.w_o, tensors[p + "efla.w_o"].t())
-            if b.efla.w_beta is not None:
-                put(b.efla.w_beta, tensors[p + "efla.w_beta"].t())
+            if b.efla.per_token_beta:
+                nb = len(names) * hd
+                put(b.efla.w_qkv[nb:nb + b.efla.H], tensors[p + "efla.w_beta"].t())
             else:
                 put(b.efla.beta_param, tensors[p + "efla.beta_param"].reshape(1))
             if b.prism is not None:

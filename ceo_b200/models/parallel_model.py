@@ -67,28 +67,35 @@ class ParallelBlock(nn.Module):
         # draw the full tensors in EflaLM's order, keep this rank's slice
         w_qkv = _full((self.P * H * d, D), std, device, gen)
         w_o = _full((D, H * d), std, device, gen)
-        self.w_qkv = nn.Parameter(_shard_rows(w_qkv, self.P, tp_rank, tp_world).to(dt))
+        w_loc = _shard_rows(w_qkv, self.P, tp_rank, tp_world)
         self.w_o = nn.Parameter(w_o.chunk(tp_world, dim=1)[tp_rank].contiguous().to(dt))
         if self.per_token_beta:
-            w_beta = _full((H, D), std, device, gen)
-            self.w_beta = nn.Parameter(w_beta.chunk(tp_world, dim=0)[tp_rank].contiguous().to(dt))
+            w_beta = _full((H, D), std, device, gen).chunk(tp_world, dim=0)[tp_rank]
+            pad = (-self.H_loc) % 8
+            w_loc = torch.cat([w_loc, w_beta, torch.zeros(pad, D, device=device)])
             self.beta_param = None
         else:
-            self.w_beta = None
             self.beta_param = nn.Parameter(torch.full((1,), float(e.initial_beta), device=device),
                                            requires_grad=e.learned_beta)
             self.beta_param.replicated = True
+        self.w_qkv = nn.Parameter(w_loc.to(dt).contiguous())
         parts = 2 if self.act == "swiglu" else 1
         w_up = _full((parts * F, D), std, device, gen)
         w_down = _full((D, F), std, device, gen)
         self.w_up = nn.Parameter(_shard_rows(w_up, parts, tp_rank, tp_world).to(dt))
         self.w_down = nn.Parameter(w_down.chunk(tp_world, dim=1)[tp_rank].contiguous().to(dt))
 
-    def _attention(self, qkv, beta, B, T, cp):
-        qkv = qkv.view(B, T, self.P, self.H_loc, self.d)
+    def _attention(self, proj, B, T, cp):
+        hd = self.H_loc * self.d
+        proj = proj.view(B, T, -1)
         if cp is None:
-            o, _ = efla_ops.efla_qkv(qkv, beta, self.normalize)
-            return o
+            if self.per_token_beta:
+                return efla_ops.efla_proj(proj, self.P, self.H_loc, self.d, self.normalize)[0]
+            return efla_ops.efla_qkv(proj.view(B, T, self.P, self.H_loc, self.d), self.beta_param,
+                                     self.normalize)[0]
+        qkv = proj[..., :self.P * hd].reshape(B, T, self.P, self.H_loc, self.d)
+        beta = torch.sigmoid(proj[..., self.P * hd:self.P * hd + self.H_loc].float()) \
+            if self.per_token_beta else self.beta_param
         q = qkv[:, :, 0]
         k = qkv[:, :, 1] if self.P == 3 else qkv[:, :, 0]
         v = qkv[:, :, self.P - 1]
@@ -103,15 +110,9 @@ class ParallelBlock(nn.Module):
     def forward(self, h, B, T, tp=None, cp=None, impl="fused"):
         """h: (rows, D) - all B*T local tokens without tp, this rank's row shard with tp."""
         n1 = self.ln1(h)
-        if tp is not None:
-            qkv = column_parallel_linear(n1, self.w_qkv, tp, impl)
-            beta = torch.sigmoid(column_parallel_linear(n1, self.w_beta, tp, impl).float()) \
-                .view(B, T, self.H_loc) if self.per_token_beta else self.beta_param
-        else:
-            qkv = linear(n1, self.w_qkv)
-            beta = torch.sigmoid(linear(n1, self.w_beta).float()).view(B, T, self.H_loc) \
-                if self.per_token_beta else self.beta_param
-        o = self._attention(qkv, beta, B, T, cp).reshape(B * T, self.H_loc * self.d)
+        proj = column_parallel_linear(n1, self.w_qkv, tp, impl) if tp is not None \
+            else linear(n1, self.w_qkv)
+        o = self._attention(proj, B, T, cp).reshape(B * T, self.H_loc * self.d)
         if tp is not None:
             h = row_parallel_linear(o, self.w_o, tp, residual=h, impl=impl)
             u = column_parallel_linear(self.ln2(h), self.w_up, tp, impl)

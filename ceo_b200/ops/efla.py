@@ -232,3 +232,107 @@ def delta_rule_decode_step(q, k, v, alpha, state):
     u = torch.einsum("bhkv,bhk->bhv", state, kf)
     state.add_(alpha.float()[..., None, None] * torch.einsum("bhk,bhv->bhkv", kf, vf - u))
     return torch.einsum("bhkv,bhk->bhv", state, qf).to(q.dtype)
+
+
+class _EflaProjFn(torch.autograd.Function):
+    """EFLA attention straight off ONE projection output ``proj`` (B, T, N) whose columns are
+    ``[q (H*d) | k (H*d) | v (H*d) | beta logits (H) | padding]`` (no q block when P = 2).
+    The per-token beta = sigmoid(logit) is taken from the same buffer, and backward fills one
+    (B, T, N) gradient buffer in place - q/k/v slices by the kernels, the logit columns from
+    d(beta) - so the projection's gradient GEMMs read it without any concatenation."""
+
+    @staticmethod
+    def forward(ctx, proj, P, H, d, normalize, s0):
+        B, T, N = proj.shape
+        assert proj.is_contiguous() and N >= P * H * d + H and N % 8 == 0 and T % CHUNK == 0
+        dev = proj.device
+        n = T // CHUNK
+        hd = H * d
+        esz = proj.element_size()
+        base = proj.data_ptr()
+        q_ptr, k_ptr = base, base + (hd * esz if P == 3 else 0)
+        v_ptr = base + (P - 1) * hd * esz
+        beta = torch.sigmoid(proj[..., P * hd:P * hd + H].float()).contiguous()
+        L = _lib.lib()
+        qn = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        kn = torch.empty_like(qn) if P == 3 else qn
+        rq = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        rk = torch.empty_like(rq)
+        alpha = torch.empty_like(rq)
+        _lib.check(L.ceo_efla_prep_fwd(q_ptr, k_ptr, beta.data_ptr(), 0, qn.data_ptr(),
+                                       kn.data_ptr(), rq.data_ptr(), rk.data_ptr(),
+                                       alpha.data_ptr(), B * T, H, d, N, N, int(normalize),
+                                       _lib.stream()), "ceo_efla_prep_fwd")
+        w = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        up = torch.empty_like(w)
+        o = torch.empty_like(w)
+        states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        s_final = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        st = _lib.status_word(dev).data_ptr()
+        _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v_ptr, alpha.data_ptr(),
+                                  _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
+                                  o.data_ptr(), s_final.data_ptr(), B, T, H, d, hd, hd, N, st,
+                                  _lib.stream()), "ceo_efla_fwd")
+        ctx.save_for_backward(proj, beta, qn, kn, rq, rk, alpha, w, up, states)
+        ctx.cfg = (P, H, d, normalize, s0 is not None)
+        return o, s_final
+
+    @staticmethod
+    def backward(ctx, do, ds_final):
+        proj, beta, qn, kn, rq, rk, alpha, w, up, states = ctx.saved_tensors
+        P, H, d, normalize, has_s0 = ctx.cfg
+        B, T, N = proj.shape
+        dev = proj.device
+        hd = H * d
+        esz = proj.element_size()
+        do = do.contiguous()
+        dproj = torch.empty_like(proj)
+        dqn = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
+        dkn = torch.empty_like(dqn)
+        dalpha = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        dloc = torch.empty_like(dqn)
+        dup = torch.empty_like(dqn)
+        dstates = torch.empty_like(states)
+        ds0 = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
+        if ds_final is not None:
+            ds_final = ds_final.contiguous().float()
+        base, dbase = proj.data_ptr(), dproj.data_ptr()
+        v_ptr, dv_ptr = base + (P - 1) * hd * esz, dbase + (P - 1) * hd * esz
+        L = _lib.lib()
+        st = _lib.status_word(dev).data_ptr()
+        _lib.check(L.ceo_efla_bwd(qn.data_ptr(), kn.data_ptr(), v_ptr, alpha.data_ptr(),
+                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), do.data_ptr(),
+                                  _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
+                                  dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(), dv_ptr,
+                                  dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, hd, hd, N, hd, hd,
+                                  N, st, _lib.stream()), "ceo_efla_bwd")
+        dbeta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        if P == 3:
+            dq_ptr, dk_ptr, dq_stride = dbase, dbase + hd * esz, N
+        else:
+            dkn.add_(dqn)
+            dq_ptr, dk_ptr, dq_stride = dloc.data_ptr(), dbase, hd
+        _lib.check(L.ceo_efla_prep_bwd(dqn.data_ptr(), dkn.data_ptr(), qn.data_ptr(),
+                                       kn.data_ptr(), rq.data_ptr(), rk.data_ptr(),
+                                       beta.data_ptr(), 0, dalpha.data_ptr(), dq_ptr, dk_ptr,
+                                       dbeta.data_ptr(), B * T, H, d, dq_stride, N, int(normalize),
+                                       _lib.stream()), "ceo_efla_prep_bwd")
+        tail = dproj[..., P * hd:]
+        tail.zero_()
+        tail[..., :H].copy_(dbeta * beta * (1.0 - beta))
+        return dproj, None, None, None, None, (ds0 if has_s0 else None)
+
+
+def efla_proj(proj, P: int, H: int, d: int, normalize: bool = True, s0=None):
+    """EFLA attention on a fused projection output with the beta logits in it.
+    proj: (B, T, N), columns [q | k | v | H beta logits | pad] (P = 3) or [k | v | ...] (P = 2).
+    Returns (o (B,T,H,d), S_T)."""
+    if not proj.is_cuda:
+        B, T, N = proj.shape
+        hd = H * d
+        qkv = proj[..., :P * hd].reshape(B, T, P, H, d)
+        beta = torch.sigmoid(proj[..., P * hd:P * hd + H].float())
+        q = qkv[:, :, 0]
+        k = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
+        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0)
+    return _EflaProjFn.apply(proj, P, H, d, normalize, s0)

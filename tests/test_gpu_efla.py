@@ -121,3 +121,37 @@ def test_efla_qkv_fused(P, normalize, scalar_beta):
     assert _rel(o, o_r) < 2e-2
     assert _rel(a.grad, b.grad) < 4e-2, _rel(a.grad, b.grad)
     assert _rel(ba.grad, bb.grad) < 4e-2, _rel(ba.grad, bb.grad)
+
+
+@pytest.mark.parametrize("P,normalize", [(3, True), (2, False)])
+def test_efla_proj_with_beta_logits_in_projection(P, normalize):
+    B, T, H, d = 2, 128, 4, 64
+    g = torch.Generator(device=DEV).manual_seed(11)
+    N = P * H * d + 8
+    proj = (0.4 * torch.randn(B, T, N, device=DEV, generator=g)).to(torch.bfloat16)
+    if not normalize:
+        proj[..., :(P - 1) * H * d] *= 0.2
+    do = torch.randn(B, T, H, d, device=DEV, generator=g).to(torch.bfloat16)
+    a = proj.clone().requires_grad_()
+    o, _ = efla.efla_proj(a, P, H, d, normalize)
+    (o.float() * do.float()).sum().backward()
+    b = proj.float().requires_grad_()
+    o_r, _ = efla.efla_proj(b.cpu().to(DEV) if False else b, P, H, d, normalize) \
+        if False else (None, None)
+    hd = H * d
+    qkv = b[..., :P * hd].reshape(B, T, P, H, d)
+    beta = torch.sigmoid(b[..., P * hd:P * hd + H])
+    q = qkv[:, :, 0]
+    k = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
+    if normalize:
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        alpha = -torch.expm1(-beta)
+    else:
+        alpha = ref.efla_coefficient(beta, k.pow(2).sum(-1))
+    o_r, _ = ref.delta_rule_chunked(q, k, qkv[:, :, P - 1], alpha)
+    (o_r * do.float()).sum().backward()
+    assert _rel(o, o_r) < 2e-2
+    assert _rel(a.grad[..., :P * hd], b.grad[..., :P * hd]) < 4e-2
+    assert _rel(a.grad[..., P * hd:P * hd + H], b.grad[..., P * hd:P * hd + H]) < 5e-2
+    assert float(a.grad[..., P * hd + H:].abs().max()) == 0.0
