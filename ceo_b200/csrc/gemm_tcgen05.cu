@@ -90,8 +90,10 @@ enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4,
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int r, int& m_blk, int& n_blk) {
   const int per_group = p.grp_m * p.num_n;
   const int g = r / per_group, rem = r - g * per_group;
-  m_blk = (g * p.grp_m + rem % p.grp_m + p.m_rot) % p.num_m;
-  n_blk = (rem / p.grp_m + p.n_rot) % p.num_n;
+  const int left = p.num_m - g * p.grp_m;           // the last group may be narrower
+  const int gsz = left < p.grp_m ? left : p.grp_m;
+  m_blk = (g * p.grp_m + rem % gsz + p.m_rot) % p.num_m;
+  n_blk = (rem / gsz + p.n_rot) % p.num_n;
 }
 
 template <int A_MN, int B_MN>
@@ -688,7 +690,9 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   p.status = status;
   p.rank = fz.rank;
   p.world = fz.world;
-  p.grp_m = p.num_m;
+  // bands of 16 row blocks: a wave of 148 tiles is then ~16 x 9 tiles whose A and B panels
+  // both stay in L2 (m-fastest over all rows re-reads A once per ~2 n-blocks)
+  p.grp_m = p.num_m > 16 ? 16 : p.num_m;
   int cap = g_num_sms;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (fz.kind == 1 || fz.kind == 2) {

@@ -55,6 +55,11 @@ def main(argv=None):
     ap.add_argument("--ffn", type=int, default=5632)
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--torch", action="store_true")
+    ap.add_argument("--only", default="", help="run only the rows whose group name contains this")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--json", type=str, default="")
     a = ap.parse_args(argv)
     bw, fl, kind = peaks()
@@ -75,9 +80,15 @@ def main(argv=None):
         rows.append(r)
         print(json.dumps(r), flush=True)
 
+    global time_ms
+    _time = time_ms
+    time_ms = lambda fn, iters=a.iters, warmup=3: _time(fn, iters, warmup)  # noqa: E731
+    want = lambda group: (not a.only) or a.only in group  # noqa: E731
     x = torch.randn(M, D, device=dev).bfloat16()
     for name, n_out, k_in in (("qkv", 3 * D, D), ("gate_up", 2 * Fh, D), ("down", D, Fh),
                               ("out", D, D)):
+        if not want("gemm_" + name):
+            continue
         xin = x if k_in == D else torch.randn(M, k_in, device=dev).bfloat16()
         w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
         dy = torch.randn(M, n_out, device=dev).bfloat16()
@@ -93,12 +104,55 @@ def main(argv=None):
             time_ms(lambda: G.gemm(dy, xin, a_mn=True, b_mn=True, out=mg, accumulate=True)),
             fl_, 0, tb)
 
-    w = torch.ones(D, device=dev).bfloat16()
-    y, _ = N.rmsnorm(x, w)
-    rec("rmsnorm_fwd", time_ms(lambda: N.rmsnorm(x, w)), 0, 2.0 * M * D * 2,
-        time_ms(lambda: torch.nn.functional.rms_norm(x, (D,), w)) if a.torch else None)
-    gu = torch.randn(M, 2 * Fh, device=dev).bfloat16()
-    rec("swiglu_fwd", time_ms(lambda: N.swiglu(gu)), 0, 3.0 * M * Fh * 2)
+    if want("norm"):
+        w = torch.ones(D, device=dev).bfloat16().requires_grad_()
+        xr = x.clone().requires_grad_()
+        rec("rmsnorm_fwd", time_ms(lambda: N.rmsnorm(x, w)), 0, 2.0 * M * D * 2,
+            time_ms(lambda: torch.nn.functional.rms_norm(x, (D,), w)) if a.torch else None)
+        y, _ = N.rmsnorm(xr, w)
+        dy = torch.randn_like(y)
+        rec("rmsnorm_bwd", time_ms(lambda: torch.autograd.grad(y, (xr, w), dy, retain_graph=True)),
+            0, 3.0 * M * D * 2)
+    if want("swiglu"):
+        gu = torch.randn(M, 2 * Fh, device=dev).bfloat16().requires_grad_()
+        rec("swiglu_fwd", time_ms(lambda: N.swiglu(gu)), 0, 3.0 * M * Fh * 2)
+        o = N.swiglu(gu)
+        do = torch.randn_like(o)
+        rec("swiglu_bwd", time_ms(lambda: torch.autograd.grad(o, gu, do, retain_graph=True)), 0,
+            5.0 * M * Fh * 2)
+    if want("efla"):
+        from ..ops import efla as E
+        from ..parallel.cp import efla_flops
+        T, H, d = a.seq_len, a.heads, a.head_dim
+        B = max(1, M // T)
+        proj = (0.5 * torch.randn(B, T, 3 * H * d + 16, device=dev)).bfloat16().requires_grad_()
+        rec(f"efla_fwd B{B} T{T} H{H} d{d} (prep + 3 kernels)",
+            time_ms(lambda: E.efla_proj(proj, 3, H, d, True)), efla_flops(B, T, H, d, False))
+        o, _ = E.efla_proj(proj, 3, H, d, True)
+        do = torch.randn_like(o)
+        rec("efla_bwd (3 kernels + prep)",
+            time_ms(lambda: torch.autograd.grad(o, proj, do, retain_graph=True)),
+            efla_flops(B, T, H, d, True) - efla_flops(B, T, H, d, False))
+    if want("loss"):
+        V = a.vocab
+        hn = torch.randn(M, D, device=dev).bfloat16().requires_grad_()
+        wh = (torch.randn(V, D, device=dev) * 0.02).bfloat16().requires_grad_()
+        wh.main_grad = torch.zeros(V, D, device=dev)
+        tgt = torch.randint(0, V, (M,), device=dev)
+        rec(f"lm_head + cross-entropy fwd+bwd {M}x{V}x{D}",
+            time_ms(lambda: N.linear_cross_entropy(hn, wh, tgt)), 6.0 * M * V * D)
+    if want("optim"):
+        n = 1 << 28
+        ms_, m_, v_ = (torch.zeros(n, device=dev) for _ in range(3))
+        g_ = torch.randn(n, device=dev)
+        sh = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        from ..ops import _lib
+        L = _lib.lib()
+        rec("adamw (fp32 master + bf16 shadow) 2^28 elements",
+            time_ms(lambda: L.ceo_adamw_step(ms_.data_ptr(), m_.data_ptr(), v_.data_ptr(),
+                                             g_.data_ptr(), 1, sh.data_ptr(), n, 1e-3, 0.9, 0.95,
+                                             1e-8, 0.1, 1, None, 1.0, 0, _lib.stream())), 0,
+            n * 30.0)
     if a.json:
         Path(a.json).write_text(json.dumps(rows, indent=1))
 
