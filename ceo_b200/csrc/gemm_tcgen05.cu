@@ -54,6 +54,7 @@ struct GemmParams {
   // ---- collectives fused into the kernel (all zero for a plain GEMM) --------------------
   int m_rot, n_rot;        // tile traversal starts at this m / n block (local data first)
   int grp_m;               // row blocks per traversal group (see tile_coords)
+  int split_k;             // >1: k-slices of a tile accumulate into fp32 C with atomics
   // all-gather of one operand: the first `ag_ctas` CTAs pull the peers' row-shards into
   // the local gathered buffer (which the tensor map reads) and publish one flag per block
   // of BM (A) or BN (B) rows; the TMA producer waits for a block's flag before loading it.
@@ -142,7 +143,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   // the first ag_ctas CTAs only copy (all-gather); the others walk the output tiles
   const bool copy_cta = static_cast<int>(blockIdx.x) < p.ag_ctas;
   const int tile_step = static_cast<int>(gridDim.x) - p.ag_ctas;
-  const int first_tile = copy_cta ? total_tiles : static_cast<int>(blockIdx.x) - p.ag_ctas;
+  // split-K: a work unit is (k-slice, tile); slices of one tile accumulate into C with atomics
+  const int total_units = total_tiles * p.split_k;
+  const int kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
+  const int first_tile = copy_cta ? total_units : static_cast<int>(blockIdx.x) - p.ag_ctas;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -150,9 +154,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
-        const int b = t / tiles_per_batch;
-        const int r = t - b * tiles_per_batch;
+      for (int t = first_tile; t < total_units && ok; t += tile_step) {
+        const int ks = t / total_tiles, tt = t - ks * total_tiles;
+        const int kb0 = ks * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
+        const int b = tt / tiles_per_batch;
+        const int r = tt - b * tiles_per_batch;
         int mb_, nb_;
         tile_coords(p, r, mb_, nb_);
         const int m0 = mb_ * BM, n0 = nb_ * BN;
@@ -169,7 +175,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             fence_proxy_async_all();
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
             atomicCAS(p.status, 0, ST_PRODUCER);
             ok = false;
@@ -277,9 +283,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
+      for (int t = first_tile; t < total_units && ok; t += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
+        const int kb0 = (t / total_tiles) * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1)) {
           atomicCAS(p.status, 0, ST_MMA_TMEM);
           ok = false;
@@ -287,7 +294,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph)) {
             atomicCAS(p.status, 0, ST_MMA_FULL);
             ok = false;
@@ -302,7 +309,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                      : umma_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? umma_smem_desc(sb + k * 2048, PANEL_BYTES, 1024)
                                      : umma_smem_desc(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -315,11 +322,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
     int it = 0;
     bool ok = true;
-    for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
+    for (int t = first_tile; t < total_units && ok; t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
-      const int b = t / tiles_per_batch;
-      const int r = t - b * tiles_per_batch;
+      const int tt = t % total_tiles;
+      const int b = tt / tiles_per_batch;
+      const int r = tt - b * tiles_per_batch;
       int mb_, nb_;
       tile_coords(p, r, mb_, nb_);
       const int m0 = mb_ * BM, n0 = nb_ * BN;
@@ -420,7 +428,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         if (p.out_f32) {
           float* crow = reinterpret_cast<float*>(cbase) + coff + n;
-          if (full && ((p.ldc & 3) == 0)) {
+          if (p.split_k > 1) {
+            // k-slices of this tile land in any order: accumulate with vector reductions
+            if (full && ((p.ldc & 3) == 0)) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(crow + 4 * q),
+                             "f"(f[4 * q]), "f"(f[4 * q + 1]), "f"(f[4 * q + 2]), "f"(f[4 * q + 3])
+                             : "memory");
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n + j < p.N) atomicAdd(crow + j, f[j]);
+            }
+          } else if (full && ((p.ldc & 3) == 0)) {
             float4* cp = reinterpret_cast<float4*>(crow);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -611,6 +631,7 @@ static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t 
 }
 
 static int g_num_sms = 0;
+static int g_deterministic = 0;  // 1: no split-K (its atomics make the fp32 sum order vary)
 
 template <int A_MN, int B_MN>
 static cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
@@ -647,7 +668,7 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
                     long long batch_stride_a, long long batch_stride_b, long long batch_stride_c,
                     int out_f32, int accumulate, float alpha, const float* bias,
                     const void* residual, long long ldr, long long batch_stride_r, int* status,
-                    int max_ctas, const FusedDesc& fz, cudaStream_t stream) {
+                    int max_ctas, const FusedDesc& fz, cudaStream_t stream, int split_k_mode = 1) {
   using namespace ceo;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA needs 16-byte aligned bases and row strides
@@ -738,6 +759,22 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
     p.grp_m = p.num_m;
   }
   long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
+  p.split_k = 1;
+  if (fz.kind == 0 && out_f32 && accumulate && !bias && !residual && split_k_mode != 0 &&
+      !ceo::g_deterministic) {
+    // few tiles with a long K (weight gradients): pick the split that fills whole waves best
+    const int num_kb = (K + BK - 1) / BK;
+    // every extra slice re-sends the whole fp32 C through L2 atomics, so a split has to buy a
+    // clear gain in wave efficiency (measured: 5 slices of the 2048x5632 gradient lose)
+    double best = 0.0;
+    for (int s = 1; s <= 3 && s * 16 <= num_kb; ++s) {
+      const long long units = total * s;
+      const long long waves = (units + cap - 1) / cap;
+      const double eff = static_cast<double>(units) / (waves * cap) - 0.05 * (s - 1);
+      if (eff > best + (s > 1 ? 0.05 : 0.0)) { best = eff; p.split_k = s; }
+    }
+  }
+  total *= p.split_k;
   int grid = static_cast<int>(total + p.ag_ctas < cap ? total + p.ag_ctas : cap);
   cudaError_t e;
   if (a_mn_major == 0 && b_mn_major == 0) e = launch<0, 0>(ta, tb, p, grid, stream);
@@ -809,4 +846,10 @@ extern "C" int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int 
   fz.rs_ldo = ldo;
   return gemm_run(A, B, stage[rank], M, N, K, lda, ldb, N, a_mn_major, b_mn_major, 1, 0, 0, 0, 0,
                   0, alpha, nullptr, nullptr, 0, 0, status, 0, fz, stream);
+}
+
+// 1 = bit-reproducible GEMM results (weight-gradient GEMMs then never split K).
+extern "C" int ceo_set_deterministic(int on) {
+  ceo::g_deterministic = on ? 1 : 0;
+  return 0;
 }

@@ -37,6 +37,10 @@ int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
                   const void* residual, long long ldr, long long batch_stride_r, int* status,
                   int max_ctas, cudaStream_t stream);
 
+/* 1: weight-gradient GEMMs never split K (split-K accumulates with fp32 atomics, whose order
+ * varies from run to run).  Default 0. */
+int ceo_set_deterministic(int on);
+
 /* ---- EFLA (chunked delta rule), chunk = 64, D in {64, 128}, T % 64 == 0 -------------
  * q,k,v: bf16 (B,T,H,D) with a token stride in elements (slices of a fused QKV output are
  * fine); alpha fp32 (B,T,H); s0 / s_final / ds_final / ds0 fp32 (B,H,D,D) (s0, ds_final may

@@ -179,6 +179,75 @@ __global__ void muon_apply_kernel(float* __restrict__ master, const bf16* __rest
   }
 }
 
+// float4-vectorised variants for fp32 gradients (the flat main_grad buffer): 16-byte loads
+// and stores on every stream, 8-byte stores for the bf16 shadow.
+__global__ void __launch_bounds__(256)
+adamw_vec4_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
+                  float4* __restrict__ grad, uint2* __restrict__ shadow, long long n4, float lr,
+                  float b1, float b2, float eps, float wd, float bc1_inv, float bc2_inv,
+                  const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
+  const float decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 g4 = grad[i], m4 = m[i], v4 = v[i], p4 = master[i];
+    float* gp = reinterpret_cast<float*>(&g4);
+    float* mp = reinterpret_cast<float*>(&m4);
+    float* vp = reinterpret_cast<float*>(&v4);
+    float* pp = reinterpret_cast<float*>(&p4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g = gp[j] * gs;
+      mp[j] = b1 * mp[j] + (1.f - b1) * g;
+      vp[j] = b2 * vp[j] + (1.f - b2) * g * g;
+      pp[j] = pp[j] * decay - lr * (mp[j] * bc1_inv) / (sqrtf(vp[j] * bc2_inv) + eps);
+    }
+    m[i] = m4;
+    v[i] = v4;
+    master[i] = p4;
+    if (shadow) {
+      uint2 o;
+      bf162* h = reinterpret_cast<bf162*>(&o);
+      h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
+      h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
+      shadow[i] = o;
+    }
+    if (zero_grad) grad[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+lion_vec4_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ grad,
+                 uint2* __restrict__ shadow, long long n4, float lr, float b1, float b2, float wd,
+                 const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
+  const float decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 g4 = grad[i], m4 = m[i], p4 = master[i];
+    float* gp = reinterpret_cast<float*>(&g4);
+    float* mp = reinterpret_cast<float*>(&m4);
+    float* pp = reinterpret_cast<float*>(&p4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g = gp[j] * gs;
+      const float u = b1 * mp[j] + (1.f - b1) * g;
+      pp[j] = pp[j] * decay - lr * (u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f));
+      mp[j] = b2 * mp[j] + (1.f - b2) * g;
+    }
+    m[i] = m4;
+    master[i] = p4;
+    if (shadow) {
+      uint2 o;
+      bf162* h = reinterpret_cast<bf162*>(&o);
+      h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
+      h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
+      shadow[i] = o;
+    }
+    if (zero_grad) grad[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 constexpr int OPT_GRID_CAP = 148 * 8;
 
 }  // namespace ceo
@@ -231,7 +300,17 @@ extern "C" int ceo_adamw_step(float* master, float* m, float* v, void* grad, int
   const float bc1_inv = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
   const float bc2_inv = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
   const int g = grid_for(n, 256 * 4, OPT_GRID_CAP);
-  if (grad_f32)
+  const bool vec = grad_f32 && (n & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(shadow_bf16) & 7) == 0;
+  if (vec)
+    adamw_vec4_kernel<<<grid_for(n >> 2, 256 * 2, OPT_GRID_CAP * 2), 256, 0, stream>>>(
+        reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+        reinterpret_cast<float4*>(v), static_cast<float4*>(grad),
+        static_cast<uint2*>(shadow_bf16), n >> 2, lr, beta1, beta2, eps, weight_decay, bc1_inv,
+        bc2_inv, gscale_ptr, gscale, zero_grad);
+  else if (grad_f32)
     adamw_kernel<float><<<g, 256, 0, stream>>>(master, m, v, static_cast<float*>(grad),
                                                static_cast<bf16*>(shadow_bf16), n, lr, beta1,
                                                beta2, eps, weight_decay, bc1_inv, bc2_inv,
@@ -250,7 +329,16 @@ extern "C" int ceo_lion_step(float* master, float* m, void* grad, int grad_f32, 
                              cudaStream_t stream) {
   if (n <= 0) return -5;
   const int g = grid_for(n, 256 * 4, OPT_GRID_CAP);
-  if (grad_f32)
+  const bool vec = grad_f32 && (n & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(grad)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(shadow_bf16) & 7) == 0;
+  if (vec)
+    lion_vec4_kernel<<<grid_for(n >> 2, 256 * 2, OPT_GRID_CAP * 2), 256, 0, stream>>>(
+        reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+        static_cast<float4*>(grad), static_cast<uint2*>(shadow_bf16), n >> 2, lr, beta1, beta2,
+        weight_decay, gscale_ptr, gscale, zero_grad);
+  else if (grad_f32)
     lion_kernel<float><<<g, 256, 0, stream>>>(master, m, static_cast<float*>(grad),
                                               static_cast<bf16*>(shadow_bf16), n, lr, beta1, beta2,
                                               weight_decay, gscale_ptr, gscale, zero_grad);

@@ -27,6 +27,9 @@ class TrainEngine:
         dtype = None
         if self.device.type == "cuda":
             dtype = torch.bfloat16
+        if self.device.type == "cuda":
+            from ..ops import _lib
+            _lib.lib().ceo_set_deterministic(int(cfg.runtime.deterministic))
         self.model = EflaLM(cfg.model, self.device, dtype=dtype, seed=seed)
         self.flat = FlatParams(self.model, self.world, self.rank,
                                alloc=getattr(comm, "alloc", None))
