@@ -144,7 +144,8 @@ __global__ void __launch_bounds__(128)
 efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
                       const bf16* __restrict__ u, const float* __restrict__ s0,
                       bf16* __restrict__ up, bf16* __restrict__ states,
-                      float* __restrict__ s_final, int T, int H, long long ks) {
+                      float* __restrict__ s_final, float* __restrict__ p_final, int T, int H,
+                      long long ks) {
   constexpr int LD = D + 8, NT = BV / 8, MT = D / 64;
   extern __shared__ __align__(16) uint8_t smem[];
   bf16* Ws = reinterpret_cast<bf16*>(smem);
@@ -153,7 +154,11 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
   bf16* Ss = Us + CH * LDV;
   bf16* Ups = Ss + D * LDV;
 
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, v0 = blockIdx.x * BV;
+  // With p_final the grid has twice the column slices: the second half runs the homogeneous
+  // recurrence (U = 0) on the identity, i.e. the span's transfer matrix P = prod (I - K^T W),
+  // which context parallelism needs next to the zero-state response.
+  const bool ident = blockIdx.x >= D / BV;
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, v0 = (blockIdx.x % (D / BV)) * BV;
   const int n = T / CH;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const long long HD = static_cast<long long>(H) * D;
@@ -167,13 +172,14 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
       for (int e = 0; e < 4; ++e) {
         const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
         const int col = v0 + nt * 8 + 2 * tg + (e & 1);
-        sacc[mt][nt][e] = s0 ? s0[(static_cast<long long>(bh) * D + row) * D + col] : 0.f;
+        sacc[mt][nt][e] = ident ? (row == col ? 1.f : 0.f)
+                                : (s0 ? s0[(static_cast<long long>(bh) * D + row) * D + col] : 0.f);
       }
 
   auto issue_wu = [&](int c) {
     const long long tok0 = static_cast<long long>(b) * T + c * CH;
     tile_load_async<D, 128>(Ws, LD, w + tok0 * HD + h * D, HD, CH);
-    tile_load_async<BV, 128>(Us, LDV, u + tok0 * HD + h * D + v0, HD, CH);
+    if (!ident) tile_load_async<BV, 128>(Us, LDV, u + tok0 * HD + h * D + v0, HD, CH);
   };
   auto issue_k = [&](int c) {
     const long long tok0 = static_cast<long long>(b) * T + c * CH;
@@ -191,7 +197,7 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
     for (int mt = 0; mt < MT; ++mt) {
       const int r0 = warp * 16 * MT + mt * 16;
       frag_store_bf16<NT>(Ss + r0 * LDV, LDV, sacc[mt]);
-      frag_store_bf16<NT>(sg + static_cast<long long>(r0) * D, D, sacc[mt]);
+      if (!ident) frag_store_bf16<NT>(sg + static_cast<long long>(r0) * D, D, sacc[mt]);
     }
     cp_async_wait<1>();
     __syncthreads();
@@ -205,11 +211,12 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int row = 16 * warp + g + hf * 8, col = nt * 8 + 2 * tg;
-          const float2 uu =
-              __bfloat1622float2(*reinterpret_cast<const bf162*>(Us + row * LDV + col));
+          const float2 uu = ident ? make_float2(0.f, 0.f)
+                                  : __bfloat1622float2(*reinterpret_cast<const bf162*>(
+                                        Us + row * LDV + col));
           const bf162 r = __floats2bfloat162_rn(uu.x - acc[nt][2 * hf], uu.y - acc[nt][2 * hf + 1]);
           *reinterpret_cast<bf162*>(Ups + row * LDV + col) = r;
-          *reinterpret_cast<bf162*>(up + (tok0 + row) * HD + h * D + v0 + col) = r;
+          if (!ident) *reinterpret_cast<bf162*>(up + (tok0 + row) * HD + h * D + v0 + col) = r;
         }
     }
     __syncthreads();
@@ -233,7 +240,8 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
       for (int e = 0; e < 4; ++e) {
         const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
         const int col = v0 + nt * 8 + 2 * tg + (e & 1);
-        s_final[(static_cast<long long>(bh) * D + row) * D + col] = sacc[mt][nt][e];
+        (ident ? p_final : s_final)[(static_cast<long long>(bh) * D + row) * D + col] =
+            sacc[mt][nt][e];
       }
 }
 
@@ -789,7 +797,7 @@ static int efla_fwd_impl(const bf16* q, const bf16* k, const bf16* v, const floa
   // U is staged in `o` (same shape, overwritten by the last kernel)
   efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(k, v, alpha, w, o, T, H, ks, vs);
   efla_state_fwd_kernel<D><<<gser, 128, smem_state_fwd<D>(), st>>>(k, w, o, s0, up, states,
-                                                                    s_final, T, H, ks);
+                                                                    s_final, nullptr, T, H, ks);
   efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(q, k, up, states, o, T, H, qs, ks);
   return static_cast<int>(cudaGetLastError());
 }
@@ -916,7 +924,8 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
 // Stage-by-stage access to the six kernels, for callers that interleave them with other work
 // (context parallelism runs the state recurrences more than once around a state exchange).
 // ptrs: 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u, 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO,
-//       12 dloc, 13 dup, 14 dstates, 15 ds_final, 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha
+//       12 dloc, 13 dup, 14 dstates, 15 ds_final, 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha,
+//       21 p_final (stage 1 only, optional: also computes the span's transfer matrix)
 // strides (elements per token): 0 q, 1 k, 2 v, 3 dq, 4 dk, 5 dv
 // stage: 0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd, 5 bwd_final
 namespace ceo {
@@ -944,8 +953,9 @@ static int efla_stage_impl(int stage, void* const* P, const long long* S, int B,
                                                          H, S[1], S[2]);
       break;
     case 1:
-      efla_state_fwd_kernel<D><<<gser, 128, smem_state_fwd<D>(), st>>>(
-          b16(1), b16(4), b16(5), f32(9), b16(6), b16(7), f32(10), T, H, S[1]);
+      efla_state_fwd_kernel<D><<<dim3(P[21] ? 2 * (D / BV) : D / BV, B * H), 128,
+                                 smem_state_fwd<D>(), st>>>(
+          b16(1), b16(4), b16(5), f32(9), b16(6), b16(7), f32(10), f32(21), T, H, S[1]);
       break;
     case 2:
       efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(b16(0), b16(1), b16(6), b16(7), b16(8),

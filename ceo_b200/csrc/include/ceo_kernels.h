@@ -57,9 +57,11 @@ int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha
                  long long v_stride, long long dq_stride, long long dk_stride,
                  long long dv_stride, int* status, cudaStream_t stream);
 /* One of the six EFLA kernels at a time (0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd,
- * 5 bwd_final).  ptrs (host array of 21 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
+ * 5 bwd_final).  ptrs (host array of 22 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
  * 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO, 12 dloc, 13 dup, 14 dstates, 15 ds_final,
- * 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha; strides (host array of 6): q, k, v, dq, dk, dv. */
+ * 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha, 21 p_final (optional, stage 1: also returns the
+ * span's transfer matrix P with S_out = P S_in + R); strides (host array of 6): q, k, v, dq,
+ * dk, dv. */
 int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T, int H,
                    int D, cudaStream_t stream);
 /* q/k L2 normalisation (optional) + alpha = c(beta, |k|^2); one launch each way.

@@ -26,11 +26,11 @@ from .symm import SymmetricBuffer
 
 _IDX = {"q": 0, "k": 1, "v": 2, "alpha": 3, "w": 4, "u": 5, "up": 6, "states": 7, "o": 8,
         "s0": 9, "s_final": 10, "dO": 11, "dloc": 12, "dup": 13, "dstates": 14, "ds_final": 15,
-        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20}
+        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20, "p_final": 21}
 
 
 def _stage(stage: int, tensors: dict, strides, B, T, H, d):
-    ptrs = (ctypes.c_void_p * 21)()
+    ptrs = (ctypes.c_void_p * 22)()
     for k, t in tensors.items():
         ptrs[_IDX[k]] = None if t is None else t.data_ptr()
     st = (ctypes.c_longlong * 6)(*strides)
@@ -88,11 +88,8 @@ class _CPDeltaRule(torch.autograd.Function):
         base = {"q": q, "k": k, "v": v, "alpha": alpha, "w": w, "u": u, "up": up,
                 "states": states, "o": o}
         _stage(0, base, strides, B, T, H, d)
-        # R_r: state pass from zero;  P_r: the homogeneous pass on the identity (U = 0)
-        _stage(1, dict(base, s0=None, s_final=R), strides, B, T, H, d)
-        eye = torch.eye(d, device=dev, dtype=torch.float32).expand(B, H, d, d).contiguous()
-        zero_u = torch.zeros_like(u)
-        _stage(1, dict(base, u=zero_u, s0=eye, s_final=P), strides, B, T, H, d)
+        # one launch: R_r (state pass from zero) and P_r (homogeneous pass on the identity)
+        _stage(1, dict(base, s0=None, s_final=R, p_final=P), strides, B, T, H, d)
         allmaps = cp.exchange(torch.stack([P, R]))          # (G, 2, B, H, d, d)
         s_in = torch.zeros_like(R)
         for j in range(cp.rank):                            # fold the maps of earlier ranks
