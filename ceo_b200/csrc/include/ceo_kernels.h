@@ -162,6 +162,27 @@ int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* sc
 int ceo_fp8_update_scale(float* history, int hist_len, int* cursor, float* amax, float* scale,
                          float fp8_max, float margin_pow2, cudaStream_t stream);
 
+/* ---- scan / gather / scatter / memory utilities --------------------------------------
+ * cumsum: fp32 rows of n elements, inclusive or exclusive, optionally from the end of the row;
+ * `scratch` must hold ceo_cumsum_scratch_floats(rows, n) floats (0 for many short rows).
+ * gather / scatter move rows of row_bytes (multiple of 16) by 64-bit row indices; indices out
+ * of range give zero rows (gather) or are skipped (scatter).  transpose16 works on any 2-byte
+ * element type. */
+int ceo_cumsum_scratch_floats(long long rows, long long n);
+int ceo_cumsum_f32(const float* x, float* y, long long rows, long long n, int exclusive,
+                   int reverse, float* scratch, cudaStream_t stream);
+int ceo_gather_rows(const long long* idx, const void* src, void* dst, long long n,
+                    long long row_bytes, long long src_rows, cudaStream_t stream);
+int ceo_scatter_rows(const long long* idx, const void* src, void* dst, long long n,
+                     long long row_bytes, long long dst_rows, cudaStream_t stream);
+int ceo_scatter_add_f32(const long long* idx, const float* src, float* dst, long long n, int D,
+                        long long dst_rows, cudaStream_t stream);
+int ceo_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch,
+               long long rows, long long row_bytes, cudaStream_t stream);
+int ceo_transpose16(const void* src, void* dst, int rows, int cols, long long lds, long long ldd,
+                    cudaStream_t stream);
+int ceo_memset32(void* x, long long n, unsigned int value, cudaStream_t stream);
+
 /* ---- peer-memory collectives (NVLink), fused with their compute --------------------------
  * Buffers are plain cudaMalloc allocations mapped into every rank through CUDA IPC; the
  * `void* const*` arguments are host arrays of `world` device pointers indexed by rank (this

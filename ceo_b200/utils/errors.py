@@ -21,6 +21,9 @@ class RankFailure(CommunicationError): pass       # noqa: E701
 class KernelWaitTimeout(TrainingError): pass      # noqa: E701
 class OutOfMemory(TrainingError): pass            # noqa: E701
 class UnsupportedDevice(TrainingError): pass      # noqa: E701
+class NoGpuAvailable(TrainingError): pass         # noqa: E701
+class InvalidWorldSize(TrainingError): pass       # noqa: E701
+class PeerAccessUnavailable(CommunicationError): pass  # noqa: E701
 
 
 class ErrorContext:

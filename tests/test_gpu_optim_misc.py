@@ -149,3 +149,49 @@ def test_model_with_prism_branch_trains_on_gpu():
                                    lr=2e-3)[0]) for _ in range(4)]
     assert all(l == l for l in losses) and losses[-1] < losses[0]
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("rows,n", [(300, 777), (3, 200_000), (1, 1_000_003)])
+@pytest.mark.parametrize("exclusive,reverse", [(False, False), (True, False), (False, True),
+                                               (True, True)])
+def test_cumsum_matches_fp64(rows, n, exclusive, reverse):
+    from ceo_b200.ops import tensor_ops as T
+    x = torch.randn(rows, n, device="cuda")
+    y = T.cumsum(x, exclusive, reverse)
+    xd = x.double().flip(-1) if reverse else x.double()
+    r = xd.cumsum(-1)
+    if exclusive:
+        r = r - xd
+    r = r.flip(-1) if reverse else r
+    assert (y.double() - r).abs().max().item() < 2e-3 * (n ** 0.5)
+
+
+def test_gather_scatter_copy_transpose_memset():
+    from ceo_b200.ops import tensor_ops as T
+    g = torch.Generator(device="cuda").manual_seed(3)
+    src = torch.randn(1000, 72, device="cuda", generator=g).bfloat16()
+    idx = torch.randint(-2, 1002, (5000,), device="cuda", generator=g)
+    out = T.gather_rows(src, idx)
+    ok = (idx >= 0) & (idx < 1000)
+    exp = torch.where(ok[:, None], src[idx.clamp(0, 999)], torch.zeros_like(out))
+    assert torch.equal(out, exp)
+    perm = torch.randperm(1000, device="cuda")
+    dst = torch.zeros_like(src)
+    T.scatter_rows(dst, perm, src)
+    assert torch.equal(dst[perm], src)
+    acc = torch.zeros(50, 64, device="cuda")
+    vals = torch.randn(4000, 64, device="cuda", generator=g)
+    where = torch.randint(0, 50, (4000,), device="cuda", generator=g)
+    T.scatter_add_rows(acc, where, vals)
+    exp = torch.zeros(50, 64, device="cuda", dtype=torch.float64).index_add_(0, where, vals.double())
+    assert (acc.double() - exp).abs().max().item() < 1e-3
+    big = torch.randn(333, 512, device="cuda", generator=g)
+    view = big[:, 128:384]
+    d2 = torch.empty(333, 256, device="cuda")
+    T.copy2d(d2, view)
+    assert torch.equal(d2, view)
+    m = torch.randn(301, 190, device="cuda", generator=g).bfloat16()
+    assert torch.equal(T.transpose2d(m), m.t().contiguous())
+    z = torch.empty(100_003, dtype=torch.int32, device="cuda")
+    T.memset32(z, 0xDEADBEEF)
+    assert (z.view(torch.int32) == (0xDEADBEEF - 2 ** 32)).all()

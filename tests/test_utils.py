@@ -211,3 +211,56 @@ def test_cli_args_and_errors():
     with pytest.raises(errors.InfDetected):
         errors.check_finite_slice([1.0, math.inf])
     assert "step 3" in str(errors.ErrorContext(ValueError("x"), "forward", 3, 1))
+
+
+def test_tensor_ops_cpu_paths():
+    import torch
+    from ceo_b200.ops import tensor_ops as T
+    x = torch.arange(1, 6, dtype=torch.float32)[None]
+    assert T.cumsum(x).tolist() == [[1, 3, 6, 10, 15]]
+    assert T.cumsum(x, exclusive=True).tolist() == [[0, 1, 3, 6, 10]]
+    assert T.cumsum(x, reverse=True).tolist() == [[15, 14, 12, 9, 5]]
+    assert T.cumsum(x, True, True).tolist() == [[14, 12, 9, 5, 0]]
+    src = torch.arange(12.).view(3, 4)
+    out = T.gather_rows(src, torch.tensor([2, -1, 0, 5]))
+    assert out.tolist() == [[8, 9, 10, 11], [0] * 4, [0, 1, 2, 3], [0] * 4]
+    dst = torch.zeros(3, 4)
+    T.scatter_add_rows(dst, torch.tensor([1, 1, 7]), torch.ones(3, 4))
+    assert dst[1].tolist() == [2.0] * 4 and dst.sum().item() == 8.0
+    assert T.transpose2d(src.bfloat16()).shape == (4, 3)
+
+
+def test_topology_from_fake_nvml_and_sysfs(tmp_path):
+    from ceo_b200.runtime.device import DeviceInfo, Topology, parse_cpulist
+    assert parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    for nid, cpus in ((0, "0-3"), (1, "4-7")):
+        d = tmp_path / "devices" / "system" / "node" / f"node{nid}"
+        d.mkdir(parents=True)
+        (d / "cpulist").write_text(cpus + "\n")
+        (d / "meminfo").write_text(f"Node {nid} MemTotal:       1024 kB\n")
+    for bdf, node in (("0000:1b:00.0", 0), ("0000:9d:00.0", 1)):
+        d = tmp_path / "bus" / "pci" / "devices" / bdf
+        d.mkdir(parents=True)
+        (d / "numa_node").write_text(f"{node}\n")
+
+    class FakeNvml:
+        def count(self): return 2
+        def pci(self, i): return (0, (0x1b, 0x9d)[i], 0, ("00000000:1B:00.0", "00000000:9D:00.0")[i])
+        def nvlinks(self, i): return 18
+
+    t = Topology.detect(nvml=FakeNvml(), sysfs=str(tmp_path))
+    assert [n.gpus for n in t.numa_nodes] == [[0], [1]]
+    assert t.numa_nodes[1].cpus == [4, 5, 6, 7] and t.numa_nodes[0].memory_size == 1024 * 1024
+    assert t.gpu_affinity[1].pci_bus == 0x9d and t.gpu_affinity[1].nvlink_active == 18
+    assert t.gpu_for_numa(1) == 1 and t.gpu_for_numa(5) is None
+    assert t.cpus_for_gpu(0) == [0, 1, 2, 3]
+    # no sources at all: one node, bus = index (all the reference reports)
+    class NoNvml:
+        def count(self): return 3
+        def pci(self, i): raise RuntimeError
+        def nvlinks(self, i): return 0
+    t = Topology.detect(nvml=NoNvml(), sysfs=str(tmp_path / "nowhere"))
+    assert len(t.numa_nodes) == 1 and t.numa_nodes[0].gpus == [0, 1, 2]
+    assert [a.pci_bus for a in t.gpu_affinity] == [0, 1, 2]
+    assert DeviceInfo(0, "B200", 10, 0, 148, 1).is_blackwell
+    assert not DeviceInfo(0, "H100", 9, 0, 132, 1).is_blackwell
