@@ -107,6 +107,9 @@ def main(argv=None):
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=0,
+                    help="tensor-parallel size (0: 1 for the default config, else the config's)")
+    ap.add_argument("--cp", type=int, default=0, help="context-parallel size (0: the config's)")
     a = ap.parse_args(argv)
 
     if a.impl == "reference":
@@ -142,18 +145,33 @@ def main(argv=None):
 
     cfg = Config.parse_from_file(a.config)
     cfg.runtime.world_size = world
-    cfg.runtime.tensor_parallel_size = 1
+    headline = os.path.basename(a.config) == "efla_1p3b.yaml"
+    tp = a.tp or (1 if headline else min(cfg.runtime.tensor_parallel_size, world))
+    cp = a.cp or min(cfg.runtime.context_parallel_size, world)
+    cfg.runtime.tensor_parallel_size, cfg.runtime.context_parallel_size = tp, cp
+    dp = world // (tp * cp)
     seq = a.seq_len or cfg.data.seq_len
+    cfg.data.seq_len = seq
     gbs = a.global_batch or cfg.training.global_batch_size
     mbs = a.micro_batch or cfg.training.micro_batch_size
-    if gbs % (mbs * world):
-        raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x {world}")
-    n_micro = gbs // (mbs * world)
+    cfg.training.micro_batch_size = mbs
+    if world % (tp * cp) or gbs % (mbs * dp):
+        raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x dp {dp}")
+    n_micro = gbs // (mbs * dp)
     tokens_per_step = gbs * seq
 
-    eng = TrainEngine(cfg, dev, comm)
+    if tp * cp > 1:
+        # tensor / context parallel groups inside the node, data parallel (sharded optimizer)
+        # across them; every rank of one tp x cp group reads the same batches
+        from ceo_b200.runtime.parallel_engine import ParallelEngine
+        eng = ParallelEngine(cfg, dev, fused=a.comm != "nccl" or tp > 1,
+                             impl="nccl" if a.comm == "nccl" else "fused")
+        data_rank = eng.pc.dp_rank
+    else:
+        eng = TrainEngine(cfg, dev, comm)
+        data_rank = rank
     data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
-                           cfg.data.synthetic.s, cfg.data.synthetic.seed, rank)
+                           cfg.data.synthetic.s, cfg.data.synthetic.seed, data_rank)
     host = [data.batch(mbs, seq, pin=True) for _ in range(n_micro)]
     on_dev = [(t.to(dev), g.to(dev)) for t, g in host]
     lr = cfg.training.learning_rate
@@ -205,14 +223,16 @@ def main(argv=None):
         value = tokens_per_step * a.steps / (ms * 1e-3)
         flops = eng.model.flops_per_token(seq) * value
         out = {
-            "metric": "train tokens/sec (box, device-timed, max over ranks) EFLA-1.3B",
+            "metric": "train tokens/sec (box, device-timed, max over ranks) " + cfg.model.name,
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded Zipf(1.1) tokens, N(0,0.02) random-init weights)",
             "config": {"model": cfg.model.name, "global_batch": gbs, "seq_len": seq,
                        "tokens_per_step": tokens_per_step, "micro_batch": mbs,
-                       "grad_accum_steps": n_micro, "parallelism": f"fsdp{world}",
+                       "grad_accum_steps": n_micro,
+                       "parallelism": (f"fsdp{world}" if tp * cp == 1 else
+                                       f"tp{tp}xcp{cp}xfsdp{dp}"),
                        "optimizer": cfg.training.optimizer,
                        "collectives": type(comm).__name__ if comm else "none",
                        "l2": "inputs larger than L2 (each micro-batch streams >1 GB)"},

@@ -29,37 +29,154 @@ __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, const uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// acc[NT][4] += A (16 x K) * B (K x 8*NT), operands in shared memory (bf16).
+// acc[MT][NT][4] += A (16*MT x K) * B (K x 8*NT), operands in shared memory (bf16).
 //   A_T = false: A stored [m][k] with leading dimension lda; `A` points at (m0, 0)
 //   A_T = true : A stored [k][m];                            `A` points at (0, m0)
 //   B_T = false: B stored [n][k] with leading dimension ldb; `B` points at (n0, 0)
 //   B_T = true : B stored [k][n];                            `B` points at (0, n0)
 // Rows of both tiles must start on 16-byte boundaries (lda, ldb multiples of 8).
-// Accumulator layout (g = lane/4, t = lane%4): acc[nt][0..1] -> row g, cols nt*8+2t, +1;
-// acc[nt][2..3] -> row g+8, same cols.
-template <int NT, int K, bool A_T, bool B_T>
-__device__ __forceinline__ void warp_gemm(float (*acc)[4], const __nv_bfloat16* A, int lda,
-                                          const __nv_bfloat16* B, int ldb) {
-  static_assert(NT % 2 == 0 && K % 16 == 0, "tile shape");
+// Accumulator layout (g = lane/4, t = lane%4): acc[mt][nt][0..1] -> row 16*mt+g, cols
+// nt*8+2t, +1; acc[mt][nt][2..3] -> row 16*mt+g+8, same cols.
+// The MT row tiles share every B fragment, and the fragments of k-step i+1 are requested
+// before the MMAs of k-step i are issued (two register sets), so ldmatrix latency overlaps
+// the tensor work; the asm statements are volatile, hence emitted in exactly this order.
+template <int MT, int NT, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_frags(uint32_t (*a)[4], uint32_t (*b)[4],
+                                           const __nv_bfloat16* A, int lda,
+                                           const __nv_bfloat16* B, int ldb, int k0) {
   const int lane = threadIdx.x & 31;
   const int l7 = lane & 7, b3 = (lane >> 3) & 1, b4 = lane >> 4;
 #pragma unroll
-  for (int k0 = 0; k0 < K; k0 += 16) {
-    uint32_t a[4];
+  for (int mt = 0; mt < MT; ++mt) {
     if (!A_T)
-      ldsm_x4(a, smem_addr(A + (l7 + b3 * 8) * lda + k0 + b4 * 8));
+      ldsm_x4(a[mt], smem_addr(A + (mt * 16 + l7 + b3 * 8) * lda + k0 + b4 * 8));
     else
-      ldsm_x4_t(a, smem_addr(A + (k0 + l7 + b4 * 8) * lda + b3 * 8));
+      ldsm_x4_t(a[mt], smem_addr(A + (k0 + l7 + b4 * 8) * lda + mt * 16 + b3 * 8));
+  }
 #pragma unroll
-    for (int nt = 0; nt < NT; nt += 2) {
-      uint32_t b[4];
-      if (!B_T)
-        ldsm_x4(b, smem_addr(B + (nt * 8 + l7 + b4 * 8) * ldb + k0 + b3 * 8));
-      else
-        ldsm_x4_t(b, smem_addr(B + (k0 + l7 + b3 * 8) * ldb + nt * 8 + b4 * 8));
-      mma16816(acc[nt], a, b);
-      mma16816(acc[nt + 1], a, b + 2);
-    }
+  for (int nt = 0; nt < NT; nt += 2) {
+    if (!B_T)
+      ldsm_x4(b[nt / 2], smem_addr(B + (nt * 8 + l7 + b4 * 8) * ldb + k0 + b3 * 8));
+    else
+      ldsm_x4_t(b[nt / 2], smem_addr(B + (k0 + l7 + b3 * 8) * ldb + nt * 8 + b4 * 8));
+  }
+}
+
+template <int MT, int NT, int K, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_gemm_mt(float (*acc)[NT][4], const __nv_bfloat16* A, int lda,
+                                             const __nv_bfloat16* B, int ldb) {
+  static_assert(NT % 2 == 0 && K % 16 == 0, "tile shape");
+  constexpr bool PIPE = (4 * MT + 2 * NT) <= 24;  // two fragment sets only while they are cheap
+  constexpr int NB = PIPE ? 2 : 1;
+  uint32_t a[NB][MT][4], b[NB][NT / 2][4];
+  if (PIPE) warp_frags<MT, NT, A_T, B_T>(a[0], b[0], A, lda, B, ldb, 0);
+#pragma unroll
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    const int cur = PIPE ? (k0 / 16) & 1 : 0;
+    if (!PIPE) warp_frags<MT, NT, A_T, B_T>(a[0], b[0], A, lda, B, ldb, k0);
+    if (PIPE && k0 + 16 < K)
+      warp_frags<MT, NT, A_T, B_T>(a[cur ^ 1], b[cur ^ 1], A, lda, B, ldb, k0 + 16);
+#pragma unroll
+    for (int nt = 0; nt < NT; nt += 2)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma16816(acc[mt][nt], a[cur][mt], b[cur][nt / 2]);
+        mma16816(acc[mt][nt + 1], a[cur][mt], b[cur][nt / 2] + 2);
+      }
+  }
+}
+
+// One row tile: acc[NT][4] += A (16 x K) * B (K x 8*NT).
+template <int NT, int K, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_gemm(float (*acc)[4], const __nv_bfloat16* A, int lda,
+                                          const __nv_bfloat16* B, int ldb) {
+  warp_gemm_mt<1, NT, K, A_T, B_T>(reinterpret_cast<float (*)[NT][4]>(acc), A, lda, B, ldb);
+}
+
+// ---- the same products over tiles in the layout TMA writes with 128-byte swizzle ----------
+// A tile of R rows x C columns (bf16) is stored as C/64 panels of R rows x 128 bytes; inside a
+// panel the 16-byte chunk j of row r sits at chunk (j ^ (r & 7)).  Panels start on 1024-byte
+// boundaries.  ldmatrix rows are whole chunks, so fragments load conflict-free.
+struct SwzTile {
+  uint32_t base;         // shared-space address of the tile
+  uint32_t panel_bytes;  // rows * 128
+  __device__ __forceinline__ uint32_t at(int row, int col) const {
+    return base + (col >> 6) * panel_bytes + row * 128 +
+           (((((col >> 3) & 7) ^ (row & 7))) << 4) + (col & 7) * 2;
+  }
+};
+__device__ __forceinline__ SwzTile swz_tile(const void* p, int rows) {
+  SwzTile t;
+  t.base = smem_addr(p);
+  t.panel_bytes = rows * 128;
+  return t;
+}
+__device__ __forceinline__ void sts_bf162(uint32_t addr, float x, float y) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(*reinterpret_cast<const uint32_t*>(&v))
+               : "memory");
+}
+__device__ __forceinline__ float2 lds_bf162(uint32_t addr) {
+  uint32_t u;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u) : "r"(addr));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
+
+// acc[MT][NT][4] += A * B with A rows m0.. and B columns n0.. of swizzled tiles (A_T / B_T as
+// in warp_gemm_mt: false = tile stored [m][k] / [n][k], true = stored [k][m] / [k][n]).
+template <int MT, int NT, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_frags_swz(uint32_t (*a)[4], uint32_t (*b)[4],
+                                               const SwzTile& A, int m0, const SwzTile& B, int n0,
+                                               int k0) {
+  const int lane = threadIdx.x & 31;
+  const int l7 = lane & 7, b3 = (lane >> 3) & 1, b4 = lane >> 4;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    if (!A_T)
+      ldsm_x4(a[mt], A.at(m0 + mt * 16 + l7 + b3 * 8, k0 + b4 * 8));
+    else
+      ldsm_x4_t(a[mt], A.at(k0 + l7 + b4 * 8, m0 + mt * 16 + b3 * 8));
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; nt += 2) {
+    if (!B_T)
+      ldsm_x4(b[nt / 2], B.at(n0 + nt * 8 + l7 + b4 * 8, k0 + b3 * 8));
+    else
+      ldsm_x4_t(b[nt / 2], B.at(k0 + l7 + b3 * 8, n0 + nt * 8 + b4 * 8));
+  }
+}
+template <int MT, int NT, int K, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_gemm_swz(float (*acc)[NT][4], const SwzTile& A, int m0,
+                                              const SwzTile& B, int n0) {
+  static_assert(NT % 2 == 0 && K % 16 == 0, "tile shape");
+  constexpr bool PIPE = (4 * MT + 2 * NT) <= 24;
+  constexpr int NB = PIPE ? 2 : 1;
+  uint32_t a[NB][MT][4], b[NB][NT / 2][4];
+  if (PIPE) warp_frags_swz<MT, NT, A_T, B_T>(a[0], b[0], A, m0, B, n0, 0);
+#pragma unroll
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    const int cur = PIPE ? (k0 / 16) & 1 : 0;
+    if (!PIPE) warp_frags_swz<MT, NT, A_T, B_T>(a[0], b[0], A, m0, B, n0, k0);
+    if (PIPE && k0 + 16 < K)
+      warp_frags_swz<MT, NT, A_T, B_T>(a[cur ^ 1], b[cur ^ 1], A, m0, B, n0, k0 + 16);
+#pragma unroll
+    for (int nt = 0; nt < NT; nt += 2)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma16816(acc[mt][nt], a[cur][mt], b[cur][nt / 2]);
+        mma16816(acc[mt][nt + 1], a[cur][mt], b[cur][nt / 2] + 2);
+      }
+  }
+}
+// Stores a 16 x 8*NT accumulator tile as bf16 at rows m0.., columns n0.. of a swizzled tile.
+template <int NT>
+__device__ __forceinline__ void frag_store_swz(const SwzTile& t, int m0, int n0,
+                                               float (*acc)[4]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    sts_bf162(t.at(m0 + g, n0 + nt * 8 + 2 * tg), acc[nt][0], acc[nt][1]);
+    sts_bf162(t.at(m0 + g + 8, n0 + nt * 8 + 2 * tg), acc[nt][2], acc[nt][3]);
   }
 }
 

@@ -16,11 +16,16 @@
 //   efla_state_bwd_kernel  (serial, reverse)  dU' = D + K dS ;  dS <- dS + Q^T dO - W^T dU'
 //   efla_bwd_final_kernel  (parallel)  dK, dV, d(alpha) (re-solves the 64x64 system)
 //
-// All products run on tensor cores (warp-level bf16 MMA out of shared memory); the only
+// Every tile enters shared memory through TMA (tensor maps, 128-byte swizzle, completion on
+// mbarriers, requested up front in the order the steps need them); the serial kernels also
+// leave through TMA stores issued by a dedicated copy warp.  All products run on tensor cores
+// (warp-level bf16 MMA, fragments read conflict-free from the swizzled tiles); the only
 // backward workspace is one d x d bf16 state per chunk, against one per *token* in the
 // reference (kernels/cuda/efla.cu:235-313, 590-601), whose kernels walk the sequence token
 // by token with the state in global memory (efla.cu:154-233, 315-454).
 #include "common/mma.cuh"
+#include "common/ptx.cuh"
+#include "common/tmap.h"
 #include "common/util.cuh"
 #include "include/ceo_kernels.h"
 
@@ -28,20 +33,7 @@ namespace ceo {
 
 constexpr int CH = 64;    // chunk length
 constexpr int GLD = 68;   // leading dimension of the fp32 64x64 Gram tile
-constexpr int XLD = 72;   // leading dimension of bf16 64x64 tiles
-constexpr int BV = 32;    // value columns per CTA in the serial kernels
-constexpr int LDV = BV + 8;
-
-// cp.async a [rows][COLS] bf16 tile (row stride `gstride` elements) into smem with leading dim `sld`
-template <int COLS, int NTHR>
-__device__ __forceinline__ void tile_load_async(bf16* s, int sld, const bf16* g, long long gstride,
-                                                int rows) {
-  constexpr int V = COLS / 8;
-  for (int i = threadIdx.x; i < rows * V; i += NTHR) {
-    const int r = i / V, c = i - r * V;
-    cp_async16(s + r * sld + c * 8, g + r * gstride + c * 8);
-  }
-}
+constexpr int BV = 64;    // value columns per CTA in the serial kernels
 
 template <int NT>
 __device__ __forceinline__ void frag_store_bf16(bf16* base, long long ld, float (*acc)[4]) {
@@ -55,56 +47,164 @@ __device__ __forceinline__ void frag_store_bf16(bf16* base, long long ld, float 
   }
 }
 
-// Column c of X = (I + diag(al) Gs)^-1 for a strictly-lower Gs, by forward substitution in
-// registers; thread c of the first 64 threads calls this.  x[i] = 0 for i < c, x[c] = 1.
-__device__ __forceinline__ void solve_column(const float* __restrict__ Gs,
-                                             const float* __restrict__ al, int c, float* x) {
+// ---- tiles moved by TMA ------------------------------------------------------------------
+// Token-major tensors (q, k, v, w, u, ...) are mapped as matrices [B*T][H*D] with the token
+// stride as leading dimension, the state snapshots as [B*H*n*D][D]; both with 64-column boxes
+// and 128-byte swizzle, so a 64 x D token tile lands as D/64 panels of 64 rows x 128 bytes and
+// a D x D state as D/64 panels of D rows x 128 bytes (SwzTile in common/mma.cuh).
+constexpr int EFLA_WAIT_STATUS = 0x4546;
+constexpr int PANEL = CH * 128;  // bytes of a 64-row x 64-column swizzled panel
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+template <int D>
+__device__ __forceinline__ void tma_tok_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar,
+                                             int x0, int tok0) {
 #pragma unroll
-  for (int i = 0; i < CH; ++i) {
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int pnl = 0; pnl < D / 64; ++pnl) tma_load_2d(dst + pnl * PANEL, tm, bar, x0 + pnl * 64, tok0);
+}
+template <int D>
+__device__ __forceinline__ void tma_state_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar,
+                                               int row0) {
 #pragma unroll
-    for (int j = 0; j + 3 < i; j += 4) {
-      const float4 gq = *reinterpret_cast<const float4*>(Gs + i * GLD + j);
-      s0 += gq.x * x[j];
-      s1 += gq.y * x[j + 1];
-      s2 += gq.z * x[j + 2];
-      s3 += gq.w * x[j + 3];
+  for (int pnl = 0; pnl < D / 64; ++pnl) tma_load_2d(dst + pnl * D * 128, tm, bar, pnl * 64, row0);
+}
+// Wait for a tile group that is loaded once per CTA (phase 0).  Bounded: when a wait anywhere
+// in the grid has run out, the status word is set and every later wait returns at once.
+__device__ __forceinline__ void tile_wait(uint64_t* bar, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status)) return;
+  if (!mbar_wait(bar, 0) && status) atomicExch(status, EFLA_WAIT_STATUS);
+}
+// one row tile: acc[NT][4] += A[m0.., :] * B[.., n0..] over swizzled tiles
+template <int NT, int K, bool A_T, bool B_T>
+__device__ __forceinline__ void wg(float (*acc)[4], const SwzTile& A, int m0, const SwzTile& B,
+                                   int n0) {
+  warp_gemm_swz<1, NT, K, A_T, B_T>(reinterpret_cast<float (*)[NT][4]>(acc), A, m0, B, n0);
+}
+
+// X = (I + diag(al) G)^-1 for a strictly-lower 64x64 G (fp32, leading dimension GLD), with all
+// NTHR threads of the CTA and the working set in shared memory (compact rolled loops: this
+// code runs once per CTA, so its size matters more than its instruction count).
+//   1. the four 16x16 diagonal blocks by forward substitution (one column per thread of the
+//      first two warps: 16 dependent steps);
+//   2. inside each 32x32 diagonal block, X21 = -X22 (A21 X11) as two fp32 block products;
+//   3. the same at the 64 level with 32x32 blocks.
+// Xf receives X on and below the diagonal; everything above the diagonal is scratch.  Xf may
+// be Gs itself (G is then destroyed).  Starts and ends on a CTA barrier.
+//
+// C[i][j0..j0+3] = sign * rs[i] * sum_kk A[i][kk] * B[kk][j0..], for `nblk` independent N x N
+// blocks whose operands sit `step` elements apart.
+template <int NTHR, int N>
+__device__ __forceinline__ void solve_block_prod(const float* A, const float* B, float* C,
+                                                 const float* rs, float sign, int nblk,
+                                                 int step) {
+  constexpr int Q = N / 4;
+  for (int o = threadIdx.x; o < nblk * N * Q; o += NTHR) {
+    const int blk = o / (N * Q), rem = o - blk * N * Q, i = rem / Q, j0 = (rem - i * Q) * 4;
+    const float* a = A + blk * step + i * GLD;
+    const float* bb = B + blk * step + j0;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int kk = 0; kk < N; ++kk) {
+      const float av = a[kk];
+      const float4 bv = *reinterpret_cast<const float4*>(bb + kk * GLD);
+      acc.x += av * bv.x; acc.y += av * bv.y; acc.z += av * bv.z; acc.w += av * bv.w;
     }
-#pragma unroll
-    for (int j = (i / 4) * 4; j < i; ++j) s0 += Gs[i * GLD + j] * x[j];
-    const float s = (s0 + s1) + (s2 + s3);
-    x[i] = (i == c) ? 1.f : (i < c ? 0.f : -al[i] * s);
+    const float f = rs ? sign * rs[blk * (step / (GLD + 1)) + i] : sign;
+    *reinterpret_cast<float4*>(C + blk * step + i * GLD + j0) =
+        make_float4(f * acc.x, f * acc.y, f * acc.z, f * acc.w);
   }
+}
+
+template <int NTHR>
+__device__ __forceinline__ void solve_blocked(const float* Gs, const float* __restrict__ al,
+                                              float* Xf) {
+  // 1. diagonal 16x16 blocks: thread (blk, cl) owns column cl of block blk.  Right-looking
+  //    substitution with the column in registers: once x_j is known, every later row's partial
+  //    sum takes its G[i][j] x_j term, so a step's critical path is one multiply and one FMA
+  //    and no load depends on a value computed here.
+  if (threadIdx.x < CH) {
+    const int blk = threadIdx.x >> 4, cl = threadIdx.x & 15, o = 16 * blk;
+    const float* gblk = Gs + o * GLD + o;
+    float sum[16], x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      x[j] = (j == cl) ? 1.f : (j < cl ? 0.f : -al[o + j] * sum[j]);
+#pragma unroll
+      for (int i = j + 1; i < 16; ++i) sum[i] += gblk[i * GLD + j] * x[j];
+    }
+    __syncwarp();  // all of G's block has been read before X replaces it (Xf may be Gs)
+    float* xcol = Xf + o * GLD + o + cl;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) xcol[j * GLD] = x[j];
+  }
+  __syncthreads();
+  // 2. 32x32 diagonal blocks (two of them, 32 * (GLD + 1) elements apart)
+  constexpr int S32 = 32 * (GLD + 1);
+  //    T = a .* (G21 X11) -> upper-right 16x16 of the block (scratch)
+  solve_block_prod<NTHR, 16>(Gs + 16 * GLD, Xf, Xf + 16, al + 16, 1.f, 2, S32);
+  __syncthreads();
+  //    X21 = -X22 T
+  solve_block_prod<NTHR, 16>(Xf + 16 * GLD + 16, Xf + 16, Xf + 16 * GLD, nullptr, -1.f, 2, S32);
+  __syncthreads();
+  //    X11 of the 64 level must be lower triangular: clear the scratch
+  for (int o = threadIdx.x; o < 2 * 16 * 16; o += NTHR) {
+    const int blk = o >> 8, i = (o >> 4) & 15, j = o & 15;
+    Xf[blk * S32 + i * GLD + 16 + j] = 0.f;
+  }
+  __syncthreads();
+  // 3. 64 level: T = a .* (G21 X11) -> upper-right 32x32 (scratch);  X21 = -X22 T
+  solve_block_prod<NTHR, 32>(Gs + 32 * GLD, Xf, Xf + 32, al + 32, 1.f, 1, 0);
+  __syncthreads();
+  solve_block_prod<NTHR, 32>(Xf + 32 * GLD + 32, Xf + 32, Xf + 32 * GLD, nullptr, -1.f, 1, 0);
+  __syncthreads();
 }
 
 // ============================================================ forward: W, U
 template <int D>
 __global__ void __launch_bounds__(128)
-efla_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v,
-               const float* __restrict__ alpha, bf16* __restrict__ w, bf16* __restrict__ u, int T,
-               int H, long long ks, long long vs) {
-  constexpr int LD = D + 8;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Ks = reinterpret_cast<bf16*>(smem);
-  bf16* Vs = Ks + CH * LD;
-  float* Gs = reinterpret_cast<float*>(Vs + CH * LD);
-  bf16* Ts = reinterpret_cast<bf16*>(Gs + CH * GLD);
-  float* al = reinterpret_cast<float*>(Ts + CH * XLD);
+efla_wy_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const float* __restrict__ alpha, bf16* __restrict__ w, bf16* __restrict__ u,
+               bf16* __restrict__ xinv, int T, int H, int* status) {
+  constexpr int TILE = (D / 64) * PANEL;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Ks = smem;
+  uint8_t* Vs = Ks + TILE;
+  uint8_t* Ts = Vs + TILE;
+  float* Gs = reinterpret_cast<float*>(Ts + PANEL);
+  float* al = Gs + CH * GLD;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(al + CH);
 
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-  const long long tok0 = static_cast<long long>(b) * T + blockIdx.x * CH;
-  tile_load_async<D, 128>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-  tile_load_async<D, 128>(Vs, LD, v + tok0 * vs + h * D, vs, CH);
-  cp_async_commit();
-  if (threadIdx.x < CH) al[threadIdx.x] = alpha[(tok0 + threadIdx.x) * H + h];
-  cp_async_wait<0>();
+  const int tok0 = b * T + blockIdx.x * CH;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    fence_mbar_init();
+  }
   __syncthreads();
+  // one thread per tile requests it (a TMA instruction is slow to issue; spread them)
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Ks, &tm_k, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 32) {
+    mbar_arrive_expect_tx(&bars[1], TILE);
+    tma_tok_tile<D>(Vs, &tm_v, &bars[1], h * D, tok0);
+  }
+  if (threadIdx.x < CH) al[threadIdx.x] = alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h];
+  __syncthreads();
+  tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const SwzTile Kt = swz_tile(Ks, CH), Vt = swz_tile(Vs, CH), Tt = swz_tile(Ts, CH);
   {
     float acc[8][4];
     zero_acc<8>(acc);
-    warp_gemm<8, D, false, false>(acc, Ks + 16 * warp * LD, LD, Ks, LD);
+    wg<8, D, false, false>(acc, Kt, 16 * warp, Kt, 0);
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -114,55 +214,148 @@ efla_wy_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v,
       }
   }
   __syncthreads();
-  if (threadIdx.x < CH) {
-    float x[CH];
-    const int c = threadIdx.x;
-    solve_column(Gs, al, c, x);
-    const float ac = al[c];
-#pragma unroll
-    for (int i = 0; i < CH; ++i) Ts[i * XLD + c] = __float2bfloat16(x[i] * ac);
+  solve_blocked<128>(Gs, al, Gs);
+  // T = X diag(a) feeds the two products below; X itself (bf16) is kept for the backward pass
+  bf16* xg = xinv + (static_cast<long long>(bh) * (T / CH) + blockIdx.x) * CH * CH;
+  for (int e = threadIdx.x; e < CH * CH / 2; e += 128) {
+    const int i = e >> 5, c = (e & 31) * 2;
+    const float x0 = c <= i ? Gs[i * GLD + c] : 0.f;
+    const float x1 = c + 1 <= i ? Gs[i * GLD + c + 1] : 0.f;
+    sts_bf162(Tt.at(i, c), x0 * al[c], x1 * al[c + 1]);
+    *reinterpret_cast<bf162*>(xg + i * CH + c) = __floats2bfloat162_rn(x0, x1);
   }
   __syncthreads();
-  const long long orow = (tok0 + 16 * warp) * H + h;  // row index into (B*T*H, D)
+  const long long orow = (static_cast<long long>(tok0) + 16 * warp) * H + h;  // row of (B*T*H, D)
   {
     float acc[D / 8][4];
     zero_acc<D / 8>(acc);
-    warp_gemm<D / 8, CH, false, true>(acc, Ts + 16 * warp * XLD, XLD, Ks, LD);
+    wg<D / 8, CH, false, true>(acc, Tt, 16 * warp, Kt, 0);
     frag_store_bf16<D / 8>(w + orow * D, static_cast<long long>(H) * D, acc);
   }
+  tile_wait(&bars[1], status);
   {
     float acc[D / 8][4];
     zero_acc<D / 8>(acc);
-    warp_gemm<D / 8, CH, false, true>(acc, Ts + 16 * warp * XLD, XLD, Vs, LD);
+    wg<D / 8, CH, false, true>(acc, Tt, 16 * warp, Vt, 0);
     frag_store_bf16<D / 8>(u + orow * D, static_cast<long long>(H) * D, acc);
   }
 }
 
 // ==================================================== forward: state recurrence
+// One CTA per (b,h) and 64-column slice of the value dimension: eight compute warps (warp
+// (r, half) owns token rows 16r.. of the chunk products and 32 of the slice's columns) and
+// one copy warp.  One thread of the copy warp moves every tile with TMA (tensor-map loads on
+// mbarriers into 128-byte-swizzled tiles, tensor-map stores in bulk groups): W and K of a
+// chunk are double-buffered and requested two chunks ahead, so the serial chain per chunk is
+// W S -> U' -> K^T U' with no global load or store instruction in the compute warps.  Every
+// wait is bounded; the first one that runs out sets the status word and a flag that turns all
+// later waits into no-ops, so the kernel still runs to its end.
+constexpr int SER_THREADS = 288;  // 8 compute warps + 1 copy warp
+
+struct SerialSync {
+  uint64_t full[2], empty[2], full_u, ready_s, ready_u, st_free;
+  volatile uint32_t dead;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void compute_bar_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+__device__ __forceinline__ void ser_wait(SerialSync* sy, uint64_t* bar, uint32_t parity,
+                                         int* status) {
+  if (sy->dead) return;
+  if (!mbar_wait(bar, parity)) {
+    sy->dead = 1;
+    if (status) atomicExch(status, EFLA_WAIT_STATUS);
+  }
+}
+__device__ __forceinline__ void serial_sync_init(SerialSync* sy) {
+  mbar_init(&sy->full[0], 1);
+  mbar_init(&sy->full[1], 1);
+  mbar_init(&sy->empty[0], 8);
+  mbar_init(&sy->empty[1], 8);
+  mbar_init(&sy->full_u, 1);
+  mbar_init(&sy->ready_s, 1);
+  mbar_init(&sy->ready_u, 1);
+  mbar_init(&sy->st_free, 1);
+  sy->dead = 0;
+  fence_mbar_init();
+}
+
+// Token-major tensors (k, w, u, up, ...) are mapped as matrices [B*T][H*D] with the token
+// stride as leading dimension; the state snapshots as [B*H*n*D][D].
 template <int D>
-__global__ void __launch_bounds__(128)
-efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
-                      const bf16* __restrict__ u, const float* __restrict__ s0,
-                      bf16* __restrict__ up, bf16* __restrict__ states,
-                      float* __restrict__ s_final, float* __restrict__ p_final, int T, int H,
-                      long long ks) {
-  constexpr int LD = D + 8, NT = BV / 8, MT = D / 64;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Ws = reinterpret_cast<bf16*>(smem);
-  bf16* Ks = Ws + CH * LD;
-  bf16* Us = Ks + CH * LD;
-  bf16* Ss = Us + CH * LDV;
-  bf16* Ups = Ss + D * LDV;
+__global__ void __launch_bounds__(SER_THREADS, 2)
+efla_state_fwd_kernel(const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_u,
+                      const __grid_constant__ CUtensorMap tm_up,
+                      const __grid_constant__ CUtensorMap tm_states,
+                      const float* __restrict__ s0, float* __restrict__ s_final,
+                      float* __restrict__ p_final, int T, int H, int* status) {
+  constexpr int NT = 4, MT = D / 64, NSL = D / BV, TILE = (D / 64) * PANEL;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Wb = smem;                 // [2][TILE]
+  uint8_t* Kb = Wb + 2 * TILE;        // [2][TILE]
+  uint8_t* Us = Kb + 2 * TILE;        // [PANEL]
+  uint8_t* Ss = Us + PANEL;           // [D rows x 128 B]
+  uint8_t* Ups = Ss + D * 128;        // [PANEL]
+  SerialSync* sy = reinterpret_cast<SerialSync*>(Ups + PANEL);
 
   // With p_final the grid has twice the column slices: the second half runs the homogeneous
   // recurrence (U = 0) on the identity, i.e. the span's transfer matrix P = prod (I - K^T W),
   // which context parallelism needs next to the zero-state response.
-  const bool ident = blockIdx.x >= D / BV;
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, v0 = (blockIdx.x % (D / BV)) * BV;
+  const bool ident = blockIdx.x >= NSL;
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, v0 = (blockIdx.x % NSL) * BV;
   const int n = T / CH;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
-  const long long HD = static_cast<long long>(H) * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 0) serial_sync_init(sy);
+  __syncthreads();
+
+  if (warp == 8) {
+    if (lane != 0) return;
+    // ------------------------------------------------------------------ copy thread
+    auto load_wk = [&](int c) {
+      const int st = c & 1, tok0 = b * T + c * CH;
+      mbar_arrive_expect_tx(&sy->full[st], 2 * TILE);
+#pragma unroll
+      for (int pnl = 0; pnl < D / 64; ++pnl) {
+        tma_load_2d(Wb + st * TILE + pnl * PANEL, &tm_w, &sy->full[st], h * D + pnl * 64, tok0);
+        tma_load_2d(Kb + st * TILE + pnl * PANEL, &tm_k, &sy->full[st], h * D + pnl * 64, tok0);
+      }
+    };
+    auto load_u = [&](int c) {
+      mbar_arrive_expect_tx(&sy->full_u, PANEL);
+      tma_load_2d(Us, &tm_u, &sy->full_u, h * D + v0, b * T + c * CH);
+    };
+    load_wk(0);
+    if (!ident) load_u(0);
+    if (n > 1) load_wk(1);
+    for (int c = 0; c < n; ++c) {
+      if (!ident) {
+        ser_wait(sy, &sy->ready_s, c & 1, status);
+        tma_store_2d(&tm_states, Ss, v0, (bh * n + c) * D);
+        ser_wait(sy, &sy->ready_u, c & 1, status);
+        tma_store_2d(&tm_up, Ups, h * D + v0, b * T + c * CH);
+        bulk_commit();
+        if (c + 1 < n) load_u(c + 1);  // the U tile is free once chunk c's U' exists
+        bulk_wait_read<0>();
+        mbar_arrive(&sy->st_free);
+      }
+      if (c + 2 < n) {
+        ser_wait(sy, &sy->empty[c & 1], (c >> 1) & 1, status);
+        load_wk(c + 2);
+      }
+    }
+    bulk_wait<0>();
+    return;
+  }
+
+  // -------------------------------------------------------------------- compute warps
+  const int g = lane >> 2, tg = lane & 3;
+  const int r = warp & 3, half = warp >> 2, cw = 32 * half;
   float sacc[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -170,76 +363,52 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
-        const int col = v0 + nt * 8 + 2 * tg + (e & 1);
+        const int row = r * 16 * MT + mt * 16 + g + (e >> 1) * 8;
+        const int col = v0 + cw + nt * 8 + 2 * tg + (e & 1);
         sacc[mt][nt][e] = ident ? (row == col ? 1.f : 0.f)
                                 : (s0 ? s0[(static_cast<long long>(bh) * D + row) * D + col] : 0.f);
       }
-
-  auto issue_wu = [&](int c) {
-    const long long tok0 = static_cast<long long>(b) * T + c * CH;
-    tile_load_async<D, 128>(Ws, LD, w + tok0 * HD + h * D, HD, CH);
-    if (!ident) tile_load_async<BV, 128>(Us, LDV, u + tok0 * HD + h * D + v0, HD, CH);
-  };
-  auto issue_k = [&](int c) {
-    const long long tok0 = static_cast<long long>(b) * T + c * CH;
-    tile_load_async<D, 128>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-  };
-  issue_wu(0);
-  cp_async_commit();
-  issue_k(0);
-  cp_async_commit();
+  const SwzTile St = swz_tile(Ss, D), Ut = swz_tile(Us, CH), Upt = swz_tile(Ups, CH);
 
   for (int c = 0; c < n; ++c) {
+    const SwzTile Wt = swz_tile(Wb + (c & 1) * TILE, CH), Kt = swz_tile(Kb + (c & 1) * TILE, CH);
     // snapshot of the state entering chunk c: bf16 MMA operand + saved for O and backward
-    bf16* sg = states + ((static_cast<long long>(bh) * n + c) * D) * D + v0;
+    if (!ident && c > 0) ser_wait(sy, &sy->st_free, (c - 1) & 1, status);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int r0 = warp * 16 * MT + mt * 16;
-      frag_store_bf16<NT>(Ss + r0 * LDV, LDV, sacc[mt]);
-      if (!ident) frag_store_bf16<NT>(sg + static_cast<long long>(r0) * D, D, sacc[mt]);
-    }
-    cp_async_wait<1>();
-    __syncthreads();
+    for (int mt = 0; mt < MT; ++mt) frag_store_swz<NT>(St, r * 16 * MT + mt * 16, cw, sacc[mt]);
+    if (!ident) fence_proxy_async_smem();
+    compute_bar_sync();
+    if (!ident && threadIdx.x == 0) mbar_arrive(&sy->ready_s);
+    ser_wait(sy, &sy->full[c & 1], (c >> 1) & 1, status);
     {
-      float acc[NT][4];
-      zero_acc<NT>(acc);
-      warp_gemm<NT, D, false, true>(acc, Ws + 16 * warp * LD, LD, Ss, LDV);
-      const long long tok0 = static_cast<long long>(b) * T + c * CH;
+      float acc[1][NT][4];
+      zero_acc<NT>(acc[0]);
+      warp_gemm_swz<1, NT, D, false, true>(acc, Wt, 16 * r, St, cw);
+      if (!ident) ser_wait(sy, &sy->full_u, c & 1, status);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const int row = 16 * warp + g + hf * 8, col = nt * 8 + 2 * tg;
-          const float2 uu = ident ? make_float2(0.f, 0.f)
-                                  : __bfloat1622float2(*reinterpret_cast<const bf162*>(
-                                        Us + row * LDV + col));
-          const bf162 r = __floats2bfloat162_rn(uu.x - acc[nt][2 * hf], uu.y - acc[nt][2 * hf + 1]);
-          *reinterpret_cast<bf162*>(Ups + row * LDV + col) = r;
-          if (!ident) *reinterpret_cast<bf162*>(up + (tok0 + row) * HD + h * D + v0 + col) = r;
+          const int row = 16 * r + g + hf * 8, col = cw + nt * 8 + 2 * tg;
+          const float2 uu = ident ? make_float2(0.f, 0.f) : lds_bf162(Ut.at(row, col));
+          sts_bf162(Upt.at(row, col), uu.x - acc[0][nt][2 * hf], uu.y - acc[0][nt][2 * hf + 1]);
         }
     }
-    __syncthreads();
-    if (c + 1 < n) issue_wu(c + 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-      warp_gemm<NT, CH, true, true>(sacc[mt], Ks + warp * 16 * MT + mt * 16, LD, Ups, LDV);
-    __syncthreads();
-    if (c + 1 < n) issue_k(c + 1);
-    cp_async_commit();
+    if (!ident) fence_proxy_async_smem();
+    compute_bar_sync();
+    if (!ident && threadIdx.x == 0) mbar_arrive(&sy->ready_u);
+    warp_gemm_swz<MT, NT, CH, true, true>(sacc, Kt, r * 16 * MT, Upt, cw);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sy->empty[c & 1]);
   }
-  cp_async_wait<0>();
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
-        const int col = v0 + nt * 8 + 2 * tg + (e & 1);
+        const int row = r * 16 * MT + mt * 16 + g + (e >> 1) * 8;
+        const int col = v0 + cw + nt * 8 + 2 * tg + (e & 1);
         (ident ? p_final : s_final)[(static_cast<long long>(bh) * D + row) * D + col] =
             sacc[mt][nt][e];
       }
@@ -247,147 +416,231 @@ efla_state_fwd_kernel(const bf16* __restrict__ k, const bf16* __restrict__ w,
 
 // ================================================================ forward: O
 template <int D>
-__global__ void __launch_bounds__(256)
-efla_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
-                const bf16* __restrict__ up, const bf16* __restrict__ states,
-                bf16* __restrict__ o, int T, int H, long long qs, long long ks) {
-  constexpr int LD = D + 8, NT = D / 16;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem);
-  bf16* Ks = Qs + CH * LD;
-  bf16* Ups = Ks + CH * LD;
-  bf16* Sb = Ups + CH * LD;
-  bf16* Ps = Sb + D * LD;
+__global__ void __launch_bounds__(256, 2)
+efla_out_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_up,
+                const __grid_constant__ CUtensorMap tm_states, bf16* __restrict__ o, int T, int H,
+                int* status) {
+  constexpr int NT = D / 16, TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Qs = smem;
+  uint8_t* Ks = Qs + TILE;
+  uint8_t* Ups = Ks + TILE;
+  uint8_t* Sb = Ups + TILE;
+  uint8_t* Ps = Sb + STILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + PANEL);
 
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H, n = T / CH;
-  const long long tok0 = static_cast<long long>(b) * T + blockIdx.x * CH;
+  const int tok0 = b * T + blockIdx.x * CH;
   const long long HD = static_cast<long long>(H) * D;
-  tile_load_async<D, 256>(Qs, LD, q + tok0 * qs + h * D, qs, CH);
-  tile_load_async<D, 256>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-  tile_load_async<D, 256>(Ups, LD, up + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(Sb, LD, states + (static_cast<long long>(bh) * n + blockIdx.x) * D * D, D,
-                          D);
-  cp_async_commit();
-  cp_async_wait<0>();
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 2);
+    mbar_init(&bars[1], 2);
+    fence_mbar_init();
+  }
   __syncthreads();
+  // one thread per tile requests it (a TMA instruction is slow to issue; spread them)
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Qs, &tm_q, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 32) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Ks, &tm_k, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 64) {
+    mbar_arrive_expect_tx(&bars[1], TILE);
+    tma_tok_tile<D>(Ups, &tm_up, &bars[1], h * D, tok0);
+  } else if (threadIdx.x == 96) {
+    mbar_arrive_expect_tx(&bars[1], STILE);
+    tma_state_tile<D>(Sb, &tm_states, &bars[1], (bh * n + blockIdx.x) * D);
+  }
+  tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int r = warp & 3, half = warp >> 2;
+  const SwzTile Qt = swz_tile(Qs, CH), Kt = swz_tile(Ks, CH), Upt = swz_tile(Ups, CH),
+                St = swz_tile(Sb, D), Pt = swz_tile(Ps, CH);
   {
     float acc[4][4];
     zero_acc<4>(acc);
-    warp_gemm<4, D, false, false>(acc, Qs + 16 * r * LD, LD, Ks + 32 * half * LD, LD);
+    wg<4, D, false, false>(acc, Qt, 16 * r, Kt, 32 * half);
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
-        const float p0 = col <= row ? acc[nt][2 * hf] : 0.f;
-        const float p1 = col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f;
-        *reinterpret_cast<bf162*>(Ps + row * XLD + col) = __floats2bfloat162_rn(p0, p1);
+        sts_bf162(Pt.at(row, col), col <= row ? acc[nt][2 * hf] : 0.f,
+                  col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f);
       }
   }
+  tile_wait(&bars[1], status);
   __syncthreads();
   const int c0 = (D / 2) * half;
   float acc[NT][4];
   zero_acc<NT>(acc);
-  warp_gemm<NT, D, false, true>(acc, Qs + 16 * r * LD, LD, Sb + c0, LD);
-  warp_gemm<NT, CH, false, true>(acc, Ps + 16 * r * XLD, XLD, Ups + c0, LD);
-  frag_store_bf16<NT>(o + (tok0 + 16 * r) * HD + h * D + c0, HD, acc);
+  wg<NT, D, false, true>(acc, Qt, 16 * r, St, c0);
+  wg<NT, CH, false, true>(acc, Pt, 16 * r, Upt, c0);
+  frag_store_bf16<NT>(o + (static_cast<long long>(tok0) + 16 * r) * HD + h * D + c0, HD, acc);
 }
 
 // ============================================== backward: dQ and D = P^T dO
 template <int D>
-__global__ void __launch_bounds__(256)
-efla_bwd_local_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
-                      const bf16* __restrict__ up, const bf16* __restrict__ states,
-                      const bf16* __restrict__ dO, bf16* __restrict__ dq,
-                      bf16* __restrict__ dloc, int T, int H, long long qs, long long ks,
-                      long long dqs) {
-  constexpr int LD = D + 8, NT = D / 16;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem);
-  bf16* Ks = Qs + CH * LD;
-  bf16* Ups = Ks + CH * LD;
-  bf16* dOs = Ups + CH * LD;
-  bf16* Sb = dOs + CH * LD;
-  bf16* Ps = Sb + D * LD;
-  bf16* dPs = Ps + CH * XLD;
+__global__ void __launch_bounds__(256, 2)
+efla_bwd_local_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_up,
+                      const __grid_constant__ CUtensorMap tm_dO,
+                      const __grid_constant__ CUtensorMap tm_states, bf16* __restrict__ dq,
+                      bf16* __restrict__ dloc, int T, int H, long long dqs, int* status) {
+  constexpr int NT = D / 16, TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Qs = smem;
+  uint8_t* Ks = Qs + TILE;
+  uint8_t* Ups = Ks + TILE;
+  uint8_t* dOs = Ups + TILE;
+  uint8_t* Sb = dOs + TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Sb + STILE);
+  uint8_t* Ps = Qs;    // P and dP replace Q and U' once both products are in registers
+  uint8_t* dPs = Ups;
 
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H, n = T / CH;
-  const long long tok0 = static_cast<long long>(b) * T + blockIdx.x * CH;
+  const int tok0 = b * T + blockIdx.x * CH;
   const long long HD = static_cast<long long>(H) * D;
-  tile_load_async<D, 256>(Qs, LD, q + tok0 * qs + h * D, qs, CH);
-  tile_load_async<D, 256>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-  tile_load_async<D, 256>(Ups, LD, up + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(dOs, LD, dO + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(Sb, LD, states + (static_cast<long long>(bh) * n + blockIdx.x) * D * D, D,
-                          D);
-  cp_async_commit();
-  cp_async_wait<0>();
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 4);
+    mbar_init(&bars[1], 1);
+    fence_mbar_init();
+  }
   __syncthreads();
+  // one thread per tile requests it (a TMA instruction is slow to issue; spread them)
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Qs, &tm_q, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 32) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Ks, &tm_k, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 64) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(Ups, &tm_up, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 96) {
+    mbar_arrive_expect_tx(&bars[0], TILE);
+    tma_tok_tile<D>(dOs, &tm_dO, &bars[0], h * D, tok0);
+  } else if (threadIdx.x == 128) {
+    mbar_arrive_expect_tx(&bars[1], STILE);
+    tma_state_tile<D>(Sb, &tm_states, &bars[1], (bh * n + blockIdx.x) * D);
+  }
+  tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int r = warp & 3, half = warp >> 2;
-#pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    float acc[4][4];
-    zero_acc<4>(acc);
-    if (which == 0)
-      warp_gemm<4, D, false, false>(acc, Qs + 16 * r * LD, LD, Ks + 32 * half * LD, LD);
-    else
-      warp_gemm<4, D, false, false>(acc, dOs + 16 * r * LD, LD, Ups + 32 * half * LD, LD);
-    bf16* dst = which == 0 ? Ps : dPs;
+  const SwzTile Qt = swz_tile(Qs, CH), Kt = swz_tile(Ks, CH), Upt = swz_tile(Ups, CH),
+                dOt = swz_tile(dOs, CH), St = swz_tile(Sb, D), Pt = swz_tile(Ps, CH),
+                dPt = swz_tile(dPs, CH);
+  {
+    float accp[4][4], accd[4][4];
+    zero_acc<4>(accp);
+    zero_acc<4>(accd);
+    wg<4, D, false, false>(accp, Qt, 16 * r, Kt, 32 * half);
+    wg<4, D, false, false>(accd, dOt, 16 * r, Upt, 32 * half);
+    __syncthreads();  // all warps are done with Q and U'
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
-        const float p0 = col <= row ? acc[nt][2 * hf] : 0.f;
-        const float p1 = col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f;
-        *reinterpret_cast<bf162*>(dst + row * XLD + col) = __floats2bfloat162_rn(p0, p1);
+        const bool k0 = col <= row, k1 = col + 1 <= row;
+        sts_bf162(Pt.at(row, col), k0 ? accp[nt][2 * hf] : 0.f, k1 ? accp[nt][2 * hf + 1] : 0.f);
+        sts_bf162(dPt.at(row, col), k0 ? accd[nt][2 * hf] : 0.f, k1 ? accd[nt][2 * hf + 1] : 0.f);
       }
   }
+  tile_wait(&bars[1], status);
   __syncthreads();
   const int c0 = (D / 2) * half;
   {
     float acc[NT][4];
     zero_acc<NT>(acc);
-    warp_gemm<NT, D, false, false>(acc, dOs + 16 * r * LD, LD, Sb + c0 * LD, LD);
-    warp_gemm<NT, CH, false, true>(acc, dPs + 16 * r * XLD, XLD, Ks + c0, LD);
-    frag_store_bf16<NT>(dq + (tok0 + 16 * r) * dqs + h * D + c0, dqs, acc);
+    wg<NT, D, false, false>(acc, dOt, 16 * r, St, c0);
+    wg<NT, CH, false, true>(acc, dPt, 16 * r, Kt, c0);
+    frag_store_bf16<NT>(dq + (static_cast<long long>(tok0) + 16 * r) * dqs + h * D + c0, dqs, acc);
   }
   {
     float acc[NT][4];
     zero_acc<NT>(acc);
-    warp_gemm<NT, CH, true, true>(acc, Ps + 16 * r, XLD, dOs + c0, LD);
-    frag_store_bf16<NT>(dloc + (tok0 + 16 * r) * HD + h * D + c0, HD, acc);
+    wg<NT, CH, true, true>(acc, Pt, 16 * r, dOt, c0);
+    frag_store_bf16<NT>(dloc + (static_cast<long long>(tok0) + 16 * r) * HD + h * D + c0, HD, acc);
   }
 }
 
 // ================================================ backward: reverse recurrence
+// Same structure as the forward recurrence (eight compute warps + one copy warp), walking the
+// chunks from the last to the first.  `dup` receives the NEGATED dU' (the form the recurrence
+// consumes as an MMA operand); efla_bwd_final_kernel flips the sign back.
 template <int D>
-__global__ void __launch_bounds__(128)
-efla_state_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
-                      const bf16* __restrict__ w, const bf16* __restrict__ dO,
-                      const bf16* __restrict__ dloc, const float* __restrict__ ds_final,
-                      bf16* __restrict__ dup, bf16* __restrict__ dstates,
-                      float* __restrict__ ds0, int T, int H, long long qs, long long ks) {
-  constexpr int LD = D + 8, NT = BV / 8, MT = D / 64;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Ks = reinterpret_cast<bf16*>(smem);
-  bf16* Qs = Ks + CH * LD;
-  bf16* Ws = Qs + CH * LD;
-  bf16* Dls = Ws + CH * LD;
-  bf16* dOs = Dls + CH * LDV;
-  bf16* dSs = dOs + CH * LDV;
-  bf16* dUps = dSs + D * LDV;
+__global__ void __launch_bounds__(SER_THREADS, 1)
+efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_dO,
+                      const __grid_constant__ CUtensorMap tm_dloc,
+                      const __grid_constant__ CUtensorMap tm_dup,
+                      const __grid_constant__ CUtensorMap tm_dstates,
+                      const float* __restrict__ ds_final, float* __restrict__ ds0, int T, int H,
+                      int* status) {
+  constexpr int NT = 4, MT = D / 64, TILE = (D / 64) * PANEL;
+  constexpr int STAGE = 3 * TILE + 2 * PANEL;  // K | Q | W | Dl | dO
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* dSs = smem + 2 * STAGE;   // [D rows x 128 B]
+  uint8_t* dUps = dSs + D * 128;     // [PANEL]
+  SerialSync* sy = reinterpret_cast<SerialSync*>(dUps + PANEL);
 
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H, v0 = blockIdx.x * BV;
   const int n = T / CH;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
-  const long long HD = static_cast<long long>(H) * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 0) serial_sync_init(sy);
+  __syncthreads();
+
+  if (warp == 8) {
+    if (lane != 0) return;
+    // step i = n-1-c processes chunk c; its tiles live in stage i & 1
+    auto load = [&](int i) {
+      const int tok0 = b * T + (n - 1 - i) * CH;
+      uint8_t* st = smem + (i & 1) * STAGE;
+      uint64_t* bar = &sy->full[i & 1];
+      mbar_arrive_expect_tx(bar, STAGE);
+#pragma unroll
+      for (int pnl = 0; pnl < D / 64; ++pnl) {
+        tma_load_2d(st + pnl * PANEL, &tm_k, bar, h * D + pnl * 64, tok0);
+        tma_load_2d(st + TILE + pnl * PANEL, &tm_q, bar, h * D + pnl * 64, tok0);
+        tma_load_2d(st + 2 * TILE + pnl * PANEL, &tm_w, bar, h * D + pnl * 64, tok0);
+      }
+      tma_load_2d(st + 3 * TILE, &tm_dloc, bar, h * D + v0, tok0);
+      tma_load_2d(st + 3 * TILE + PANEL, &tm_dO, bar, h * D + v0, tok0);
+    };
+    load(0);
+    if (n > 1) load(1);
+    for (int i = 0; i < n; ++i) {
+      const int c = n - 1 - i;
+      ser_wait(sy, &sy->ready_s, i & 1, status);
+      tma_store_2d(&tm_dstates, dSs, v0, (bh * n + c) * D);
+      ser_wait(sy, &sy->ready_u, i & 1, status);
+      tma_store_2d(&tm_dup, dUps, h * D + v0, b * T + c * CH);
+      bulk_commit();
+      bulk_wait_read<0>();
+      mbar_arrive(&sy->st_free);
+      if (i + 2 < n) {
+        ser_wait(sy, &sy->empty[i & 1], (i >> 1) & 1, status);
+        load(i + 2);
+      }
+    }
+    bulk_wait<0>();
+    return;
+  }
+
+  const int g = lane >> 2, tg = lane & 3;
+  const int r = warp & 3, half = warp >> 2, cw = 32 * half;
   float dacc[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -395,81 +648,56 @@ efla_state_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
-        const int col = v0 + nt * 8 + 2 * tg + (e & 1);
+        const int row = r * 16 * MT + mt * 16 + g + (e >> 1) * 8;
+        const int col = v0 + cw + nt * 8 + 2 * tg + (e & 1);
         dacc[mt][nt][e] =
             ds_final ? ds_final[(static_cast<long long>(bh) * D + row) * D + col] : 0.f;
       }
+  const SwzTile dSt = swz_tile(dSs, D), dUpt = swz_tile(dUps, CH);
 
-  auto issue_a = [&](int c) {
-    const long long tok0 = static_cast<long long>(b) * T + c * CH;
-    tile_load_async<D, 128>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-    tile_load_async<BV, 128>(Dls, LDV, dloc + tok0 * HD + h * D + v0, HD, CH);
-  };
-  auto issue_b = [&](int c) {
-    const long long tok0 = static_cast<long long>(b) * T + c * CH;
-    tile_load_async<D, 128>(Qs, LD, q + tok0 * qs + h * D, qs, CH);
-    tile_load_async<D, 128>(Ws, LD, w + tok0 * HD + h * D, HD, CH);
-    tile_load_async<BV, 128>(dOs, LDV, dO + tok0 * HD + h * D + v0, HD, CH);
-  };
-  issue_a(n - 1);
-  cp_async_commit();
-  issue_b(n - 1);
-  cp_async_commit();
-
-  for (int c = n - 1; c >= 0; --c) {
-    bf16* sg = dstates + ((static_cast<long long>(bh) * n + c) * D) * D + v0;
+  for (int i = 0; i < n; ++i) {
+    uint8_t* st = smem + (i & 1) * STAGE;
+    const SwzTile Kt = swz_tile(st, CH), Qt = swz_tile(st + TILE, CH),
+                  Wt = swz_tile(st + 2 * TILE, CH), Dlt = swz_tile(st + 3 * TILE, CH),
+                  dOt = swz_tile(st + 3 * TILE + PANEL, CH);
+    if (i > 0) ser_wait(sy, &sy->st_free, (i - 1) & 1, status);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int r0 = warp * 16 * MT + mt * 16;
-      frag_store_bf16<NT>(dSs + r0 * LDV, LDV, dacc[mt]);
-      frag_store_bf16<NT>(sg + static_cast<long long>(r0) * D, D, dacc[mt]);
-    }
-    cp_async_wait<1>();
-    __syncthreads();
+    for (int mt = 0; mt < MT; ++mt) frag_store_swz<NT>(dSt, r * 16 * MT + mt * 16, cw, dacc[mt]);
+    fence_proxy_async_smem();
+    compute_bar_sync();
+    if (threadIdx.x == 0) mbar_arrive(&sy->ready_s);
+    ser_wait(sy, &sy->full[i & 1], (i >> 1) & 1, status);
     {
-      float acc[NT][4];
-      zero_acc<NT>(acc);
-      warp_gemm<NT, D, false, true>(acc, Ks + 16 * warp * LD, LD, dSs, LDV);
-      const long long tok0 = static_cast<long long>(b) * T + c * CH;
+      float acc[1][NT][4];
+      zero_acc<NT>(acc[0]);
+      warp_gemm_swz<1, NT, D, false, true>(acc, Kt, 16 * r, dSt, cw);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const int row = 16 * warp + g + hf * 8, col = nt * 8 + 2 * tg;
-          const float2 dl =
-              __bfloat1622float2(*reinterpret_cast<const bf162*>(Dls + row * LDV + col));
-          const float a0 = dl.x + acc[nt][2 * hf], a1 = dl.y + acc[nt][2 * hf + 1];
-          // the recurrence subtracts W^T dU': keep the negated copy as the MMA operand
-          *reinterpret_cast<bf162*>(dUps + row * LDV + col) = __floats2bfloat162_rn(-a0, -a1);
-          *reinterpret_cast<bf162*>(dup + (tok0 + row) * HD + h * D + v0 + col) =
-              __floats2bfloat162_rn(a0, a1);
+          const int row = 16 * r + g + hf * 8, col = cw + nt * 8 + 2 * tg;
+          const float2 dl = lds_bf162(Dlt.at(row, col));
+          // the recurrence subtracts W^T dU': the negated copy is the MMA operand
+          sts_bf162(dUpt.at(row, col), -(dl.x + acc[0][nt][2 * hf]),
+                    -(dl.y + acc[0][nt][2 * hf + 1]));
         }
     }
-    __syncthreads();
-    if (c > 0) issue_a(c - 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int m0 = warp * 16 * MT + mt * 16;
-      warp_gemm<NT, CH, true, true>(dacc[mt], Qs + m0, LD, dOs, LDV);
-      warp_gemm<NT, CH, true, true>(dacc[mt], Ws + m0, LD, dUps, LDV);
-    }
-    __syncthreads();
-    if (c > 0) issue_b(c - 1);
-    cp_async_commit();
+    fence_proxy_async_smem();
+    compute_bar_sync();
+    if (threadIdx.x == 0) mbar_arrive(&sy->ready_u);
+    warp_gemm_swz<MT, NT, CH, true, true>(dacc, Qt, r * 16 * MT, dOt, cw);
+    warp_gemm_swz<MT, NT, CH, true, true>(dacc, Wt, r * 16 * MT, dUpt, cw);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sy->empty[i & 1]);
   }
-  cp_async_wait<0>();
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int row = warp * 16 * MT + mt * 16 + g + (e >> 1) * 8;
-        const int col = v0 + nt * 8 + 2 * tg + (e & 1);
+        const int row = r * 16 * MT + mt * 16 + g + (e >> 1) * 8;
+        const int col = v0 + cw + nt * 8 + 2 * tg + (e & 1);
         ds0[(static_cast<long long>(bh) * D + row) * D + col] = dacc[mt][nt][e];
       }
 }
@@ -477,55 +705,105 @@ efla_state_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
 // ================================================= backward: dK, dV, d(alpha)
 template <int D>
 __global__ void __launch_bounds__(256, 1)
-efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
-                      const bf16* __restrict__ v, const float* __restrict__ alpha,
-                      const bf16* __restrict__ up, const bf16* __restrict__ states,
-                      const bf16* __restrict__ dO, const bf16* __restrict__ dup,
-                      const bf16* __restrict__ dstates, bf16* __restrict__ dk,
+efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_up,
+                      const __grid_constant__ CUtensorMap tm_dO,
+                      const __grid_constant__ CUtensorMap tm_dup,
+                      const __grid_constant__ CUtensorMap tm_states,
+                      const __grid_constant__ CUtensorMap tm_dstates,
+                      const __grid_constant__ CUtensorMap tm_xinv, const bf16* __restrict__ v,
+                      const float* __restrict__ alpha, bf16* __restrict__ dk,
                       bf16* __restrict__ dv, float* __restrict__ dalpha, int T, int H,
-                      long long qs, long long ks, long long vs, long long dks, long long dvs) {
-  constexpr int LD = D + 8, NT = D / 16;
-  extern __shared__ __align__(16) uint8_t smem[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem);
-  bf16* Ks = Qs + CH * LD;
-  bf16* Ups = Ks + CH * LD;
-  bf16* dOs = Ups + CH * LD;
-  bf16* Zs = dOs + CH * LD;  // holds dU' first, then Z
-  bf16* Sb = Zs + CH * LD;   // S_in first, then dS_out
-  float* Gs = reinterpret_cast<float*>(Sb + D * LD);
-  bf16* Xs = reinterpret_cast<bf16*>(Gs + CH * GLD);
-  bf16* dGs = Xs + CH * XLD;
-  bf16* dPs = dGs + CH * XLD;
-  float* al = reinterpret_cast<float*>(dPs + CH * XLD);
+                      long long vs, long long dks, long long dvs, int* status) {
+  constexpr int NT = D / 16, TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Qs = smem;
+  uint8_t* Ks = Qs + TILE;
+  uint8_t* Ups = Ks + TILE;
+  uint8_t* dOs = Ups + TILE;
+  uint8_t* Zs = dOs + TILE;    // holds -dU' first, then Z
+  uint8_t* Sb = Zs + TILE;     // S_in
+  uint8_t* dSb = Sb + STILE;   // dS_out
+  uint8_t* Xs = dSb + STILE;   // X = (I + diag(a) G)^-1 as the forward pass saved it
+  uint8_t* dGs = Xs + PANEL;
+  uint8_t* dPs = dGs + PANEL;
+  float* Gs = reinterpret_cast<float*>(dPs + PANEL);
+  float* al = Gs + CH * GLD;
   float* dal = al + CH;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dal + CH);
 
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H, n = T / CH;
-  const long long tok0 = static_cast<long long>(b) * T + blockIdx.x * CH;
-  const long long HD = static_cast<long long>(H) * D;
-  const long long soff = (static_cast<long long>(bh) * n + blockIdx.x) * D * D;
-  tile_load_async<D, 256>(Qs, LD, q + tok0 * qs + h * D, qs, CH);
-  tile_load_async<D, 256>(Ks, LD, k + tok0 * ks + h * D, ks, CH);
-  tile_load_async<D, 256>(Ups, LD, up + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(dOs, LD, dO + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(Zs, LD, dup + tok0 * HD + h * D, HD, CH);
-  tile_load_async<D, 256>(Sb, LD, states + soff, D, D);
-  cp_async_commit();
+  const int tok0 = b * T + blockIdx.x * CH;
+  const int srow = (bh * n + blockIdx.x) * D;
+  // every tile is requested up front, in the order the steps below need them
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 3);
+    mbar_init(&bars[2], 2);
+    mbar_init(&bars[3], 1);
+    mbar_init(&bars[4], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  // one thread per tile requests it (a TMA instruction is slow to issue; spread them)
+  switch (threadIdx.x) {
+    case 0:
+      mbar_arrive_expect_tx(&bars[0], TILE);
+      tma_tok_tile<D>(Ks, &tm_k, &bars[0], h * D, tok0);
+      break;
+    case 32:
+      mbar_arrive_expect_tx(&bars[1], PANEL);
+      tma_load_2d(Xs, &tm_xinv, &bars[1], 0, (bh * n + blockIdx.x) * CH);
+      break;
+    case 64:
+      mbar_arrive_expect_tx(&bars[1], TILE);
+      tma_tok_tile<D>(Zs, &tm_dup, &bars[1], h * D, tok0);
+      break;
+    case 96:
+      mbar_arrive_expect_tx(&bars[1], STILE);
+      tma_state_tile<D>(Sb, &tm_states, &bars[1], srow);
+      break;
+    case 128:
+      mbar_arrive_expect_tx(&bars[2], TILE);
+      tma_tok_tile<D>(Ups, &tm_up, &bars[2], h * D, tok0);
+      break;
+    case 160:
+      mbar_arrive_expect_tx(&bars[2], TILE);
+      tma_tok_tile<D>(dOs, &tm_dO, &bars[2], h * D, tok0);
+      break;
+    case 192:
+      mbar_arrive_expect_tx(&bars[3], TILE);
+      tma_tok_tile<D>(Qs, &tm_q, &bars[3], h * D, tok0);
+      break;
+    case 224:
+      mbar_arrive_expect_tx(&bars[4], STILE);
+      tma_state_tile<D>(dSb, &tm_dstates, &bars[4], srow);
+      break;
+    default:
+      break;
+  }
   if (threadIdx.x < CH) {
-    al[threadIdx.x] = alpha[(tok0 + threadIdx.x) * H + h];
+    al[threadIdx.x] = alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h];
     dal[threadIdx.x] = 0.f;
   }
-  cp_async_wait<0>();
   __syncthreads();
+  tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int r = warp & 3, half = warp >> 2;
   const int c0 = (D / 2) * half;
+  const SwzTile Qt = swz_tile(Qs, CH), Kt = swz_tile(Ks, CH), Upt = swz_tile(Ups, CH),
+                dOt = swz_tile(dOs, CH), Zt = swz_tile(Zs, CH), St = swz_tile(Sb, D),
+                dSt = swz_tile(dSb, D), Xt = swz_tile(Xs, CH), dGt = swz_tile(dGs, CH),
+                dPt = swz_tile(dPs, CH);
 
-  // 1. G = K K^T, strictly lower part, fp32
+  // 1. G = K K^T, strictly lower part, fp32 (step 4 needs it for d(alpha))
   {
     float acc[4][4];
     zero_acc<4>(acc);
-    warp_gemm<4, D, false, false>(acc, Ks + 16 * r * LD, LD, Ks + 32 * half * LD, LD);
+    wg<4, D, false, false>(acc, Kt, 16 * r, Kt, 32 * half);
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -535,35 +813,32 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
       }
   }
   __syncthreads();
-  // 2. X = (I + diag(a) G)^-1
-  if (threadIdx.x < CH) {
-    float x[CH];
-    const int c = threadIdx.x;
-    solve_column(Gs, al, c, x);
-#pragma unroll
-    for (int i = 0; i < CH; ++i) Xs[i * XLD + c] = __float2bfloat16(x[i]);
-  }
-  __syncthreads();
+  tile_wait(&bars[1], status);
   // 3. Z = X^T dU' ; R = V - K S_in ; dV = a Z ; d(alpha) += Z . R
   float zacc[NT][4];
   zero_acc<NT>(zacc);
-  warp_gemm<NT, CH, true, true>(zacc, Xs + 16 * r, XLD, Zs + c0, LD);
+  wg<NT, CH, true, true>(zacc, Xt, 16 * r, Zt, c0);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)  // `dup` holds -dU'
+#pragma unroll
+    for (int e = 0; e < 4; ++e) zacc[nt][e] = -zacc[nt][e];
   {
     float racc[NT][4];
     zero_acc<NT>(racc);
-    warp_gemm<NT, D, false, true>(racc, Ks + 16 * r * LD, LD, Sb + c0, LD);
+    wg<NT, D, false, true>(racc, Kt, 16 * r, St, c0);
     float p[2] = {0.f, 0.f};
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = c0 + nt * 8 + 2 * tg;
-        const float2 vv = __bfloat1622float2(
-            *reinterpret_cast<const bf162*>(v + (tok0 + row) * vs + h * D + col));
+        const long long tok = static_cast<long long>(tok0) + row;
+        const float2 vv =
+            __bfloat1622float2(*reinterpret_cast<const bf162*>(v + tok * vs + h * D + col));
         p[hf] += zacc[nt][2 * hf] * (vv.x - racc[nt][2 * hf]) +
                  zacc[nt][2 * hf + 1] * (vv.y - racc[nt][2 * hf + 1]);
         const float a = al[row];
-        *reinterpret_cast<bf162*>(dv + (tok0 + row) * dvs + h * D + col) =
+        *reinterpret_cast<bf162*>(dv + tok * dvs + h * D + col) =
             __floats2bfloat162_rn(a * zacc[nt][2 * hf], a * zacc[nt][2 * hf + 1]);
       }
 #pragma unroll
@@ -574,14 +849,15 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
       if (tg == 0) atomicAdd(&dal[16 * r + g + hf * 8], s);
     }
   }
-  __syncthreads();  // every warp is done reading dU' out of Zs
-  frag_store_bf16<NT>(Zs + 16 * r * LD + c0, LD, zacc);
+  __syncthreads();  // every warp is done reading dU' out of Zs and X out of the first panel
+  frag_store_swz<NT>(Zt, 16 * r, c0, zacc);
+  tile_wait(&bars[2], status);
   __syncthreads();
   // 4. dA = -strict_tril(Z U'^T) ; d(alpha) += dA . G ; dG = a dA ;  dP = tril(dO U'^T)
   {
     float acc[4][4];
     zero_acc<4>(acc);
-    warp_gemm<4, D, false, false>(acc, Zs + 16 * r * LD, LD, Ups + 32 * half * LD, LD);
+    wg<4, D, false, false>(acc, Zt, 16 * r, Upt, 32 * half);
     float p[2] = {0.f, 0.f};
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
@@ -589,10 +865,10 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
         const float a = al[row];
-        float d0 = col < row ? -acc[nt][2 * hf] : 0.f;
-        float d1 = col + 1 < row ? -acc[nt][2 * hf + 1] : 0.f;
+        const float d0 = col < row ? -acc[nt][2 * hf] : 0.f;
+        const float d1 = col + 1 < row ? -acc[nt][2 * hf + 1] : 0.f;
         p[hf] += d0 * Gs[row * GLD + col] + d1 * Gs[row * GLD + col + 1];
-        *reinterpret_cast<bf162*>(dGs + row * XLD + col) = __floats2bfloat162_rn(a * d0, a * d1);
+        sts_bf162(dGt.at(row, col), a * d0, a * d1);
       }
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
@@ -602,37 +878,34 @@ efla_bwd_final_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
       if (tg == 0) atomicAdd(&dal[16 * r + g + hf * 8], s);
     }
     zero_acc<4>(acc);
-    warp_gemm<4, D, false, false>(acc, dOs + 16 * r * LD, LD, Ups + 32 * half * LD, LD);
+    wg<4, D, false, false>(acc, dOt, 16 * r, Upt, 32 * half);
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
-        const float p0 = col <= row ? acc[nt][2 * hf] : 0.f;
-        const float p1 = col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f;
-        *reinterpret_cast<bf162*>(dPs + row * XLD + col) = __floats2bfloat162_rn(p0, p1);
+        sts_bf162(dPt.at(row, col), col <= row ? acc[nt][2 * hf] : 0.f,
+                  col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f);
       }
   }
+  tile_wait(&bars[3], status);
   __syncthreads();
   // 5. dK = -a (Z S_in^T) + dG K + dG^T K + dP^T Q + U' dS_out^T
   float kacc[NT][4];
   zero_acc<NT>(kacc);
-  warp_gemm<NT, D, false, false>(kacc, Zs + 16 * r * LD, LD, Sb + c0 * LD, LD);
+  wg<NT, D, false, false>(kacc, Zt, 16 * r, St, c0);
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) kacc[nt][e] *= -al[16 * r + g + (e >> 1) * 8];
-  warp_gemm<NT, CH, false, true>(kacc, dGs + 16 * r * XLD, XLD, Ks + c0, LD);
-  warp_gemm<NT, CH, true, true>(kacc, dGs + 16 * r, XLD, Ks + c0, LD);
-  warp_gemm<NT, CH, true, true>(kacc, dPs + 16 * r, XLD, Qs + c0, LD);
-  __syncthreads();  // S_in no longer needed: reuse the buffer for dS_out
-  tile_load_async<D, 256>(Sb, LD, dstates + soff, D, D);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-  warp_gemm<NT, D, false, false>(kacc, Ups + 16 * r * LD, LD, Sb + c0 * LD, LD);
-  frag_store_bf16<NT>(dk + (tok0 + 16 * r) * dks + h * D + c0, dks, kacc);
-  if (threadIdx.x < CH) dalpha[(tok0 + threadIdx.x) * H + h] = dal[threadIdx.x];
+  wg<NT, CH, false, true>(kacc, dGt, 16 * r, Kt, c0);
+  wg<NT, CH, true, true>(kacc, dGt, 16 * r, Kt, c0);
+  wg<NT, CH, true, true>(kacc, dPt, 16 * r, Qt, c0);
+  tile_wait(&bars[4], status);
+  wg<NT, D, false, false>(kacc, Upt, 16 * r, dSt, c0);
+  frag_store_bf16<NT>(dk + (static_cast<long long>(tok0) + 16 * r) * dks + h * D + c0, dks, kacc);
+  if (threadIdx.x < CH)
+    dalpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h] = dal[threadIdx.x];
 }
 
 // ===================================================== q/k normalisation + coefficient
@@ -767,64 +1040,131 @@ efla_prep_bwd_kernel(const bf16* __restrict__ dqn, const bf16* __restrict__ dkn,
 }
 
 // ------------------------------------------------------------------ host side
-template <int D> constexpr int smem_wy() { return 2 * CH * (D + 8) * 2 + CH * GLD * 4 + CH * XLD * 2 + CH * 4; }
-template <int D> constexpr int smem_state_fwd() { return 2 * CH * (D + 8) * 2 + CH * LDV * 2 + D * LDV * 2 + CH * LDV * 2; }
-template <int D> constexpr int smem_out() { return 3 * CH * (D + 8) * 2 + D * (D + 8) * 2 + CH * XLD * 2; }
-template <int D> constexpr int smem_bwd_local() { return 4 * CH * (D + 8) * 2 + D * (D + 8) * 2 + 2 * CH * XLD * 2; }
-template <int D> constexpr int smem_state_bwd() { return 3 * CH * (D + 8) * 2 + 2 * CH * LDV * 2 + D * LDV * 2 + CH * LDV * 2; }
-template <int D> constexpr int smem_bwd_final() { return 5 * CH * (D + 8) * 2 + D * (D + 8) * 2 + CH * GLD * 4 + 3 * CH * XLD * 2 + 2 * CH * 4; }
+constexpr int BAR_BYTES = 64;  // up to eight mbarriers
+template <int D> constexpr int tile_bytes() { return (D / 64) * PANEL; }
+template <int D> constexpr int stile_bytes() { return (D / 64) * D * 128; }
+template <int D> constexpr int smem_wy() { return 2 * tile_bytes<D>() + PANEL + CH * GLD * 4 + CH * 4 + BAR_BYTES + 1024; }
+template <int D> constexpr int smem_state_fwd() { return 4 * tile_bytes<D>() + 2 * PANEL + D * 128 + static_cast<int>(sizeof(SerialSync)) + 1024; }
+template <int D> constexpr int smem_out() { return 3 * tile_bytes<D>() + stile_bytes<D>() + PANEL + BAR_BYTES + 1024; }
+template <int D> constexpr int smem_bwd_local() { return 4 * tile_bytes<D>() + stile_bytes<D>() + BAR_BYTES + 1024; }
+template <int D> constexpr int smem_state_bwd() { return 2 * (3 * tile_bytes<D>() + 2 * PANEL) + D * 128 + PANEL + static_cast<int>(sizeof(SerialSync)) + 1024; }
+template <int D> constexpr int smem_bwd_final() { return 5 * tile_bytes<D>() + 2 * stile_bytes<D>() + 3 * PANEL + CH * GLD * 4 + 2 * CH * 4 + BAR_BYTES + 1024; }
 
 template <typename Kern>
 static cudaError_t set_smem(Kern kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
-
 template <int D>
-static int efla_fwd_impl(const bf16* q, const bf16* k, const bf16* v, const float* alpha,
-                         const float* s0, bf16* w, bf16* up, bf16* states, bf16* o, float* s_final,
-                         int B, int T, int H, long long qs, long long ks, long long vs,
-                         cudaStream_t st) {
+static cudaError_t efla_configure() {
   static bool cfg = false;
-  if (!cfg) {
-    cudaError_t e;
-    if ((e = set_smem(efla_wy_kernel<D>, smem_wy<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_state_fwd_kernel<D>, smem_state_fwd<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_out_kernel<D>, smem_out<D>())) != cudaSuccess) return e;
-    cfg = true;
-  }
-  const int n = T / CH;
-  dim3 gpar(n, B * H), gser(D / BV, B * H);
-  // U is staged in `o` (same shape, overwritten by the last kernel)
-  efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(k, v, alpha, w, o, T, H, ks, vs);
-  efla_state_fwd_kernel<D><<<gser, 128, smem_state_fwd<D>(), st>>>(k, w, o, s0, up, states,
-                                                                    s_final, nullptr, T, H, ks);
-  efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(q, k, up, states, o, T, H, qs, ks);
-  return static_cast<int>(cudaGetLastError());
+  if (cfg) return cudaSuccess;
+  cudaError_t e;
+  if ((e = set_smem(efla_wy_kernel<D>, smem_wy<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_state_fwd_kernel<D>, smem_state_fwd<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_out_kernel<D>, smem_out<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
+  cfg = true;
+  return cudaSuccess;
 }
 
+// Every tensor a stage touches through TMA, by the slot numbers of ceo_efla_stage.
+struct EflaTensors {
+  const void* p[24];
+  long long stride[6];  // q, k, v, dq, dk, dv
+};
+enum { I_Q = 0, I_K, I_V, I_ALPHA, I_W, I_U, I_UP, I_STATES, I_O, I_S0, I_SFINAL, I_DO, I_DLOC,
+       I_DUP, I_DSTATES, I_DSFINAL, I_DS0, I_DQ, I_DK, I_DV, I_DALPHA, I_PFINAL, I_STATUS, I_XINV };
+
 template <int D>
-static int efla_bwd_impl(const bf16* q, const bf16* k, const bf16* v, const float* alpha,
-                         const bf16* w, const bf16* up, const bf16* states, const bf16* dO,
-                         const float* ds_final, bf16* dloc, bf16* dup, bf16* dstates, bf16* dq,
-                         bf16* dk, bf16* dv, float* dalpha, float* ds0, int B, int T, int H,
-                         long long qs, long long ks, long long vs, long long dqs, long long dks,
-                         long long dvs, cudaStream_t st) {
-  static bool cfg = false;
-  if (!cfg) {
-    cudaError_t e;
-    if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
-    cfg = true;
-  }
+static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, cudaStream_t st) {
+  if (efla_configure<D>() != cudaSuccess) return static_cast<int>(cudaGetLastError());
   const int n = T / CH;
-  dim3 gpar(n, B * H), gser(D / BV, B * H);
-  efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(q, k, up, states, dO, dq, dloc,
-                                                                    T, H, qs, ks, dqs);
-  efla_state_bwd_kernel<D><<<gser, 128, smem_state_bwd<D>(), st>>>(q, k, w, dO, dloc, ds_final, dup,
-                                                                    dstates, ds0, T, H, qs, ks);
-  efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
-      q, k, v, alpha, up, states, dO, dup, dstates, dk, dv, dalpha, T, H, qs, ks, vs, dks, dvs);
+  const long long tokens = static_cast<long long>(B) * T, HD = static_cast<long long>(H) * D;
+  const long long srows = static_cast<long long>(B) * H * n * D;
+  if (tokens > 0x7fffffffll || srows > 0x7fffffffll) return -5;
+  auto b16 = [&](int i) { return static_cast<bf16*>(const_cast<void*>(t.p[i])); };
+  auto f32 = [&](int i) { return static_cast<float*>(const_cast<void*>(t.p[i])); };
+  int* status = static_cast<int*>(const_cast<void*>(t.p[I_STATUS]));
+  // token-major map of slot i (leading dimension: its token stride), state map of slot i
+  auto tok = [&](CUtensorMap* tm, int i, long long stride) {
+    if (!t.p[i] || (reinterpret_cast<uintptr_t>(t.p[i]) & 15) || (stride & 7)) return -2;
+    return encode_tmap_2d_bf16(tm, t.p[i], static_cast<uint64_t>(HD), tokens, stride, CH) ? -3 : 0;
+  };
+  auto sta = [&](CUtensorMap* tm, int i) {
+    if (!t.p[i] || (reinterpret_cast<uintptr_t>(t.p[i]) & 15)) return -2;
+    return encode_tmap_2d_bf16(tm, t.p[i], D, srows, D, D) ? -3 : 0;
+  };
+  const dim3 gpar(n, B * H);
+  CUtensorMap m[8];
+  int rc = 0;
+#define MAP(call) if ((rc = (call)) != 0) return rc
+  switch (stage) {
+    case 0:
+      MAP(tok(&m[0], I_K, t.stride[1]));
+      MAP(tok(&m[1], I_V, t.stride[2]));
+      if (!t.p[I_XINV]) return -5;
+      efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(m[0], m[1], f32(I_ALPHA), b16(I_W),
+                                                         b16(I_U), b16(I_XINV), T, H, status);
+      break;
+    case 1:
+      MAP(tok(&m[0], I_K, t.stride[1]));
+      MAP(tok(&m[1], I_W, HD));
+      MAP(tok(&m[2], I_U, HD));
+      MAP(tok(&m[3], I_UP, HD));
+      MAP(sta(&m[4], I_STATES));
+      efla_state_fwd_kernel<D><<<dim3(t.p[I_PFINAL] ? 2 * (D / BV) : D / BV, B * H), SER_THREADS,
+                                 smem_state_fwd<D>(), st>>>(
+          m[0], m[1], m[2], m[3], m[4], f32(I_S0), f32(I_SFINAL), f32(I_PFINAL), T, H, status);
+      break;
+    case 2:
+      MAP(tok(&m[0], I_Q, t.stride[0]));
+      MAP(tok(&m[1], I_K, t.stride[1]));
+      MAP(tok(&m[2], I_UP, HD));
+      MAP(sta(&m[3], I_STATES));
+      efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(m[0], m[1], m[2], m[3], b16(I_O), T, H,
+                                                           status);
+      break;
+    case 3:
+      MAP(tok(&m[0], I_Q, t.stride[0]));
+      MAP(tok(&m[1], I_K, t.stride[1]));
+      MAP(tok(&m[2], I_UP, HD));
+      MAP(tok(&m[3], I_DO, HD));
+      MAP(sta(&m[4], I_STATES));
+      efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(
+          m[0], m[1], m[2], m[3], m[4], b16(I_DQ), b16(I_DLOC), T, H, t.stride[3], status);
+      break;
+    case 4:
+      MAP(tok(&m[0], I_Q, t.stride[0]));
+      MAP(tok(&m[1], I_K, t.stride[1]));
+      MAP(tok(&m[2], I_W, HD));
+      MAP(tok(&m[3], I_DO, HD));
+      MAP(tok(&m[4], I_DLOC, HD));
+      MAP(tok(&m[5], I_DUP, HD));
+      MAP(sta(&m[6], I_DSTATES));
+      efla_state_bwd_kernel<D><<<dim3(D / BV, B * H), SER_THREADS, smem_state_bwd<D>(), st>>>(
+          m[0], m[1], m[2], m[3], m[4], m[5], m[6], f32(I_DSFINAL), f32(I_DS0), T, H, status);
+      break;
+    case 5:
+      MAP(tok(&m[0], I_Q, t.stride[0]));
+      MAP(tok(&m[1], I_K, t.stride[1]));
+      MAP(tok(&m[2], I_UP, HD));
+      MAP(tok(&m[3], I_DO, HD));
+      MAP(tok(&m[4], I_DUP, HD));
+      MAP(sta(&m[5], I_STATES));
+      MAP(sta(&m[6], I_DSTATES));
+      if (!t.p[I_XINV] || (reinterpret_cast<uintptr_t>(t.p[I_XINV]) & 15)) return -2;
+      MAP(encode_tmap_2d_bf16(&m[7], t.p[I_XINV], CH, static_cast<uint64_t>(B) * H * n * CH, CH, CH)
+              ? -3 : 0);
+      efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
+          m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], b16(I_V), f32(I_ALPHA), b16(I_DK), b16(I_DV),
+          f32(I_DALPHA), T, H, t.stride[2], t.stride[4], t.stride[5], status);
+      break;
+    default:
+      return -5;
+  }
+#undef MAP
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -837,48 +1177,48 @@ static bool efla_args_ok(int B, int T, int H, int D, long long qs, long long ks,
 using namespace ceo;
 
 extern "C" int ceo_efla_fwd(const void* q, const void* k, const void* v, const float* alpha,
-                            const float* s0, void* w, void* up, void* states, void* o,
+                            const float* s0, void* w, void* up, void* states, void* xinv, void* o,
                             float* s_final, int B, int T, int H, int D, long long q_stride,
                             long long k_stride, long long v_stride, int* status,
                             cudaStream_t stream) {
-  (void)status;
   if (!efla_args_ok(B, T, H, D, q_stride, k_stride, v_stride)) return -5;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
-       reinterpret_cast<uintptr_t>(v)) & 15)
-    return -2;
-#define CEO_EFLA_FWD(DD)                                                                        \
-  return efla_fwd_impl<DD>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),            \
-                           static_cast<const bf16*>(v), alpha, s0, static_cast<bf16*>(w),       \
-                           static_cast<bf16*>(up), static_cast<bf16*>(states),                  \
-                           static_cast<bf16*>(o), s_final, B, T, H, q_stride, k_stride, v_stride, \
-                           stream)
-  if (D == 64) CEO_EFLA_FWD(64);
-  CEO_EFLA_FWD(128);
-#undef CEO_EFLA_FWD
+  EflaTensors t = {};
+  t.p[I_Q] = q; t.p[I_K] = k; t.p[I_V] = v; t.p[I_ALPHA] = alpha; t.p[I_W] = w;
+  t.p[I_U] = o;  // U is staged in `o` (same shape, overwritten by the last kernel)
+  t.p[I_UP] = up; t.p[I_STATES] = states; t.p[I_O] = o; t.p[I_S0] = s0; t.p[I_SFINAL] = s_final;
+  t.p[I_STATUS] = status; t.p[I_XINV] = xinv;
+  t.stride[0] = q_stride; t.stride[1] = k_stride; t.stride[2] = v_stride;
+  for (int stage = 0; stage < 3; ++stage) {
+    const int rc = D == 64 ? efla_run_stage<64>(stage, t, B, T, H, stream)
+                           : efla_run_stage<128>(stage, t, B, T, H, stream);
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 extern "C" int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha,
-                            const void* w, const void* up, const void* states, const void* dO,
-                            const float* ds_final, void* dloc, void* dup, void* dstates, void* dq,
+                            const void* w, const void* up, const void* states, const void* xinv,
+                            const void* dO, const float* ds_final, void* dloc, void* dup,
+                            void* dstates, void* dq,
                             void* dk, void* dv, float* dalpha, float* ds0, int B, int T, int H,
                             int D, long long q_stride, long long k_stride, long long v_stride,
                             long long dq_stride, long long dk_stride, long long dv_stride,
                             int* status, cudaStream_t stream) {
-  (void)status;
   if (!efla_args_ok(B, T, H, D, q_stride, k_stride, v_stride)) return -5;
   if ((dq_stride | dk_stride | dv_stride) & 1) return -2;
-#define CEO_EFLA_BWD(DD)                                                                         \
-  return efla_bwd_impl<DD>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),             \
-                           static_cast<const bf16*>(v), alpha, static_cast<const bf16*>(w),      \
-                           static_cast<const bf16*>(up), static_cast<const bf16*>(states),       \
-                           static_cast<const bf16*>(dO), ds_final, static_cast<bf16*>(dloc),     \
-                           static_cast<bf16*>(dup), static_cast<bf16*>(dstates),                 \
-                           static_cast<bf16*>(dq), static_cast<bf16*>(dk), static_cast<bf16*>(dv), \
-                           dalpha, ds0, B, T, H, q_stride, k_stride, v_stride, dq_stride,   \
-                           dk_stride, dv_stride, stream)
-  if (D == 64) CEO_EFLA_BWD(64);
-  CEO_EFLA_BWD(128);
-#undef CEO_EFLA_BWD
+  EflaTensors t = {};
+  t.p[I_Q] = q; t.p[I_K] = k; t.p[I_V] = v; t.p[I_ALPHA] = alpha; t.p[I_W] = w; t.p[I_UP] = up;
+  t.p[I_STATES] = states; t.p[I_DO] = dO; t.p[I_DSFINAL] = ds_final; t.p[I_DLOC] = dloc;
+  t.p[I_DUP] = dup; t.p[I_DSTATES] = dstates; t.p[I_DQ] = dq; t.p[I_DK] = dk; t.p[I_DV] = dv;
+  t.p[I_DALPHA] = dalpha; t.p[I_DS0] = ds0; t.p[I_STATUS] = status; t.p[I_XINV] = xinv;
+  t.stride[0] = q_stride; t.stride[1] = k_stride; t.stride[2] = v_stride;
+  t.stride[3] = dq_stride; t.stride[4] = dk_stride; t.stride[5] = dv_stride;
+  for (int stage = 3; stage < 6; ++stage) {
+    const int rc = D == 64 ? efla_run_stage<64>(stage, t, B, T, H, stream)
+                           : efla_run_stage<128>(stage, t, B, T, H, stream);
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 extern "C" int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta, int beta_scalar,
@@ -925,68 +1265,20 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
 // (context parallelism runs the state recurrences more than once around a state exchange).
 // ptrs: 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u, 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO,
 //       12 dloc, 13 dup, 14 dstates, 15 ds_final, 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha,
-//       21 p_final (stage 1 only, optional: also computes the span's transfer matrix)
+//       21 p_final (stage 1 only, optional: also computes the span's transfer matrix),
+//       22 status word (int, optional) of the bounded waits,
+//       23 xinv: bf16 (B,H,T/64,64,64), written by stage 0 and read by stage 5
 // strides (elements per token): 0 q, 1 k, 2 v, 3 dq, 4 dk, 5 dv
 // stage: 0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd, 5 bwd_final
-namespace ceo {
-template <int D>
-static int efla_stage_impl(int stage, void* const* P, const long long* S, int B, int T, int H,
-                           cudaStream_t st) {
-  static bool cfg = false;
-  if (!cfg) {
-    cudaError_t e;
-    if ((e = set_smem(efla_wy_kernel<D>, smem_wy<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_state_fwd_kernel<D>, smem_state_fwd<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_out_kernel<D>, smem_out<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
-    cfg = true;
-  }
-  const int n = T / CH;
-  dim3 gpar(n, B * H), gser(D / BV, B * H);
-  auto b16 = [&](int i) { return static_cast<bf16*>(P[i]); };
-  auto f32 = [&](int i) { return static_cast<float*>(P[i]); };
-  switch (stage) {
-    case 0:
-      efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(b16(1), b16(2), f32(3), b16(4), b16(5), T,
-                                                         H, S[1], S[2]);
-      break;
-    case 1:
-      efla_state_fwd_kernel<D><<<dim3(P[21] ? 2 * (D / BV) : D / BV, B * H), 128,
-                                 smem_state_fwd<D>(), st>>>(
-          b16(1), b16(4), b16(5), f32(9), b16(6), b16(7), f32(10), f32(21), T, H, S[1]);
-      break;
-    case 2:
-      efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(b16(0), b16(1), b16(6), b16(7), b16(8),
-                                                           T, H, S[0], S[1]);
-      break;
-    case 3:
-      efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(
-          b16(0), b16(1), b16(6), b16(7), b16(11), b16(17), b16(12), T, H, S[0], S[1], S[3]);
-      break;
-    case 4:
-      efla_state_bwd_kernel<D><<<gser, 128, smem_state_bwd<D>(), st>>>(
-          b16(0), b16(1), b16(4), b16(11), b16(12), f32(15), b16(13), b16(14), f32(16), T, H, S[0],
-          S[1]);
-      break;
-    case 5:
-      efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
-          b16(0), b16(1), b16(2), f32(3), b16(6), b16(7), b16(11), b16(13), b16(14), b16(18),
-          b16(19), f32(20), T, H, S[0], S[1], S[2], S[4], S[5]);
-      break;
-    default:
-      return -5;
-  }
-  return static_cast<int>(cudaGetLastError());
-}
-}  // namespace ceo
-
 extern "C" int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T,
                               int H, int D, cudaStream_t stream) {
   if (B <= 0 || T <= 0 || H <= 0 || (T % ceo::CH) || (D != 64 && D != 128)) return -5;
-  for (int i = 0; i < 6; ++i)
+  ceo::EflaTensors t = {};
+  for (int i = 0; i < 24; ++i) t.p[i] = ptrs[i];
+  for (int i = 0; i < 6; ++i) {
     if (strides[i] & 7) return -2;
-  return D == 64 ? ceo::efla_stage_impl<64>(stage, ptrs, strides, B, T, H, stream)
-                 : ceo::efla_stage_impl<128>(stage, ptrs, strides, B, T, H, stream);
+    t.stride[i] = strides[i];
+  }
+  return D == 64 ? ceo::efla_run_stage<64>(stage, t, B, T, H, stream)
+                 : ceo::efla_run_stage<128>(stage, t, B, T, H, stream);
 }

@@ -41,21 +41,23 @@ class _DeltaRuleFn(torch.autograd.Function):
         up = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
         o = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
         states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        xinv = torch.empty(B, H, n, CHUNK, CHUNK, dtype=torch.bfloat16, device=dev)
         s_final = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
         L = _lib.lib()
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
+                                  xinv.data_ptr(),
                                   o.data_ptr(), s_final.data_ptr(), B, T, H, d, _tok_stride(q),
                                   _tok_stride(k), _tok_stride(v), st, _lib.stream()),
                    "ceo_efla_fwd")
-        ctx.save_for_backward(q, k, v, alpha, w, up, states)
+        ctx.save_for_backward(q, k, v, alpha, w, up, states, xinv)
         ctx.has_s0 = s0 is not None
         return o, s_final
 
     @staticmethod
     def backward(ctx, do, ds_final):
-        q, k, v, alpha, w, up, states = ctx.saved_tensors
+        q, k, v, alpha, w, up, states, xinv = ctx.saved_tensors
         B, T, H, d = k.shape
         n = T // CHUNK
         dev = k.device
@@ -73,7 +75,8 @@ class _DeltaRuleFn(torch.autograd.Function):
         L = _lib.lib()
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), alpha.data_ptr(),
-                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), do.data_ptr(),
+                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), xinv.data_ptr(),
+                                  do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                   dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, _tok_stride(q),
@@ -117,19 +120,21 @@ class _EflaQKVFn(torch.autograd.Function):
         up = torch.empty_like(w)
         o = torch.empty_like(w)
         states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        xinv = torch.empty(B, H, n, CHUNK, CHUNK, dtype=torch.bfloat16, device=dev)
         s_final = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
+                                  xinv.data_ptr(),
                                   o.data_ptr(), s_final.data_ptr(), B, T, H, d, H * d, H * d, ts,
                                   st, _lib.stream()), "ceo_efla_fwd")
-        ctx.save_for_backward(qkv, beta, qn, kn, rq, rk, alpha, w, up, states)
+        ctx.save_for_backward(qkv, beta, qn, kn, rq, rk, alpha, w, up, states, xinv)
         ctx.cfg = (normalize, scalar, s0 is not None)
         return o, s_final
 
     @staticmethod
     def backward(ctx, do, ds_final):
-        qkv, beta, qn, kn, rq, rk, alpha, w, up, states = ctx.saved_tensors
+        qkv, beta, qn, kn, rq, rk, alpha, w, up, states, xinv = ctx.saved_tensors
         normalize, scalar, has_s0 = ctx.cfg
         B, T, P, H, d = qkv.shape
         n = T // CHUNK
@@ -151,7 +156,8 @@ class _EflaQKVFn(torch.autograd.Function):
         L = _lib.lib()
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_bwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), alpha.data_ptr(),
-                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), do.data_ptr(),
+                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), xinv.data_ptr(),
+                                  do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(),
                                   dv.data_ptr(), dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d,
@@ -267,19 +273,21 @@ class _EflaProjFn(torch.autograd.Function):
         up = torch.empty_like(w)
         o = torch.empty_like(w)
         states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        xinv = torch.empty(B, H, n, CHUNK, CHUNK, dtype=torch.bfloat16, device=dev)
         s_final = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v_ptr, alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
+                                  xinv.data_ptr(),
                                   o.data_ptr(), s_final.data_ptr(), B, T, H, d, hd, hd, N, st,
                                   _lib.stream()), "ceo_efla_fwd")
-        ctx.save_for_backward(proj, beta, qn, kn, rq, rk, alpha, w, up, states)
+        ctx.save_for_backward(proj, beta, qn, kn, rq, rk, alpha, w, up, states, xinv)
         ctx.cfg = (P, H, d, normalize, s0 is not None)
         return o, s_final
 
     @staticmethod
     def backward(ctx, do, ds_final):
-        proj, beta, qn, kn, rq, rk, alpha, w, up, states = ctx.saved_tensors
+        proj, beta, qn, kn, rq, rk, alpha, w, up, states, xinv = ctx.saved_tensors
         P, H, d, normalize, has_s0 = ctx.cfg
         B, T, N = proj.shape
         dev = proj.device
@@ -301,7 +309,8 @@ class _EflaProjFn(torch.autograd.Function):
         L = _lib.lib()
         st = _lib.status_word(dev).data_ptr()
         _lib.check(L.ceo_efla_bwd(qn.data_ptr(), kn.data_ptr(), v_ptr, alpha.data_ptr(),
-                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), do.data_ptr(),
+                                  w.data_ptr(), up.data_ptr(), states.data_ptr(), xinv.data_ptr(),
+                                  do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(), dv_ptr,
                                   dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, hd, hd, N, hd, hd,

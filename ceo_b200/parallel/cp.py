@@ -26,13 +26,14 @@ from .symm import SymmetricBuffer
 
 _IDX = {"q": 0, "k": 1, "v": 2, "alpha": 3, "w": 4, "u": 5, "up": 6, "states": 7, "o": 8,
         "s0": 9, "s_final": 10, "dO": 11, "dloc": 12, "dup": 13, "dstates": 14, "ds_final": 15,
-        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20, "p_final": 21}
+        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20, "p_final": 21, "xinv": 23}
 
 
 def _stage(stage: int, tensors: dict, strides, B, T, H, d):
-    ptrs = (ctypes.c_void_p * 22)()
+    ptrs = (ctypes.c_void_p * 24)()
     for k, t in tensors.items():
         ptrs[_IDX[k]] = None if t is None else t.data_ptr()
+    ptrs[22] = _lib.status_word(torch.device("cuda", torch.cuda.current_device())).data_ptr()
     st = (ctypes.c_longlong * 6)(*strides)
     _lib.check(_lib.lib().ceo_efla_stage(stage, ptrs, st, B, T, H, d, _lib.stream()),
                f"ceo_efla_stage({stage})")
@@ -83,10 +84,12 @@ class _CPDeltaRule(torch.autograd.Function):
         new = lambda: torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
         w, u, up, o = new(), new(), new(), new()
         states = torch.empty(B, H, n, d, d, dtype=torch.bfloat16, device=dev)
+        xinv = torch.empty(B, H, n, efla_ops.CHUNK, efla_ops.CHUNK, dtype=torch.bfloat16,
+                           device=dev)
         R = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
         P = torch.empty_like(R)
         base = {"q": q, "k": k, "v": v, "alpha": alpha, "w": w, "u": u, "up": up,
-                "states": states, "o": o}
+                "states": states, "o": o, "xinv": xinv}
         _stage(0, base, strides, B, T, H, d)
         # one launch: R_r (state pass from zero) and P_r (homogeneous pass on the identity)
         _stage(1, dict(base, s0=None, s_final=R, p_final=P), strides, B, T, H, d)
@@ -97,13 +100,13 @@ class _CPDeltaRule(torch.autograd.Function):
         s_out = torch.empty_like(R)
         _stage(1, dict(base, s0=s_in, s_final=s_out), strides, B, T, H, d)
         _stage(2, base, strides, B, T, H, d)
-        ctx.save_for_backward(q, k, v, alpha, w, up, states, allmaps[:, 0].contiguous())
+        ctx.save_for_backward(q, k, v, alpha, w, up, states, xinv, allmaps[:, 0].contiguous())
         ctx.cp = cp
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, alpha, w, up, states, Pall = ctx.saved_tensors
+        q, k, v, alpha, w, up, states, xinv, Pall = ctx.saved_tensors
         cp = ctx.cp
         B, T, H, d = k.shape
         n = T // efla_ops.CHUNK
@@ -117,7 +120,7 @@ class _CPDeltaRule(torch.autograd.Function):
         dalpha = torch.empty(B, T, H, dtype=torch.float32, device=dev)
         Q = torch.empty(B, H, d, d, dtype=torch.float32, device=dev)
         base = {"q": q, "k": k, "v": v, "alpha": alpha, "w": w, "up": up, "states": states,
-                "dO": do, "dloc": dloc, "dup": dup, "dstates": dstates, "dq": dq, "dk": dk,
+                "xinv": xinv, "dO": do, "dloc": dloc, "dup": dup, "dstates": dstates, "dq": dq, "dk": dk,
                 "dv": dv, "dalpha": dalpha}
         _stage(3, base, strides, B, T, H, d)
         _stage(4, dict(base, ds_final=None, ds0=Q), strides, B, T, H, d)   # Q_r
