@@ -243,6 +243,8 @@ def main(argv=None):
         print(json.dumps(out))
     if comm is not None:
         comm.barrier()
+    if torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
     return 0
 
 

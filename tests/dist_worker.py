@@ -73,6 +73,34 @@ def main():
             loss, gn = eng.train_step([(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())], lr=1e-3)
         torch.save({"params": eng.flat.params.clone(), "loss": float(loss), "gn": float(gn)},
                    os.path.join(out, f"{what}_{rank}.pt"))
+    elif what == "pipeline":
+        from ceo_b200.models.model import EflaLM
+        from ceo_b200.parallel.pipeline import PipelineRunner, PipelineStage, stage_bounds
+        cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+        m = cfg.model
+        m.num_layers = 3          # uneven split: stage 0 takes two layers
+        stage = PipelineStage(m, "cpu", rank, world, seed=0, dtype=torch.float32)
+        runner = PipelineRunner(stage)
+        g = torch.Generator().manual_seed(1)
+        x = torch.randint(0, m.vocab_size, (3, 2, 65), generator=g)   # three micro-batches
+        batches = [(b[:, :-1].contiguous(), b[:, 1:].contiguous()) for b in x]
+        loss = runner.run(batches)
+        runner.sync_tied_grads()
+        full = EflaLM(m, "cpu", dtype=torch.float32, seed=0)
+        ref = sum(full(t, y) for t, y in batches) / len(batches)
+        ref.backward()
+        assert abs(float(loss) - float(ref)) < 1e-5, (float(loss), float(ref))
+        lo, hi = stage_bounds(m.num_layers, world, rank)
+        assert (lo, hi) == ((0, 2) if rank == 0 else (2, 3))
+        for i, blk in enumerate(stage.blocks):
+            for (n1, p1), (n2, p2) in zip(blk.named_parameters(),
+                                          full.blocks[lo + i].named_parameters()):
+                if p2.grad is None:
+                    continue
+                assert torch.allclose(p1.grad, p2.grad, atol=2e-5, rtol=1e-4), n1
+        if stage.embed_tokens is not None:
+            assert torch.allclose(stage.embed_tokens.grad, full.embed_tokens.grad, atol=2e-5,
+                                  rtol=1e-4)
     comm.barrier()
     dist.destroy_process_group()
 

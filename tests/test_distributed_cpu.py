@@ -68,6 +68,11 @@ def test_sharded_optimizer_matches_single_process(tmp_path, kind):
         (res[0]["params"][:n] - ref_params).abs().max()
 
 
+def test_pipeline_1f1b_matches_whole_model(tmp_path):
+    """Two pipeline stages over gloo: loss and every gradient equal the single-process model."""
+    _spawn("pipeline", 2, tmp_path)
+
+
 def test_heartbeat_detects_silent_rank(tmp_path):
     _spawn("heartbeat", 2, tmp_path, timeout=60)
     msg = (tmp_path / "detected0").read_text()
