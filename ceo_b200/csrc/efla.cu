@@ -292,7 +292,8 @@ efla_state_fwd_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_up,
                       const __grid_constant__ CUtensorMap tm_states,
                       const float* __restrict__ s0, float* __restrict__ s_final,
-                      float* __restrict__ p_final, int T, int H, int* status) {
+                      float* __restrict__ p_final, const unsigned char* __restrict__ resets, int T,
+                      int H, int* status) {
   constexpr int NT = 4, MT = D / 64, NSL = D / BV, TILE = (D / 64) * PANEL;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -369,9 +370,17 @@ efla_state_fwd_kernel(const __grid_constant__ CUtensorMap tm_k,
                                 : (s0 ? s0[(static_cast<long long>(bh) * D + row) * D + col] : 0.f);
       }
   const SwzTile St = swz_tile(Ss, D), Ut = swz_tile(Us, CH), Upt = swz_tile(Ups, CH);
+  // resets[b][c] != 0: chunk c starts a new document, the state entering it is zero (the flag
+  // of the next chunk is fetched a step ahead, off the serial chain)
+  unsigned char rz = resets ? resets[b * n] : 0;
 
   for (int c = 0; c < n; ++c) {
     const SwzTile Wt = swz_tile(Wb + (c & 1) * TILE, CH), Kt = swz_tile(Kb + (c & 1) * TILE, CH);
+    if (rz) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) zero_acc<NT>(sacc[mt]);
+    }
+    if (resets && c + 1 < n) rz = resets[b * n + c + 1];
     // snapshot of the state entering chunk c: bf16 MMA operand + saved for O and backward
     if (!ident && c > 0) ser_wait(sy, &sy->st_free, (c - 1) & 1, status);
 #pragma unroll
@@ -585,8 +594,8 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_dloc,
                       const __grid_constant__ CUtensorMap tm_dup,
                       const __grid_constant__ CUtensorMap tm_dstates,
-                      const float* __restrict__ ds_final, float* __restrict__ ds0, int T, int H,
-                      int* status) {
+                      const float* __restrict__ ds_final, float* __restrict__ ds0,
+                      const unsigned char* __restrict__ resets, int T, int H, int* status) {
   constexpr int NT = 4, MT = D / 64, TILE = (D / 64) * PANEL;
   constexpr int STAGE = 3 * TILE + 2 * PANEL;  // K | Q | W | Dl | dO
   extern __shared__ uint8_t smem_raw[];
@@ -654,6 +663,8 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             ds_final ? ds_final[(static_cast<long long>(bh) * D + row) * D + col] : 0.f;
       }
   const SwzTile dSt = swz_tile(dSs, D), dUpt = swz_tile(dUps, CH);
+  // a chunk that starts a new document passes no gradient to the chunk before it
+  unsigned char rz = resets ? resets[b * n + n - 1] : 0;
 
   for (int i = 0; i < n; ++i) {
     uint8_t* st = smem + (i & 1) * STAGE;
@@ -689,6 +700,11 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     warp_gemm_swz<MT, NT, CH, true, true>(dacc, Wt, r * 16 * MT, dUpt, cw);
     __syncwarp();
     if (lane == 0) mbar_arrive(&sy->empty[i & 1]);
+    if (rz && i + 1 < n) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) zero_acc<NT>(dacc[mt]);
+    }
+    if (resets && i + 1 < n) rz = resets[b * n + n - 2 - i];
   }
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -1071,11 +1087,11 @@ static cudaError_t efla_configure() {
 
 // Every tensor a stage touches through TMA, by the slot numbers of ceo_efla_stage.
 struct EflaTensors {
-  const void* p[24];
+  const void* p[25];
   long long stride[6];  // q, k, v, dq, dk, dv
 };
 enum { I_Q = 0, I_K, I_V, I_ALPHA, I_W, I_U, I_UP, I_STATES, I_O, I_S0, I_SFINAL, I_DO, I_DLOC,
-       I_DUP, I_DSTATES, I_DSFINAL, I_DS0, I_DQ, I_DK, I_DV, I_DALPHA, I_PFINAL, I_STATUS, I_XINV };
+       I_DUP, I_DSTATES, I_DSFINAL, I_DS0, I_DQ, I_DK, I_DV, I_DALPHA, I_PFINAL, I_STATUS, I_XINV, I_RESETS };
 
 template <int D>
 static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, cudaStream_t st) {
@@ -1116,7 +1132,8 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
       MAP(sta(&m[4], I_STATES));
       efla_state_fwd_kernel<D><<<dim3(t.p[I_PFINAL] ? 2 * (D / BV) : D / BV, B * H), SER_THREADS,
                                  smem_state_fwd<D>(), st>>>(
-          m[0], m[1], m[2], m[3], m[4], f32(I_S0), f32(I_SFINAL), f32(I_PFINAL), T, H, status);
+          m[0], m[1], m[2], m[3], m[4], f32(I_S0), f32(I_SFINAL), f32(I_PFINAL),
+          static_cast<const unsigned char*>(t.p[I_RESETS]), T, H, status);
       break;
     case 2:
       MAP(tok(&m[0], I_Q, t.stride[0]));
@@ -1144,7 +1161,8 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
       MAP(tok(&m[5], I_DUP, HD));
       MAP(sta(&m[6], I_DSTATES));
       efla_state_bwd_kernel<D><<<dim3(D / BV, B * H), SER_THREADS, smem_state_bwd<D>(), st>>>(
-          m[0], m[1], m[2], m[3], m[4], m[5], m[6], f32(I_DSFINAL), f32(I_DS0), T, H, status);
+          m[0], m[1], m[2], m[3], m[4], m[5], m[6], f32(I_DSFINAL), f32(I_DS0),
+          static_cast<const unsigned char*>(t.p[I_RESETS]), T, H, status);
       break;
     case 5:
       MAP(tok(&m[0], I_Q, t.stride[0]));
@@ -1178,15 +1196,15 @@ using namespace ceo;
 
 extern "C" int ceo_efla_fwd(const void* q, const void* k, const void* v, const float* alpha,
                             const float* s0, void* w, void* up, void* states, void* xinv, void* o,
-                            float* s_final, int B, int T, int H, int D, long long q_stride,
-                            long long k_stride, long long v_stride, int* status,
-                            cudaStream_t stream) {
+                            float* s_final, const unsigned char* resets, int B, int T, int H,
+                            int D, long long q_stride, long long k_stride, long long v_stride,
+                            int* status, cudaStream_t stream) {
   if (!efla_args_ok(B, T, H, D, q_stride, k_stride, v_stride)) return -5;
   EflaTensors t = {};
   t.p[I_Q] = q; t.p[I_K] = k; t.p[I_V] = v; t.p[I_ALPHA] = alpha; t.p[I_W] = w;
   t.p[I_U] = o;  // U is staged in `o` (same shape, overwritten by the last kernel)
   t.p[I_UP] = up; t.p[I_STATES] = states; t.p[I_O] = o; t.p[I_S0] = s0; t.p[I_SFINAL] = s_final;
-  t.p[I_STATUS] = status; t.p[I_XINV] = xinv;
+  t.p[I_STATUS] = status; t.p[I_XINV] = xinv; t.p[I_RESETS] = resets;
   t.stride[0] = q_stride; t.stride[1] = k_stride; t.stride[2] = v_stride;
   for (int stage = 0; stage < 3; ++stage) {
     const int rc = D == 64 ? efla_run_stage<64>(stage, t, B, T, H, stream)
@@ -1200,7 +1218,8 @@ extern "C" int ceo_efla_bwd(const void* q, const void* k, const void* v, const f
                             const void* w, const void* up, const void* states, const void* xinv,
                             const void* dO, const float* ds_final, void* dloc, void* dup,
                             void* dstates, void* dq,
-                            void* dk, void* dv, float* dalpha, float* ds0, int B, int T, int H,
+                            void* dk, void* dv, float* dalpha, float* ds0,
+                            const unsigned char* resets, int B, int T, int H,
                             int D, long long q_stride, long long k_stride, long long v_stride,
                             long long dq_stride, long long dk_stride, long long dv_stride,
                             int* status, cudaStream_t stream) {
@@ -1211,6 +1230,7 @@ extern "C" int ceo_efla_bwd(const void* q, const void* k, const void* v, const f
   t.p[I_STATES] = states; t.p[I_DO] = dO; t.p[I_DSFINAL] = ds_final; t.p[I_DLOC] = dloc;
   t.p[I_DUP] = dup; t.p[I_DSTATES] = dstates; t.p[I_DQ] = dq; t.p[I_DK] = dk; t.p[I_DV] = dv;
   t.p[I_DALPHA] = dalpha; t.p[I_DS0] = ds0; t.p[I_STATUS] = status; t.p[I_XINV] = xinv;
+  t.p[I_RESETS] = resets;
   t.stride[0] = q_stride; t.stride[1] = k_stride; t.stride[2] = v_stride;
   t.stride[3] = dq_stride; t.stride[4] = dk_stride; t.stride[5] = dv_stride;
   for (int stage = 3; stage < 6; ++stage) {
@@ -1267,14 +1287,15 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
 //       12 dloc, 13 dup, 14 dstates, 15 ds_final, 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha,
 //       21 p_final (stage 1 only, optional: also computes the span's transfer matrix),
 //       22 status word (int, optional) of the bounded waits,
-//       23 xinv: bf16 (B,H,T/64,64,64), written by stage 0 and read by stage 5
+//       23 xinv: bf16 (B,H,T/64,64,64), written by stage 0 and read by stage 5,
+//       24 resets: bytes (B,T/64), optional; non-zero = the chunk starts from a zero state
 // strides (elements per token): 0 q, 1 k, 2 v, 3 dq, 4 dk, 5 dv
 // stage: 0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd, 5 bwd_final
 extern "C" int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T,
                               int H, int D, cudaStream_t stream) {
   if (B <= 0 || T <= 0 || H <= 0 || (T % ceo::CH) || (D != 64 && D != 128)) return -5;
   ceo::EflaTensors t = {};
-  for (int i = 0; i < 24; ++i) t.p[i] = ptrs[i];
+  for (int i = 0; i < 25; ++i) t.p[i] = ptrs[i];
   for (int i = 0; i < 6; ++i) {
     if (strides[i] & 7) return -2;
     t.stride[i] = strides[i];

@@ -46,24 +46,25 @@ int ceo_set_deterministic(int on);
  * fine); alpha fp32 (B,T,H); s0 / s_final / ds_final / ds0 fp32 (B,H,D,D) (s0, ds_final may
  * be NULL).  Saved for backward: w, up (bf16 (B,T,H,D)), states (bf16 (B,H,T/64,D,D)), xinv (bf16
  * (B,H,T/64,64,64): the inverse of each chunk's 64x64 triangular system).
+ * resets (optional): bytes (B,T/64); non-zero marks a chunk that starts a new document, i.e.
+ * the state entering it is zero (packed sequences aligned to the chunk length).
  * Backward workspaces: dloc, dup (bf16 (B,T,H,D)), dstates (bf16 (B,H,T/64,D,D)). */
 int ceo_efla_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* s0,
-                 void* w, void* up, void* states, void* xinv, void* o, float* s_final, int B, int T,
-                 int H,
-                 int D, long long q_stride, long long k_stride, long long v_stride, int* status,
-                 cudaStream_t stream);
+                 void* w, void* up, void* states, void* xinv, void* o, float* s_final,
+                 const unsigned char* resets, int B, int T, int H, int D, long long q_stride,
+                 long long k_stride, long long v_stride, int* status, cudaStream_t stream);
 int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha, const void* w,
                  const void* up, const void* states, const void* xinv, const void* dO,
-                 const float* ds_final,
-                 void* dloc, void* dup, void* dstates, void* dq, void* dk, void* dv, float* dalpha,
-                 float* ds0, int B, int T, int H, int D, long long q_stride, long long k_stride,
+                 const float* ds_final, void* dloc, void* dup, void* dstates, void* dq, void* dk,
+                 void* dv, float* dalpha, float* ds0, const unsigned char* resets, int B, int T,
+                 int H, int D, long long q_stride, long long k_stride,
                  long long v_stride, long long dq_stride, long long dk_stride,
                  long long dv_stride, int* status, cudaStream_t stream);
 /* One of the six EFLA kernels at a time (0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd,
- * 5 bwd_final).  ptrs (host array of 24 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
+ * 5 bwd_final).  ptrs (host array of 25 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
  * 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO, 12 dloc, 13 dup, 14 dstates, 15 ds_final,
  * 16 ds0, 17 dq, 18 dk, 19 dv, 20 dalpha, 21 p_final (optional, stage 1: also returns the
- * span's transfer matrix P with S_out = P S_in + R), 22 status word (optional), 23 xinv;
+ * span's transfer matrix P with S_out = P S_in + R), 22 status word (optional), 23 xinv, 24 resets (optional);
  * strides (host array of 6): q, k, v, dq, dk, dv. */
 int ceo_efla_stage(int stage, void* const* ptrs, const long long* strides, int B, int T, int H,
                    int D, cudaStream_t stream);

@@ -241,9 +241,13 @@ class PackedSequence:
     length: int = 0
 
 
-def pack_sequences(sequences, max_len: int) -> list[PackedSequence]:
+def pack_sequences(sequences, max_len: int, align: int = 1) -> list[PackedSequence]:
     """Greedy packing in input order; a sequence longer than ``max_len`` is skipped, a
-    sequence that does not fit the open pack closes it (dataset.zig:420-465)."""
+    sequence that does not fit the open pack closes it (dataset.zig:420-465).
+
+    ``align`` > 1 starts every sequence on a multiple of ``align`` tokens (the gap is padding
+    with sequence id -1), which is what the chunked EFLA kernels need to reset the recurrent
+    state at document boundaries (``align=64``; see ``packed_batch``)."""
     packs, cur = [], None
 
     def new():
@@ -252,15 +256,39 @@ def pack_sequences(sequences, max_len: int) -> list[PackedSequence]:
         seq = np.asarray(seq, dtype=np.int64)
         if seq.size == 0 or seq.size > max_len:
             continue
-        if cur is None or cur.length + seq.size > max_len:
+        start = 0 if cur is None else -(-cur.length // align) * align
+        if cur is None or start + seq.size > max_len:
             if cur is not None:
                 packs.append(cur)
-            cur = new()
+            cur, start = new(), 0
         sid = len(cur.cumulative_lengths) - 1
-        cur.tokens[cur.length:cur.length + seq.size] = seq
-        cur.sequence_ids[cur.length:cur.length + seq.size] = sid
-        cur.length += seq.size
+        cur.tokens[start:start + seq.size] = seq
+        cur.sequence_ids[start:start + seq.size] = sid
+        cur.length = start + seq.size
         cur.cumulative_lengths.append(cur.length)
     if cur is not None and cur.length:
         packs.append(cur)
     return packs
+
+
+def packed_batch(packs, chunk: int = 64, pad_id: int = 0, ignore_index: int = -100):
+    """Model inputs for packs made with ``pack_sequences(..., align=chunk)``: ``tokens`` and
+    ``targets`` (B, L-1 rounded down to a multiple of ``chunk``; next-token targets,
+    ``ignore_index`` on padding and on each document's last token) and ``resets``
+    (B, T/chunk), set where a chunk starts a new document."""
+    import torch
+    L = len(packs[0].tokens)
+    T = ((L - 1) // chunk) * chunk
+    B = len(packs)
+    tokens = np.full((B, T), pad_id, np.int64)
+    targets = np.full((B, T), ignore_index, np.int64)
+    resets = np.zeros((B, T // chunk), bool)
+    for b, p in enumerate(packs):
+        ids = p.sequence_ids
+        tokens[b] = np.where(ids[:T] >= 0, p.tokens[:T], pad_id)
+        same = (ids[:T] >= 0) & (ids[1:T + 1] == ids[:T])
+        targets[b] = np.where(same, p.tokens[1:T + 1], ignore_index)
+        starts = np.arange(0, T, chunk)
+        prev = np.concatenate([[-2], ids[starts[1:] - 1]])
+        resets[b] = (ids[starts] >= 0) & (ids[starts] != prev)
+    return torch.from_numpy(tokens), torch.from_numpy(targets), torch.from_numpy(resets)

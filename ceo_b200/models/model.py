@@ -79,16 +79,17 @@ class EflaLayer(nn.Module):
                                            requires_grad=e.learned_beta)
         self.w_qkv = nn.Parameter(w_qkv)
 
-    def forward(self, x_norm, residual, state=None):
+    def forward(self, x_norm, residual, state=None, resets=None):
         B, T, _ = x_norm.shape
         if (-T) % efla_ops.CHUNK and x_norm.is_cuda:
             raise ValueError(f"sequence length {T} must be a multiple of {efla_ops.CHUNK} on GPU")
         proj = linear(x_norm, self.w_qkv)
         if self.per_token_beta:
-            o, s_final = efla_ops.efla_proj(proj, self.P, self.H, self.d, self.normalize, state)
+            o, s_final = efla_ops.efla_proj(proj, self.P, self.H, self.d, self.normalize, state,
+                                            resets)
         else:
             o, s_final = efla_ops.efla_qkv(proj.view(B, T, self.P, self.H, self.d),
-                                           self.beta_param, self.normalize, state)
+                                           self.beta_param, self.normalize, state, resets)
         return o.reshape(B, T, self.H * self.d), s_final
 
     def decode_step(self, x_norm, state):
@@ -137,9 +138,9 @@ class Block(nn.Module):
         self.ln2 = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
         self.mlp = MLP(cfg, device, dtype, gen, std)
 
-    def forward(self, h, state=None):
+    def forward(self, h, state=None, resets=None):
         n1 = self.ln1(h)
-        o, s_final = self.efla(n1, h, state)
+        o, s_final = self.efla(n1, h, state, resets)
         if self.prism is not None:
             a = linear(o, self.efla.w_o)
             h = h + self.prism(n1, a)
@@ -179,19 +180,21 @@ class EflaLM(nn.Module):
     def head_weight(self):
         return self.embed_tokens if self.lm_head is None else self.lm_head
 
-    def hidden(self, tokens, states=None):
+    def hidden(self, tokens, states=None, resets=None):
         h = K.embedding(tokens, self.embed_tokens)
         finals = []
         for i, blk in enumerate(self.blocks):
-            h, s = blk(h, None if states is None else states[i])
+            h, s = blk(h, None if states is None else states[i], resets)
             finals.append(s)
         return self.final_norm(h), finals
 
     def forward(self, tokens, targets=None, label_smoothing: float = 0.0, states=None,
-                return_states: bool = False):
+                return_states: bool = False, resets=None):
         """With ``targets``: mean next-token cross-entropy (the LM head and the loss are fused,
-        logits are never materialised).  Without: logits (B,T,V) in fp32."""
-        hn, finals = self.hidden(tokens, states)
+        logits are never materialised; targets equal to -100 are left out).  Without: logits
+        (B,T,V) in fp32.  ``resets`` (B, T/64): chunks that start a new document of a packed
+        batch (``data.dataset.pack_sequences(..., align=64)``); the EFLA state is zeroed there."""
+        hn, finals = self.hidden(tokens, states, resets)
         if targets is not None:
             out = K.linear_cross_entropy(hn, self.head_weight(), targets, label_smoothing)
         else:

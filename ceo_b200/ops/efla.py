@@ -19,6 +19,15 @@ from . import _lib, reference as ref
 CHUNK = 64
 
 
+def _resets_u8(resets, B: int, n: int, dev):
+    """(B, T/64) mask -> contiguous uint8 on the device (None stays None)."""
+    if resets is None:
+        return None
+    r = resets.to(device=dev, dtype=torch.uint8).contiguous()
+    assert r.shape == (B, n), "resets must have shape (B, T/64)"
+    return r
+
+
 def _tok_stride(t: torch.Tensor) -> int:
     """Row (token) stride in elements of a (B,T,H,d) tensor whose (H,d) block is dense and
     whose (B,T) dimensions collapse to one stride (true for slices of a fused QKV output)."""
@@ -30,12 +39,13 @@ def _tok_stride(t: torch.Tensor) -> int:
 
 class _DeltaRuleFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, alpha, s0):
+    def forward(ctx, q, k, v, alpha, s0, resets=None):
         B, T, H, d = k.shape
         assert v.shape[-1] == d and d in (64, 128), "head_dim must be 64 or 128"
         assert T % CHUNK == 0, "sequence length must be a multiple of 64"
         n = T // CHUNK
         dev = k.device
+        ctx.resets = resets = _resets_u8(resets, B, n, dev)
         alpha = alpha.contiguous().float()
         w = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
         up = torch.empty(B, T, H, d, dtype=torch.bfloat16, device=dev)
@@ -48,8 +58,9 @@ class _DeltaRuleFn(torch.autograd.Function):
         _lib.check(L.ceo_efla_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
                                   xinv.data_ptr(),
-                                  o.data_ptr(), s_final.data_ptr(), B, T, H, d, _tok_stride(q),
-                                  _tok_stride(k), _tok_stride(v), st, _lib.stream()),
+                                  o.data_ptr(), s_final.data_ptr(), _lib.ptr(resets), B, T, H, d,
+                                  _tok_stride(q), _tok_stride(k), _tok_stride(v), st,
+                                  _lib.stream()),
                    "ceo_efla_fwd")
         ctx.save_for_backward(q, k, v, alpha, w, up, states, xinv)
         ctx.has_s0 = s0 is not None
@@ -79,11 +90,11 @@ class _DeltaRuleFn(torch.autograd.Function):
                                   do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                  dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, _tok_stride(q),
-                                  _tok_stride(k), _tok_stride(v), H * d, H * d, H * d, st,
-                                  _lib.stream()),
+                                  dalpha.data_ptr(), ds0.data_ptr(), _lib.ptr(ctx.resets), B, T, H, d,
+                                  _tok_stride(q), _tok_stride(k), _tok_stride(v), H * d, H * d,
+                                  H * d, st, _lib.stream()),
                    "ceo_efla_bwd")
-        return dq, dk, dv, dalpha, (ds0 if ctx.has_s0 else None)
+        return dq, dk, dv, dalpha, (ds0 if ctx.has_s0 else None), None
 
 
 class _EflaQKVFn(torch.autograd.Function):
@@ -94,11 +105,12 @@ class _EflaQKVFn(torch.autograd.Function):
     read it in place."""
 
     @staticmethod
-    def forward(ctx, qkv, beta, normalize, s0):
+    def forward(ctx, qkv, beta, normalize, s0, resets=None):
         B, T, P, H, d = qkv.shape
         assert qkv.is_contiguous() and P in (2, 3) and T % CHUNK == 0
         dev = qkv.device
         n = T // CHUNK
+        ctx.resets = resets = _resets_u8(resets, B, n, dev)
         ts = P * H * d
         q_raw = qkv[:, :, 0] if P == 3 else qkv[:, :, 0]
         k_raw = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
@@ -126,7 +138,8 @@ class _EflaQKVFn(torch.autograd.Function):
         _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
                                   xinv.data_ptr(),
-                                  o.data_ptr(), s_final.data_ptr(), B, T, H, d, H * d, H * d, ts,
+                                  o.data_ptr(), s_final.data_ptr(), _lib.ptr(resets), B, T, H, d,
+                                  H * d, H * d, ts,
                                   st, _lib.stream()), "ceo_efla_fwd")
         ctx.save_for_backward(qkv, beta, qn, kn, rq, rk, alpha, w, up, states, xinv)
         ctx.cfg = (normalize, scalar, s0 is not None)
@@ -160,7 +173,8 @@ class _EflaQKVFn(torch.autograd.Function):
                                   do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(),
-                                  dv.data_ptr(), dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d,
+                                  dv.data_ptr(), dalpha.data_ptr(), ds0.data_ptr(),
+                                  _lib.ptr(ctx.resets), B, T, H, d,
                                   H * d, H * d, ts, H * d, H * d, ts, st, _lib.stream()),
                    "ceo_efla_bwd")
         dbeta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
@@ -178,41 +192,46 @@ class _EflaQKVFn(torch.autograd.Function):
                                        int(normalize), _lib.stream()), "ceo_efla_prep_bwd")
         if scalar:
             dbeta = dbeta.sum().reshape(beta.shape)
-        return dqkv, dbeta, None, (ds0 if has_s0 else None)
+        return dqkv, dbeta, None, (ds0 if has_s0 else None), None
 
 
-def efla_qkv(qkv, beta, normalize: bool = True, s0=None):
+def efla_qkv(qkv, beta, normalize: bool = True, s0=None, resets=None):
     """EFLA attention on a fused projection output.  qkv: (B,T,P,H,d), P = 3 (q,k,v) or 2
     (k,v with q = k); beta: (B,T,H) or a one-element tensor.  Returns (o (B,T,H,d), S_T)."""
     if not qkv.is_cuda:
         P = qkv.shape[2]
         q = qkv[:, :, 0]
         k = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
-        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0)
-    return _EflaQKVFn.apply(qkv, beta, normalize, s0)
+        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0,
+                              resets=resets)
+    return _EflaQKVFn.apply(qkv, beta, normalize, s0, resets)
 
 
-def delta_rule(q, k, v, alpha, s0=None, impl: str = "auto"):
+def delta_rule(q, k, v, alpha, s0=None, impl: str = "auto", resets=None):
     """Delta-rule linear attention.  q,k,v: (B,T,H,d) bf16; alpha: (B,T,H).
     Returns ``(o, S_T)`` with ``S_T`` the fp32 final state (B,H,d,d).
+
+    ``resets``: optional (B, T/64) mask; a set entry means that 64-token chunk starts a new
+    document, so the state entering it is zero (packed sequences aligned to the chunk).
 
     ``impl``: "auto" (CUDA kernels on GPU, chunked oracle on CPU), "chunked" or
     "sequential" (fp32 PyTorch oracles, any device)."""
     if impl == "sequential":
-        o, s = ref.delta_rule_sequential(q, k, v, alpha, s0)
+        o, s = ref.delta_rule_sequential(q, k, v, alpha, s0, resets, CHUNK)
         return o.to(q.dtype), s
     if impl == "chunked" or not k.is_cuda:
         T = k.shape[1]
         pad = (-T) % CHUNK
         if pad:  # zero-alpha padding tokens leave the state untouched
+            assert resets is None, "resets need a sequence length that is a multiple of 64"
             zp = lambda t: torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad))
             o, s = ref.delta_rule_chunked(zp(q), zp(k), zp(v),
                                           torch.nn.functional.pad(alpha, (0, 0, 0, pad)), s0,
                                           CHUNK)
             return o[:, :T].to(q.dtype), s
-        o, s = ref.delta_rule_chunked(q, k, v, alpha, s0, CHUNK)
+        o, s = ref.delta_rule_chunked(q, k, v, alpha, s0, CHUNK, resets)
         return o.to(q.dtype), s
-    return _DeltaRuleFn.apply(q, k, v, alpha, s0)
+    return _DeltaRuleFn.apply(q, k, v, alpha, s0, resets)
 
 
 def l2norm(x, eps: float = 1e-6):
@@ -220,7 +239,8 @@ def l2norm(x, eps: float = 1e-6):
     return (xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)).to(x.dtype)
 
 
-def efla_attention(q, k, v, beta, *, normalize_qk: bool = True, s0=None, impl: str = "auto"):
+def efla_attention(q, k, v, beta, *, normalize_qk: bool = True, s0=None, impl: str = "auto",
+                   resets=None):
     """q,k,v: (B,T,H,d); beta: (B,T,H) (already positive, e.g. a sigmoid) or a scalar tensor.
     Returns (o, S_T)."""
     if normalize_qk:
@@ -228,7 +248,7 @@ def efla_attention(q, k, v, beta, *, normalize_qk: bool = True, s0=None, impl: s
         k = l2norm(k)
     lam = k.float().pow(2).sum(-1)
     alpha = ref.efla_coefficient(beta.float().expand_as(lam), lam)
-    return delta_rule(q, k, v, alpha, s0, impl)
+    return delta_rule(q, k, v, alpha, s0, impl, resets)
 
 
 def delta_rule_decode_step(q, k, v, alpha, state):
@@ -248,11 +268,12 @@ class _EflaProjFn(torch.autograd.Function):
     d(beta) - so the projection's gradient GEMMs read it without any concatenation."""
 
     @staticmethod
-    def forward(ctx, proj, P, H, d, normalize, s0):
+    def forward(ctx, proj, P, H, d, normalize, s0, resets=None):
         B, T, N = proj.shape
         assert proj.is_contiguous() and N >= P * H * d + H and N % 8 == 0 and T % CHUNK == 0
         dev = proj.device
         n = T // CHUNK
+        ctx.resets = resets = _resets_u8(resets, B, n, dev)
         hd = H * d
         esz = proj.element_size()
         base = proj.data_ptr()
@@ -279,7 +300,8 @@ class _EflaProjFn(torch.autograd.Function):
         _lib.check(L.ceo_efla_fwd(qn.data_ptr(), kn.data_ptr(), v_ptr, alpha.data_ptr(),
                                   _lib.ptr(s0), w.data_ptr(), up.data_ptr(), states.data_ptr(),
                                   xinv.data_ptr(),
-                                  o.data_ptr(), s_final.data_ptr(), B, T, H, d, hd, hd, N, st,
+                                  o.data_ptr(), s_final.data_ptr(), _lib.ptr(resets), B, T, H, d,
+                                  hd, hd, N, st,
                                   _lib.stream()), "ceo_efla_fwd")
         ctx.save_for_backward(proj, beta, qn, kn, rq, rk, alpha, w, up, states, xinv)
         ctx.cfg = (P, H, d, normalize, s0 is not None)
@@ -313,7 +335,8 @@ class _EflaProjFn(torch.autograd.Function):
                                   do.data_ptr(),
                                   _lib.ptr(ds_final), dloc.data_ptr(), dup.data_ptr(),
                                   dstates.data_ptr(), dqn.data_ptr(), dkn.data_ptr(), dv_ptr,
-                                  dalpha.data_ptr(), ds0.data_ptr(), B, T, H, d, hd, hd, N, hd, hd,
+                                  dalpha.data_ptr(), ds0.data_ptr(), _lib.ptr(ctx.resets), B, T, H,
+                                  d, hd, hd, N, hd, hd,
                                   N, st, _lib.stream()), "ceo_efla_bwd")
         dbeta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
         if P == 3:
@@ -329,10 +352,10 @@ class _EflaProjFn(torch.autograd.Function):
         tail = dproj[..., P * hd:]
         tail.zero_()
         tail[..., :H].copy_(dbeta * beta * (1.0 - beta))
-        return dproj, None, None, None, None, (ds0 if has_s0 else None)
+        return dproj, None, None, None, None, (ds0 if has_s0 else None), None
 
 
-def efla_proj(proj, P: int, H: int, d: int, normalize: bool = True, s0=None):
+def efla_proj(proj, P: int, H: int, d: int, normalize: bool = True, s0=None, resets=None):
     """EFLA attention on a fused projection output with the beta logits in it.
     proj: (B, T, N), columns [q | k | v | H beta logits | pad] (P = 3) or [k | v | ...] (P = 2).
     Returns (o (B,T,H,d), S_T)."""
@@ -343,5 +366,6 @@ def efla_proj(proj, P: int, H: int, d: int, normalize: bool = True, s0=None):
         beta = torch.sigmoid(proj[..., P * hd:P * hd + H].float())
         q = qkv[:, :, 0]
         k = qkv[:, :, 1] if P == 3 else qkv[:, :, 0]
-        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0)
-    return _EflaProjFn.apply(proj, P, H, d, normalize, s0)
+        return efla_attention(q, k, qkv[:, :, P - 1], beta, normalize_qk=normalize, s0=s0,
+                              resets=resets)
+    return _EflaProjFn.apply(proj, P, H, d, normalize, s0, resets)

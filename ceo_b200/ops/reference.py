@@ -87,10 +87,11 @@ def efla_coefficient(beta, lam):
     return torch.where(small, series, exact)
 
 
-def delta_rule_sequential(q, k, v, alpha, s0=None):
+def delta_rule_sequential(q, k, v, alpha, s0=None, resets=None, chunk=64):
     """Token-by-token delta rule.  q,k,v: (B,T,H,d); alpha: (B,T,H).
     S_t = (I - a_t k_t k_t^T) S_{t-1} + a_t k_t v_t^T ;  o_t = S_t^T q_t.
-    Returns (o (B,T,H,dv), S_T (B,H,dk,dv))."""
+    ``resets`` (B, T/chunk): a set entry zeroes the state of that batch row before the first
+    token of the chunk.  Returns (o (B,T,H,dv), S_T (B,H,dk,dv))."""
     B, T, H, dk = k.shape
     dv = v.shape[-1]
     qf, kf, vf, af = q.float(), k.float(), v.float(), alpha.float()
@@ -99,13 +100,15 @@ def delta_rule_sequential(q, k, v, alpha, s0=None):
     outs = []
     for t in range(T):
         kt, vt, qt, at = kf[:, t], vf[:, t], qf[:, t], af[:, t]
+        if resets is not None and t % chunk == 0:
+            S = S * (~resets[:, t // chunk].bool()).to(S.dtype).view(B, 1, 1, 1)
         u = torch.einsum("bhkv,bhk->bhv", S, kt)
         S = S + at[..., None, None] * torch.einsum("bhk,bhv->bhkv", kt, vt - u)
         outs.append(torch.einsum("bhkv,bhk->bhv", S, qt))
     return torch.stack(outs, dim=1), S
 
 
-def delta_rule_chunked(q, k, v, alpha, s0=None, chunk=64):
+def delta_rule_chunked(q, k, v, alpha, s0=None, chunk=64, resets=None):
     """Chunkwise WY / UT-transform form of the same recurrence (what the CUDA kernels
     compute): per chunk A = strict_tril(diag(a) K K^T), T = (I+A)^-1 diag(a), W = T K,
     U = T V, U' = U - W S, O = Q S + tril(Q K^T) U', S += K^T U'."""
@@ -128,6 +131,8 @@ def delta_rule_chunked(q, k, v, alpha, s0=None, chunk=64):
         else s0.float().clone()
     outs = []
     for c in range(n):
+        if resets is not None:
+            S = S * (~resets[:, c].bool()).to(S.dtype).view(B, 1, 1, 1)
         Up = U[:, :, c] - W[:, :, c] @ S
         outs.append(qf[:, :, c] @ S + P[:, :, c] @ Up)
         S = S + kf[:, :, c].transpose(-1, -2) @ Up

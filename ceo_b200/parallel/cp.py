@@ -26,11 +26,11 @@ from .symm import SymmetricBuffer
 
 _IDX = {"q": 0, "k": 1, "v": 2, "alpha": 3, "w": 4, "u": 5, "up": 6, "states": 7, "o": 8,
         "s0": 9, "s_final": 10, "dO": 11, "dloc": 12, "dup": 13, "dstates": 14, "ds_final": 15,
-        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20, "p_final": 21, "xinv": 23}
+        "ds0": 16, "dq": 17, "dk": 18, "dv": 19, "dalpha": 20, "p_final": 21, "xinv": 23, "resets": 24}
 
 
 def _stage(stage: int, tensors: dict, strides, B, T, H, d):
-    ptrs = (ctypes.c_void_p * 24)()
+    ptrs = (ctypes.c_void_p * 25)()
     for k, t in tensors.items():
         ptrs[_IDX[k]] = None if t is None else t.data_ptr()
     ptrs[22] = _lib.status_word(torch.device("cuda", torch.cuda.current_device())).data_ptr()

@@ -194,3 +194,39 @@ def test_telemetry_files_and_prometheus(tmp_path):
     assert st.avg_loss() == 3.0 and st.tokens_per_sec() == 200.0
     assert check_nan_inf([1.0, float("nan")]) and not check_nan_inf([1.0, 2.0])
     assert not HealthStatus(memory_ok=False).healthy()
+
+
+def test_aligned_packing_and_state_resets_match_separate_documents():
+    """Documents packed on 64-token boundaries with resets give, per document, the loss the
+    model gives that document alone."""
+    import numpy as np
+    import torch
+    from ceo_b200.data.dataset import pack_sequences, packed_batch
+    from ceo_b200.models.model import EflaLM
+    from ceo_b200.utils.config import Config
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = Config.parse_from_file(os.path.join(root, "configs", "smoke_cpu.yaml")).model
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(1, cfg.vocab_size, size=n) for n in (70, 100, 40, 129)]
+    packs = pack_sequences(docs, 321, align=64)
+    assert [p.cumulative_lengths for p in packs] == [[0, 70, 228, 296], [0, 129]]
+    tokens, targets, resets = packed_batch(packs)
+    assert tokens.shape == (2, 320) and resets.tolist() == [[True, False, True, False, True],
+                                                            [True, False, False, False, False]]
+    model = EflaLM(cfg, "cpu", dtype=torch.float32, seed=0)
+    packed = model(tokens, targets, resets=resets)
+    # the same documents one by one (each padded to a multiple of 64 with ignored targets)
+    num, den = 0.0, 0
+    for d in docs:
+        T = -(-(len(d) - 1) // 64) * 64
+        tok = torch.zeros(1, T, dtype=torch.long)
+        tgt = torch.full((1, T), -100, dtype=torch.long)
+        tok[0, :len(d) - 1] = torch.from_numpy(d[:-1])
+        tgt[0, :len(d) - 1] = torch.from_numpy(d[1:])
+        n = len(d) - 1
+        num += float(model(tok, tgt)) * n
+        den += n
+    assert abs(float(packed) - num / den) < 2e-5
+    # without the resets the documents leak into each other
+    assert abs(float(model(tokens, targets)) - num / den) > 1e-4

@@ -155,3 +155,33 @@ def test_efla_proj_with_beta_logits_in_projection(P, normalize):
     assert _rel(a.grad[..., :P * hd], b.grad[..., :P * hd]) < 4e-2
     assert _rel(a.grad[..., P * hd:P * hd + H], b.grad[..., P * hd:P * hd + H]) < 5e-2
     assert float(a.grad[..., P * hd + H:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("B,T,H,d", [(2, 256, 2, 64), (2, 320, 2, 128)])
+def test_efla_document_resets_forward_and_backward(B, T, H, d):
+    """Chunk-aligned state resets (packed documents): kernels against the chunked oracle."""
+    q, k, v, alpha = _inputs(B, T, H, d, seed=3)
+    n = T // 64
+    g = torch.Generator(device=DEV).manual_seed(4)
+    do = torch.randn(B, T, H, d, device=DEV, generator=g).to(torch.bfloat16)
+    resets = torch.zeros(B, n, dtype=torch.bool, device=DEV)
+    resets[0, 0] = resets[0, 2] = resets[1, 1] = resets[1, n - 1] = True
+    s0 = 0.1 * torch.randn(B, H, d, d, device=DEV, generator=g)
+    dsf = 0.05 * torch.randn(B, H, d, d, device=DEV, generator=g)
+
+    leaves = [t.detach().clone().requires_grad_() for t in (q, k, v, alpha)]
+    s0k = s0.clone().requires_grad_()
+    o, s = efla.delta_rule(*leaves, s0k, resets=resets)
+    ((o.float() * do.float()).sum() + (s * dsf).sum()).backward()
+
+    rl = [t.detach().float().requires_grad_() for t in (q, k, v, alpha)]
+    s0r = s0.clone().requires_grad_()
+    o_r, s_r = ref.delta_rule_chunked(*rl, s0r, 64, resets)
+    ((o_r * do.float()).sum() + (s_r * dsf).sum()).backward()
+    assert _rel(o, o_r) < 2e-2 and _rel(s, s_r) < 2e-2
+    for nme, a, b in zip(["dq", "dk", "dv", "dalpha"], leaves, rl):
+        assert _rel(a.grad, b.grad) < 3e-2, (nme, _rel(a.grad, b.grad))
+    # row 0 resets at chunk 0: its initial state has no effect, so no gradient either
+    assert s0k.grad[0].abs().max().item() == 0.0
+    assert _rel(s0k.grad[1], s0r.grad[1]) < 3e-2
+    assert _lib.read_status() == 0
