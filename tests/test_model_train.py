@@ -148,8 +148,8 @@ def test_smoke_config_loss_decreases_and_matches_oracle():
         chunked = float(eng.model(tok, tgt))
         orig = efla.delta_rule
         try:
-            efla.delta_rule = lambda q, k, v, a, s0=None, impl="auto": orig(q, k, v, a, s0,
-                                                                             "sequential")
+            efla.delta_rule = lambda q, k, v, a, s0=None, impl="auto", resets=None: orig(
+                q, k, v, a, s0, "sequential", resets)
             sequential = float(eng.model(tok, tgt))
         finally:
             efla.delta_rule = orig
