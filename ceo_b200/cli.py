@@ -28,7 +28,7 @@ USAGE = """efla-train <command> [options]
                | encode --tokenizer T (--text S | --input F) [--output O]
                | decode --tokenizer T --tokens 1,2,3
   validate     --config C
-  profile      (prints how to profile a run)
+  profile      [--config C --micro-batches N --out F]  (hints, or a per-kernel time table)
   version | help
 """
 
@@ -234,12 +234,38 @@ def run_validate(args: ArgParser) -> int:
 
 
 def run_profile(args: ArgParser) -> int:
-    print("Timing: python bench.py --gpus 1 (CUDA events, device-timed)\n"
-          "Per-kernel roofline: python -m ceo_b200.utils.kernel_bench --torch\n"
-          "Launch list: ncu --metrics gpu__time_duration.sum --clock-control none -c 4000 --csv "
-          "python bench.py --steps 1 --warmup 1 --global-batch 4 --skip-e2e\n"
-          "One kernel in depth: ncu --set full --clock-control none -k regex:<kernel> -c 3 "
-          "-o prof <small command>")
+    """Without --config: how to profile.  With --config on a GPU machine: one training step of
+    that config under the in-process profiler, as a per-kernel time table (a diagnostic, not a
+    benchmark: bench.py times without any profiler)."""
+    o = _options(args, {"--config": ("str", None), "--micro-batches": ("int", 2),
+                        "--out": ("str", None)})
+    hints = ("Timing: python bench.py --gpus 1 (CUDA events, device-timed)\n"
+             "Per-kernel roofline: python -m ceo_b200.utils.kernel_bench --torch\n"
+             "Launch list: ncu --metrics gpu__time_duration.sum --clock-control none -c 4000 --csv "
+             "python bench.py --steps 1 --warmup 1 --global-batch 4 --skip-e2e\n"
+             "One kernel in depth: ncu --set full --clock-control none -k regex:<kernel> -c 3 "
+             "-o prof <small command>\n"
+             "Timeline ranges: CEO_TRACE=1 puts NVTX ranges around forward / backward / optimizer")
+    import torch
+    if not o.get("config") or not torch.cuda.is_available():
+        print(hints)
+        return 0
+    from .data.synthetic import SyntheticTokens
+    from .runtime.engine import TrainEngine
+    from .utils import tracing
+    cfg = Config.parse_from_file(o["config"])
+    cfg.runtime.world_size, cfg.runtime.tensor_parallel_size = 1, 1
+    dev = torch.device("cuda", 0)
+    eng = TrainEngine(cfg, dev, None)
+    data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
+                           cfg.data.synthetic.s, cfg.data.synthetic.seed, 0)
+    mb = [tuple(t.to(dev) for t in data.batch(cfg.training.micro_batch_size, cfg.data.seq_len))
+          for _ in range(int(o["micro_batches"]))]
+    text = tracing.format_table(tracing.kernel_table(lambda: eng.train_step(mb, 1e-4)))
+    print(text)
+    if o.get("out"):
+        with open(o["out"], "w") as f:
+            f.write(text + "\n")
     return 0
 
 

@@ -10,6 +10,8 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.tracing import trace_range
+
 from ..models.model import EflaLM
 from ..optim.flat import FlatParams
 from ..optim.optimizers import LRScheduler, build_optimizer
@@ -71,12 +73,15 @@ class TrainEngine:
                         nxt = tuple(self._to_device(x) for x in batches[i + 1])
             else:
                 tok, tgt = batches[i]
-            loss = self.model(tok, tgt, self.label_smoothing)
-            loss.backward()
+            with trace_range("forward"):
+                loss = self.model(tok, tgt, self.label_smoothing)
+            with trace_range("backward"):
+                loss.backward()
             total += loss.detach().float()
             self.tokens_seen += tok.numel() * self.world
         # mean over micro-batches and data-parallel ranks (the collectives sum)
-        gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.world))
+        with trace_range("optimizer"):
+            gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.world))
         self.scheduler.step()
         self.step_count += 1
         mean = total / n
