@@ -700,7 +700,7 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     warp_gemm_swz<MT, NT, CH, true, true>(dacc, Wt, r * 16 * MT, dUpt, cw);
     __syncwarp();
     if (lane == 0) mbar_arrive(&sy->empty[i & 1]);
-    if (rz && i + 1 < n) {
+    if (rz) {  // also for chunk 0: a reset there makes the initial state irrelevant
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) zero_acc<NT>(dacc[mt]);
     }
