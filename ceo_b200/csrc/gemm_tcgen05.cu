@@ -389,6 +389,109 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           __syncwarp();
         }
+      } else if (!p.out_f32 && !p.accumulate && !p.bias && ((p.N | p.ldc) & 7) == 0 &&
+                 (!p.residual || (p.ldr & 7) == 0)) {
+        // bf16 output (+ bf16 residual): same 64-column transpose through the per-warp tile,
+        // so both the residual read and the store move whole 128-byte lines (a lane-per-row
+        // store touches 32 different lines per instruction)
+        uint8_t* sb = smem + STAGES * STAGE_BYTES + 256 + quad * EPI_WARP_BYTES;
+        const int row0 = m0 + quad * 32;  // row of lane 0
+        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(cbase) +
+                               static_cast<long long>(b) * p.batch_stride_c +
+                               static_cast<long long>(row0) * p.ldc;
+        const __nv_bfloat16* rbase =
+            p.residual ? reinterpret_cast<const __nv_bfloat16*>(p.residual) +
+                             static_cast<long long>(b) * p.batch_stride_r +
+                             static_cast<long long>(row0) * p.ldr
+                       : nullptr;
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          const int ncol = n0 + c2 * 64 + (lane & 7) * 8;
+          if (rbase) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = i * 4 + (lane >> 3);
+              uint4 o = make_uint4(0, 0, 0, 0);
+              if (row0 + rl < p.M && ncol < p.N)
+                o = *reinterpret_cast<const uint4*>(rbase + static_cast<long long>(rl) * p.ldr + ncol);
+              *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = o;
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c2 * 64 + hc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4* slot = reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16);
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q4 * 8 + j]) * p.alpha;
+              if (rbase) {
+                const uint4 u = *slot;
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(h[j]);
+                  f[2 * j] += x.x;
+                  f[2 * j + 1] += x.y;
+                }
+              }
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *slot = o;
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            if (row0 + rl < p.M && ncol < p.N)
+              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol) = o;
+          }
+          __syncwarp();
+        }
+      } else if (p.out_f32 && !p.bias && !p.residual && p.split_k == 1 &&
+                 ((p.N | p.ldc) & 3) == 0) {
+        // fp32 output (weight gradients, usually accumulating): 32 columns at a time through
+        // the same per-warp tile, so the read-modify-write of C moves whole 128-byte lines
+        uint8_t* sb = smem + STAGES * STAGE_BYTES + 256 + quad * EPI_WARP_BYTES;
+        const int row0 = m0 + quad * 32;
+        float* gbase = reinterpret_cast<float*>(cbase) + static_cast<long long>(b) * p.batch_stride_c +
+                       static_cast<long long>(row0) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(sb + lane * EPI_ROW_BYTES + q * 16) =
+                make_float4(__uint_as_float(v[4 * q]) * p.alpha, __uint_as_float(v[4 * q + 1]) * p.alpha,
+                            __uint_as_float(v[4 * q + 2]) * p.alpha,
+                            __uint_as_float(v[4 * q + 3]) * p.alpha);
+          __syncwarp();
+          const int ncol = n0 + c * 32 + (lane & 7) * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            float4 o = *reinterpret_cast<const float4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            if (row0 + rl < p.M && ncol < p.N) {
+              float4* dst = reinterpret_cast<float4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol);
+              if (p.accumulate) {
+                const float4 old = *dst;
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *dst = o;
+            }
+          }
+          __syncwarp();
+        }
       } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
