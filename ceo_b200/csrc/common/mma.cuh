@@ -168,6 +168,35 @@ __device__ __forceinline__ void warp_gemm_swz(float (*acc)[NT][4], const SwzTile
       }
   }
 }
+// Same product with the k-steps dealt alternately to two accumulator sets that are summed at
+// the end: for a single row tile with a long K the dependent MMA chain is what bounds the
+// time, and this halves it (used on the serial critical path of the state recurrences).
+template <int NT, int K, bool A_T, bool B_T>
+__device__ __forceinline__ void warp_gemm_swz_2chain(float (*acc)[4], const SwzTile& A, int m0,
+                                                     const SwzTile& B, int n0) {
+  static_assert(NT % 2 == 0 && K % 32 == 0, "tile shape");
+  float acc2[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f;
+  uint32_t a[2][1][4], b[2][NT / 2][4];
+  warp_frags_swz<1, NT, A_T, B_T>(a[0], b[0], A, m0, B, n0, 0);
+#pragma unroll
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    const int cur = (k0 / 16) & 1;
+    if (k0 + 16 < K) warp_frags_swz<1, NT, A_T, B_T>(a[cur ^ 1], b[cur ^ 1], A, m0, B, n0, k0 + 16);
+    float (*dst)[4] = cur ? acc2 : acc;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt += 2) {
+      mma16816(dst[nt], a[cur][0], b[cur][nt / 2]);
+      mma16816(dst[nt + 1], a[cur][0], b[cur][nt / 2] + 2);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] += acc2[i][e];
+}
+
 // Stores a 16 x 8*NT accumulator tile as bf16 at rows m0.., columns n0.. of a swizzled tile.
 template <int NT>
 __device__ __forceinline__ void frag_store_swz(const SwzTile& t, int m0, int n0,

@@ -681,7 +681,7 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     {
       float acc[1][NT][4];
       zero_acc<NT>(acc[0]);
-      warp_gemm_swz<1, NT, D, false, true>(acc, Kt, 16 * r, dSt, cw);
+      warp_gemm_swz_2chain<NT, D, false, true>(acc[0], Kt, 16 * r, dSt, cw);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll

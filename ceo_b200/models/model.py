@@ -47,10 +47,14 @@ class Norm(nn.Module):
         self.bias = nn.Parameter(torch.zeros(dim, device=device, dtype=dtype)) \
             if kind == "layernorm" else None
 
-    def forward(self, x):
+    def forward(self, x, skip: bool = False):
+        """``skip=True`` returns ``(y, x_skip)``: use ``x_skip`` where the residual stream goes
+        on (RMSNorm folds the gradient add into its backward kernel)."""
         if self.kind == "rmsnorm":
-            return K.rmsnorm(x, self.weight, self.eps)[0]
-        return K.layernorm(x, self.weight, self.bias, self.eps)
+            y, xs = K.rmsnorm(x, self.weight, self.eps, skip=skip)
+            return (y, xs) if skip else y
+        y = K.layernorm(x, self.weight, self.bias, self.eps)
+        return (y, x) if skip else y
 
 
 class EflaLayer(nn.Module):
@@ -139,14 +143,15 @@ class Block(nn.Module):
         self.mlp = MLP(cfg, device, dtype, gen, std)
 
     def forward(self, h, state=None, resets=None):
-        n1 = self.ln1(h)
+        n1, h = self.ln1(h, skip=True)
         o, s_final = self.efla(n1, h, state, resets)
         if self.prism is not None:
             a = linear(o, self.efla.w_o)
             h = h + self.prism(n1, a)
         else:
             h = linear(o, self.efla.w_o, h)
-        h = self.mlp(self.ln2(h), h)
+        n2, h = self.ln2(h, skip=True)
+        h = self.mlp(n2, h)
         return h, s_final
 
     def decode_step(self, h, state):

@@ -109,16 +109,18 @@ class ParallelBlock(nn.Module):
 
     def forward(self, h, B, T, tp=None, cp=None, impl="fused"):
         """h: (rows, D) - all B*T local tokens without tp, this rank's row shard with tp."""
-        n1 = self.ln1(h)
+        n1, h = self.ln1(h, skip=True)
         proj = column_parallel_linear(n1, self.w_qkv, tp, impl) if tp is not None \
             else linear(n1, self.w_qkv)
         o = self._attention(proj, B, T, cp).reshape(B * T, self.H_loc * self.d)
         if tp is not None:
             h = row_parallel_linear(o, self.w_o, tp, residual=h, impl=impl)
-            u = column_parallel_linear(self.ln2(h), self.w_up, tp, impl)
+            n2, h = self.ln2(h, skip=True)
+            u = column_parallel_linear(n2, self.w_up, tp, impl)
         else:
             h = linear(o, self.w_o, h)
-            u = linear(self.ln2(h), self.w_up)
+            n2, h = self.ln2(h, skip=True)
+            u = linear(n2, self.w_up)
         a = K.swiglu(u) if self.act == "swiglu" else K.activation(u, self.act)
         if tp is not None:
             return row_parallel_linear(a, self.w_down, tp, residual=h, impl=impl)

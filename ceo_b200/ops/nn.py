@@ -19,7 +19,7 @@ ACT_MODES = {"gelu": 0, "gelu_tanh": 0, "gelu_erf": 1, "silu": 2, "relu": 3}
 # --------------------------------------------------------------------------- RMSNorm
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, residual, eps):
+    def forward(ctx, x, weight, residual, eps, skip=False):
         shp = x.shape
         D = shp[-1]
         x2 = x.reshape(-1, D)
@@ -42,6 +42,10 @@ class _RMSNormFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         if residual is not None:
             return y.view(shp), h.view(shp)
+        if skip:
+            # the input itself is the second output: the gradient of every other use of it (the
+            # residual stream) arrives here as `dh` and is added inside the backward kernel
+            return y.view(shp), x
         return y.view(shp), None
 
     @staticmethod
@@ -75,15 +79,19 @@ class _RMSNormFn(torch.autograd.Function):
         dx = dx.view(ctx.shape)
         if dw_ret is not None:
             dw_ret = dw_ret.to(weight.dtype)
-        return dx, dw_ret, (dx if ctx.has_res else None), None
+        return dx, dw_ret, (dx if ctx.has_res else None), None, None
 
 
-def rmsnorm(x, weight, eps: float = 1e-6, residual=None):
+def rmsnorm(x, weight, eps: float = 1e-6, residual=None, skip: bool = False):
     """``y = rmsnorm(x + residual) * weight``.  Returns ``(y, h)`` with ``h = x + residual``
-    (``h`` is None when there is no residual)."""
+    (``h`` is None when there is no residual).  ``skip=True`` (no residual): ``h`` is ``x``
+    routed through this op, to be used wherever the residual stream continues, so that its
+    gradient is added to the normalisation's inside the backward kernel instead of by a
+    separate elementwise add."""
     if not x.is_cuda:
-        return ref.rmsnorm(x, weight, eps, residual)
-    return _RMSNormFn.apply(x, weight, residual, eps)
+        y, h = ref.rmsnorm(x, weight, eps, residual)
+        return y, (x if (skip and residual is None) else h)
+    return _RMSNormFn.apply(x, weight, residual, eps, skip and residual is None)
 
 
 # ------------------------------------------------------------------------- LayerNorm
