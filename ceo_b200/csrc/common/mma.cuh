@@ -1,6 +1,6 @@
 // Warp-level bf16 tensor-core tiles out of shared memory (ldmatrix + mma.sync
 // m16n8k16, fp32 accumulate) for the small per-chunk products of the EFLA kernels
-// (64x64x128 and the like), where one warp owns 16 output rows.
+// (64x64x128 and the like), where one warp owns 16 or 32 output rows.
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -29,71 +29,7 @@ __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, const uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// acc[MT][NT][4] += A (16*MT x K) * B (K x 8*NT), operands in shared memory (bf16).
-//   A_T = false: A stored [m][k] with leading dimension lda; `A` points at (m0, 0)
-//   A_T = true : A stored [k][m];                            `A` points at (0, m0)
-//   B_T = false: B stored [n][k] with leading dimension ldb; `B` points at (n0, 0)
-//   B_T = true : B stored [k][n];                            `B` points at (0, n0)
-// Rows of both tiles must start on 16-byte boundaries (lda, ldb multiples of 8).
-// Accumulator layout (g = lane/4, t = lane%4): acc[mt][nt][0..1] -> row 16*mt+g, cols
-// nt*8+2t, +1; acc[mt][nt][2..3] -> row 16*mt+g+8, same cols.
-// The MT row tiles share every B fragment, and the fragments of k-step i+1 are requested
-// before the MMAs of k-step i are issued (two register sets), so ldmatrix latency overlaps
-// the tensor work; the asm statements are volatile, hence emitted in exactly this order.
-template <int MT, int NT, bool A_T, bool B_T>
-__device__ __forceinline__ void warp_frags(uint32_t (*a)[4], uint32_t (*b)[4],
-                                           const __nv_bfloat16* A, int lda,
-                                           const __nv_bfloat16* B, int ldb, int k0) {
-  const int lane = threadIdx.x & 31;
-  const int l7 = lane & 7, b3 = (lane >> 3) & 1, b4 = lane >> 4;
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-    if (!A_T)
-      ldsm_x4(a[mt], smem_addr(A + (mt * 16 + l7 + b3 * 8) * lda + k0 + b4 * 8));
-    else
-      ldsm_x4_t(a[mt], smem_addr(A + (k0 + l7 + b4 * 8) * lda + mt * 16 + b3 * 8));
-  }
-#pragma unroll
-  for (int nt = 0; nt < NT; nt += 2) {
-    if (!B_T)
-      ldsm_x4(b[nt / 2], smem_addr(B + (nt * 8 + l7 + b4 * 8) * ldb + k0 + b3 * 8));
-    else
-      ldsm_x4_t(b[nt / 2], smem_addr(B + (k0 + l7 + b3 * 8) * ldb + nt * 8 + b4 * 8));
-  }
-}
-
-template <int MT, int NT, int K, bool A_T, bool B_T>
-__device__ __forceinline__ void warp_gemm_mt(float (*acc)[NT][4], const __nv_bfloat16* A, int lda,
-                                             const __nv_bfloat16* B, int ldb) {
-  static_assert(NT % 2 == 0 && K % 16 == 0, "tile shape");
-  constexpr bool PIPE = (4 * MT + 2 * NT) <= 24;  // two fragment sets only while they are cheap
-  constexpr int NB = PIPE ? 2 : 1;
-  uint32_t a[NB][MT][4], b[NB][NT / 2][4];
-  if (PIPE) warp_frags<MT, NT, A_T, B_T>(a[0], b[0], A, lda, B, ldb, 0);
-#pragma unroll
-  for (int k0 = 0; k0 < K; k0 += 16) {
-    const int cur = PIPE ? (k0 / 16) & 1 : 0;
-    if (!PIPE) warp_frags<MT, NT, A_T, B_T>(a[0], b[0], A, lda, B, ldb, k0);
-    if (PIPE && k0 + 16 < K)
-      warp_frags<MT, NT, A_T, B_T>(a[cur ^ 1], b[cur ^ 1], A, lda, B, ldb, k0 + 16);
-#pragma unroll
-    for (int nt = 0; nt < NT; nt += 2)
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        mma16816(acc[mt][nt], a[cur][mt], b[cur][nt / 2]);
-        mma16816(acc[mt][nt + 1], a[cur][mt], b[cur][nt / 2] + 2);
-      }
-  }
-}
-
-// One row tile: acc[NT][4] += A (16 x K) * B (K x 8*NT).
-template <int NT, int K, bool A_T, bool B_T>
-__device__ __forceinline__ void warp_gemm(float (*acc)[4], const __nv_bfloat16* A, int lda,
-                                          const __nv_bfloat16* B, int ldb) {
-  warp_gemm_mt<1, NT, K, A_T, B_T>(reinterpret_cast<float (*)[NT][4]>(acc), A, lda, B, ldb);
-}
-
-// ---- the same products over tiles in the layout TMA writes with 128-byte swizzle ----------
+// ---- products over tiles in the layout TMA writes with 128-byte swizzle ------------------
 // A tile of R rows x C columns (bf16) is stored as C/64 panels of R rows x 128 bytes; inside a
 // panel the 16-byte chunk j of row r sits at chunk (j ^ (r & 7)).  Panels start on 1024-byte
 // boundaries.  ldmatrix rows are whole chunks, so fragments load conflict-free.
@@ -122,8 +58,15 @@ __device__ __forceinline__ float2 lds_bf162(uint32_t addr) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
 }
 
-// acc[MT][NT][4] += A * B with A rows m0.. and B columns n0.. of swizzled tiles (A_T / B_T as
-// in warp_gemm_mt: false = tile stored [m][k] / [n][k], true = stored [k][m] / [k][n]).
+// acc[MT][NT][4] += A (16*MT x K) * B (K x 8*NT) with A rows m0.. and B columns n0.. of
+// swizzled tiles.
+//   A_T = false: A tile stored [m][k];  true: stored [k][m]
+//   B_T = false: B tile stored [n][k];  true: stored [k][n]
+// Accumulator layout (g = lane/4, t = lane%4): acc[mt][nt][0..1] -> row 16*mt+g, cols
+// nt*8+2t, +1; acc[mt][nt][2..3] -> row 16*mt+g+8, same cols.
+// The MT row tiles share every B fragment, and the fragments of k-step i+1 are requested
+// before the MMAs of k-step i are issued (two register sets), so ldmatrix latency overlaps
+// the tensor work; the asm statements are volatile, hence emitted in exactly this order.
 template <int MT, int NT, bool A_T, bool B_T>
 __device__ __forceinline__ void warp_frags_swz(uint32_t (*a)[4], uint32_t (*b)[4],
                                                const SwzTile& A, int m0, const SwzTile& B, int n0,
@@ -213,19 +156,6 @@ template <int NT>
 __device__ __forceinline__ void zero_acc(float (*acc)[4]) {
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-}
-
-// cp.async 16-byte copy, global -> shared
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gsrc)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 }  // namespace ceo

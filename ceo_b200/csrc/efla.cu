@@ -492,6 +492,192 @@ efla_out_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   frag_store_bf16<NT>(o + (static_cast<long long>(tok0) + 16 * r) * HD + h * D + c0, HD, acc);
 }
 
+// ===================================================== forward: O on tcgen05 (D = 128)
+// Two adjacent chunks per CTA, so that every product has a 128-row operand for the 5th-gen
+// tensor core (accumulators in TMEM, operands read by the MMA unit straight from the TMA
+// tiles):
+//   P   (128 x 128) = [Q1;Q2] [K1;K2]^T        only the two 64x64 diagonal blocks are used
+//   O_i^T (128 x 64) = S_i^T Q_i^T + U'_i^T P_i^T     (M = value dim, N = the chunk's tokens)
+// The transposed form makes the value dimension the 128-lane M of the MMA: S_i and U'_i are
+// read as M-major operands exactly as TMA lays them out, Q_i and the masked P_i as K-major
+// ones.  128 threads = the 128 TMEM lanes; thread 0 also issues the TMA requests and MMAs.
+constexpr int OUT_TC_THREADS = 128;
+constexpr int OUT_TC_SMEM = 2 * 32768 /*Q,K*/ + 2 * 16384 /*U'*/ + 2 * 32768 /*S*/ + 2 * PANEL /*P*/ +
+                            64 /*barriers + TMEM slot*/ + 1024;
+
+__global__ void __launch_bounds__(OUT_TC_THREADS, 1)
+efla_out_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_up,
+                   const __grid_constant__ CUtensorMap tm_states, bf16* __restrict__ o, int T,
+                   int H, int* status) {
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* Qs = smem;                 // 128 tokens x 128: two panels of 128 rows x 128 B
+  uint8_t* Ks = Qs + 32768;
+  uint8_t* Ups = Ks + 32768;          // per chunk: 64 tokens x 128 (two 64-row panels)
+  uint8_t* Sb = Ups + 2 * 16384;      // per chunk: 128 x 128 (two 128-row panels)
+  uint8_t* Ps = Sb + 2 * 32768;       // per chunk: 64 x 64, one panel
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * PANEL);  // 0,1: TMA; 2,3,4: MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, n = T / CH;
+  const int c0 = 2 * blockIdx.x;                 // first chunk of the pair
+  const int tok0 = b * T + c0 * CH;
+  const long long HD = static_cast<long long>(H) * D;
+  const int warp = threadIdx.x >> 5;
+  // bounded wait that gives up at once when any wait of the grid has already run out
+  auto waitb = [&](uint64_t* bar) {
+    if (status && *reinterpret_cast<volatile int*>(status)) return false;
+    return mbar_wait(bar, 0);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bars[0], 2 * 32768);
+#pragma unroll
+    for (int pnl = 0; pnl < 2; ++pnl)
+#pragma unroll
+      for (int rh = 0; rh < 2; ++rh) {
+        tma_load_2d(Qs + pnl * 16384 + rh * 8192, &tm_q, &bars[0], h * D + pnl * 64, tok0 + rh * 64);
+        tma_load_2d(Ks + pnl * 16384 + rh * 8192, &tm_k, &bars[0], h * D + pnl * 64, tok0 + rh * 64);
+      }
+    mbar_arrive_expect_tx(&bars[1], 2 * 16384 + 2 * 32768);
+#pragma unroll
+    for (int ci = 0; ci < 2; ++ci) {
+      tma_tok_tile<D>(Ups + ci * 16384, &tm_up, &bars[1], h * D, tok0 + ci * CH);
+      tma_state_tile<D>(Sb + ci * 32768, &tm_states, &bars[1], (bh * n + c0 + ci) * D);
+    }
+    // P = Q K^T for the pair
+    if (!waitb(&bars[0])) ok = false;
+    tc_fence_after();
+    if (ok) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        umma_f16(tmem, umma_smem_desc(qa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                 umma_smem_desc(ka + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), idesc, k ? 1u : 0u);
+      umma_commit(&bars[2]);
+    }
+    // O_i^T = S_i^T Q_i^T (columns 128 + 64 i of TMEM)
+    if (ok && !waitb(&bars[1])) ok = false;
+    tc_fence_after();
+    if (ok) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 64, 1, 0);
+      const uint32_t qa = smem_u32(Qs);
+#pragma unroll
+      for (int ci = 0; ci < 2; ++ci) {
+        const uint32_t sa = smem_u32(Sb + ci * 32768);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_f16(tmem + 128 + 64 * ci, umma_smem_desc(sa + k * 2048, 16384, 1024),
+                   umma_smem_desc(qa + (k >> 2) * 16384 + ci * 8192 + (k & 3) * 32, 16, 1024), idesc,
+                   k ? 1u : 0u);
+      }
+      umma_commit(&bars[3]);
+    }
+    if (!ok && status) atomicExch(status, EFLA_WAIT_STATUS);
+  }
+  __syncwarp();
+
+  // masked P -> bf16 K-major panels (thread = one token row of the pair)
+  {
+    const int ci = warp >> 1, rl = threadIdx.x & 63;
+    const bool got = waitb(&bars[2]);
+    tc_fence_after();
+    uint8_t* prow = Ps + ci * PANEL + rl * 128;
+#pragma unroll
+    for (int hc = 0; hc < 2; ++hc) {
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 64 * ci + hc * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 o4;
+        bf162* oh = reinterpret_cast<bf162*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = hc * 32 + q4 * 8 + 2 * j;
+          oh[j] = __floats2bfloat162_rn(got && col <= rl ? __uint_as_float(v[q4 * 8 + 2 * j]) : 0.f,
+                                        got && col + 1 <= rl ? __uint_as_float(v[q4 * 8 + 2 * j + 1])
+                                                             : 0.f);
+        }
+        const int chunk = hc * 4 + q4;
+        *reinterpret_cast<uint4*>(prow + ((chunk ^ (rl & 7)) << 4)) = o4;
+      }
+    }
+  }
+  fence_proxy_async_smem();  // the MMA unit reads P through the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (threadIdx.x == 0) {
+    // O_i^T += U'_i^T P_i^T
+    bool ok2 = waitb(&bars[3]);
+    tc_fence_after();
+    if (ok2) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 64, 1, 0);
+#pragma unroll
+      for (int ci = 0; ci < 2; ++ci) {
+        const uint32_t ua = smem_u32(Ups + ci * 16384), pa = smem_u32(Ps + ci * PANEL);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem + 128 + 64 * ci, umma_smem_desc(ua + k * 2048, 8192, 1024),
+                   umma_smem_desc(pa + k * 32, 16, 1024), idesc, 1u);
+      }
+      umma_commit(&bars[4]);
+    } else if (status) {
+      atomicExch(status, EFLA_WAIT_STATUS);
+    }
+  }
+  __syncwarp();
+
+  // O^T (lane = value index) -> staging [token][value] in the dead Q tile -> coalesced stores
+  {
+    const bool got = waitb(&bars[4]);
+    tc_fence_after();
+    bf16* stage = reinterpret_cast<bf16*>(Qs);
+#pragma unroll 1
+    for (int cc = 0; cc < 4; ++cc) {  // 4 x 32 tokens
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 128 + cc * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        stage[(cc * 32 + j) * D + threadIdx.x] = __float2bfloat16(got ? __uint_as_float(v[j]) : 0.f);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  {
+    const uint4* stage = reinterpret_cast<const uint4*>(Qs);
+    for (int i = threadIdx.x; i < 128 * 16; i += OUT_TC_THREADS) {
+      const int row = i >> 4, cu = i & 15;
+      *reinterpret_cast<uint4*>(o + (static_cast<long long>(tok0) + row) * HD + h * D + cu * 8) =
+          stage[i];
+    }
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
 // ============================================== backward: dQ and D = P^T dO
 template <int D>
 __global__ void __launch_bounds__(256, 2)
@@ -1078,6 +1264,7 @@ static cudaError_t efla_configure() {
   if ((e = set_smem(efla_wy_kernel<D>, smem_wy<D>())) != cudaSuccess) return e;
   if ((e = set_smem(efla_state_fwd_kernel<D>, smem_state_fwd<D>())) != cudaSuccess) return e;
   if ((e = set_smem(efla_out_kernel<D>, smem_out<D>())) != cudaSuccess) return e;
+  if (D == 128 && (e = set_smem(efla_out_tc_kernel, OUT_TC_SMEM)) != cudaSuccess) return e;
   if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
   if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
   if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
@@ -1140,8 +1327,12 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
       MAP(tok(&m[1], I_K, t.stride[1]));
       MAP(tok(&m[2], I_UP, HD));
       MAP(sta(&m[3], I_STATES));
-      efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(m[0], m[1], m[2], m[3], b16(I_O), T, H,
-                                                           status);
+      if (D == 128 && (n & 1) == 0)  // chunk pairs on the tcgen05 path
+        efla_out_tc_kernel<<<dim3(n / 2, B * H), OUT_TC_THREADS, OUT_TC_SMEM, st>>>(
+            m[0], m[1], m[2], m[3], b16(I_O), T, H, status);
+      else
+        efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(m[0], m[1], m[2], m[3], b16(I_O), T,
+                                                             H, status);
       break;
     case 3:
       MAP(tok(&m[0], I_Q, t.stride[0]));
