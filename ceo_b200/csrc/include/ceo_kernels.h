@@ -60,6 +60,9 @@ int ceo_efla_bwd(const void* q, const void* k, const void* v, const float* alpha
                  int H, int D, long long q_stride, long long k_stride,
                  long long v_stride, long long dq_stride, long long dk_stride,
                  long long dv_stride, int* status, cudaStream_t stream);
+/* 1: compute the chunk outputs with the tcgen05 kernel (chunk pairs, D = 128, even chunk count;
+ * other shapes keep the warp-MMA kernel).  Default 0: it is the slower of the two today. */
+int ceo_efla_set_tcgen05(int on);
 /* One of the six EFLA kernels at a time (0 wy, 1 state_fwd, 2 out, 3 bwd_local, 4 state_bwd,
  * 5 bwd_final).  ptrs (host array of 25 device pointers): 0 q, 1 k, 2 v, 3 alpha, 4 w, 5 u,
  * 6 up, 7 states, 8 o, 9 s0, 10 s_final, 11 dO, 12 dloc, 13 dup, 14 dstates, 15 ds_final,

@@ -29,7 +29,7 @@ _scratch = {}
 # kernels launched per entry point (everything not listed launches exactly one)
 _LAUNCHES = {"ceo_efla_fwd": 3, "ceo_efla_bwd": 3, "ceo_rmsnorm_bwd": 2, "ceo_layernorm_bwd": 4,
              "ceo_sumsq": 2, "ceo_reduce": 2, "ceo_muon_momentum": 2, "ceo_norm_bwd_blocks": 0,
-             "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0, "ceo_cumsum_scratch_floats": 0}
+             "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0, "ceo_cumsum_scratch_floats": 0, "ceo_efla_set_tcgen05": 0}
 launch_count = 0
 
 

@@ -185,3 +185,19 @@ def test_efla_document_resets_forward_and_backward(B, T, H, d):
     assert s0k.grad[0].abs().max().item() == 0.0
     assert _rel(s0k.grad[1], s0r.grad[1]) < 3e-2
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 2), (2, 512, 4)])
+def test_efla_output_kernel_on_tcgen05_matches_oracle(B, T, H):
+    """The tcgen05 variant of the output kernel (off by default) against the fp32 oracle."""
+    q, k, v, alpha = _inputs(B, T, H, 128, seed=5)
+    L = _lib.lib()
+    L.ceo_efla_set_tcgen05(1)
+    try:
+        o, s = efla.delta_rule(q, k, v, alpha)
+        torch.cuda.synchronize()
+    finally:
+        L.ceo_efla_set_tcgen05(0)
+    o_r, s_r = ref.delta_rule_sequential(q, k, v, alpha)
+    assert _rel(o, o_r) < 2e-2 and _rel(s, s_r) < 2e-2
+    assert _lib.read_status() == 0
