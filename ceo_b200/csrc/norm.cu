@@ -203,6 +203,166 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
     partial[static_cast<size_t>(blockIdx.x) * D + i] = dws[i];
 }
 
+// ---------------------------------------------- RMSNorm, several rows per iteration
+// For D = NVT * 2048: thread t owns the 16-byte column chunks t, t + 256, ... of every row and
+// the CTA walks R rows per iteration.  One block reduction (one barrier, the scratch is
+// double-buffered) then serves R rows, a thread's weight-gradient partials are 8 * NVT
+// registers, and R rows of loads are in flight per thread, which is what these kernels need
+// to approach the memory bandwidth at two to four CTAs per SM.
+template <int NVT, int R>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                        const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ h_out,
+                        float* __restrict__ rstd, int rows, float eps) {
+  constexpr int D = NVT * 2048, NW = NORM_THREADS / 32;
+  __shared__ float red[2][NW][R];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4 wp[NVT];
+#pragma unroll
+  for (int i = 0; i < NVT; ++i) wp[i] = reinterpret_cast<const uint4*>(w)[threadIdx.x + i * NORM_THREADS];
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, it ^= 1) {
+    uint4 xv[R][NVT];
+    float ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool okr = row0 + r < rows;
+      const size_t off = static_cast<size_t>(okr ? row0 + r : row0) * D;
+#pragma unroll
+      for (int i = 0; i < NVT; ++i)
+        xv[r][i] = reinterpret_cast<const uint4*>(x + off)[threadIdx.x + i * NORM_THREADS];
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool okr = row0 + r < rows;
+      const size_t off = static_cast<size_t>(okr ? row0 + r : row0) * D;
+      ss[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NVT; ++i) {
+        float v[8];
+        unpack8(xv[r][i], v);
+        if (res) {
+          float t[8];
+          unpack8(reinterpret_cast<const uint4*>(res + off)[threadIdx.x + i * NORM_THREADS], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += t[j];
+          xv[r][i] = pack8(v);  // normalise exactly what is stored as h
+          if (h_out && okr)
+            reinterpret_cast<uint4*>(h_out + off)[threadIdx.x + i * NORM_THREADS] = xv[r][i];
+          unpack8(xv[r][i], v);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss[r] += v[j] * v[j];
+      }
+      ss[r] = warp_reduce_sum(ss[r]);
+      if (lane == 0) red[it][warp][r] = ss[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float tot = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < NW; ++wi) tot += red[it][wi][r];
+      const float rs = rsqrtf(tot / D + eps);
+      if (row0 + r < rows) {
+        if (threadIdx.x == 0 && rstd) rstd[row0 + r] = rs;
+        const size_t off = static_cast<size_t>(row0 + r) * D;
+#pragma unroll
+        for (int i = 0; i < NVT; ++i) {
+          float v[8], wv[8], o[8];
+          unpack8(xv[r][i], v);
+          unpack8(wp[i], wv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[j] * rs * wv[j];
+          reinterpret_cast<uint4*>(y + off)[threadIdx.x + i * NORM_THREADS] = pack8(o);
+        }
+      }
+    }
+  }
+}
+
+template <int NVT, int R>
+__global__ void __launch_bounds__(NORM_THREADS, 2)
+rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                        const bf16* __restrict__ w, const float* __restrict__ rstd,
+                        const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ partial, int rows) {
+  constexpr int D = NVT * 2048, NW = NORM_THREADS / 32;
+  __shared__ float red[2][NW][R];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float wv[NVT][8], dwacc[NVT][8];
+#pragma unroll
+  for (int i = 0; i < NVT; ++i) {
+    unpack8(reinterpret_cast<const uint4*>(w)[threadIdx.x + i * NORM_THREADS], wv[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, it ^= 1) {
+    uint4 xv[R][NVT], gv[R][NVT];
+    float rs[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool okr = row0 + r < rows;
+      const size_t off = static_cast<size_t>(okr ? row0 + r : row0) * D;
+      rs[r] = okr ? rstd[row0 + r] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NVT; ++i) {
+        xv[r][i] = reinterpret_cast<const uint4*>(x + off)[threadIdx.x + i * NORM_THREADS];
+        gv[r][i] = reinterpret_cast<const uint4*>(dy + off)[threadIdx.x + i * NORM_THREADS];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < NVT; ++i) {
+        float xf[8], gf[8];
+        unpack8(xv[r][i], xf);
+        unpack8(gv[r][i], gf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[i][j] += gf[j] * xf[j] * rs[r];  // rs = 0 for rows past the end
+          dot += gf[j] * wv[i][j] * xf[j];
+        }
+      }
+      dot = warp_reduce_sum(dot);
+      if (lane == 0) red[it][warp][r] = dot;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) continue;
+      float tot = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < NW; ++wi) tot += red[it][wi][r];
+      const float coef = tot * rs[r] * rs[r] * rs[r] / D;
+      const size_t off = static_cast<size_t>(row0 + r) * D;
+#pragma unroll
+      for (int i = 0; i < NVT; ++i) {
+        float xf[8], gf[8], o[8];
+        unpack8(xv[r][i], xf);
+        unpack8(gv[r][i], gf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gf[j] * wv[i][j] * rs[r] - xf[j] * coef;
+        if (dres) {
+          float t[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + off)[threadIdx.x + i * NORM_THREADS], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += t[j];
+        }
+        reinterpret_cast<uint4*>(dx + off)[threadIdx.x + i * NORM_THREADS] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NVT; ++i) {
+    float* pp = partial + static_cast<size_t>(blockIdx.x) * D + (threadIdx.x + i * NORM_THREADS) * 8;
+    *reinterpret_cast<float4*>(pp) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+    *reinterpret_cast<float4*>(pp + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+  }
+}
+
 // out[c] (+)= sum_b partial[b][c]
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                        int nblk, int D, int accumulate) {
@@ -351,6 +511,22 @@ extern "C" int ceo_rmsnorm_fwd(const void* x, const void* residual, const void* 
                                void* h_out, float* rstd, int rows, int D, float eps,
                                cudaStream_t stream) {
   if (!norm_shape_ok(rows, D)) return -5;
+  if (D == 2048 || D == 4096) {
+    constexpr int R = 4;
+    int g = (rows + R - 1) / R;
+    if (g > 148 * 4) g = 148 * 4;
+    if (D == 2048)
+      rmsnorm_fwd_rows_kernel<1, R><<<g, NORM_THREADS, 0, stream>>>(
+          static_cast<const bf16*>(x), static_cast<const bf16*>(residual),
+          static_cast<const bf16*>(w), static_cast<bf16*>(y), static_cast<bf16*>(h_out), rstd, rows,
+          eps);
+    else
+      rmsnorm_fwd_rows_kernel<2, R><<<g, NORM_THREADS, 0, stream>>>(
+          static_cast<const bf16*>(x), static_cast<const bf16*>(residual),
+          static_cast<const bf16*>(w), static_cast<bf16*>(y), static_cast<bf16*>(h_out), rstd, rows,
+          eps);
+    return static_cast<int>(cudaGetLastError());
+  }
   rmsnorm_fwd_kernel<<<rows, NORM_THREADS, 0, stream>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(residual), static_cast<const bf16*>(w),
       static_cast<bf16*>(y), static_cast<bf16*>(h_out), rstd, rows, D, eps);
@@ -367,7 +543,19 @@ extern "C" int ceo_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   const bf16* wp = static_cast<const bf16*>(w);
   const bf16* rp = static_cast<const bf16*>(dres);
   bf16* dxp = static_cast<bf16*>(dx);
-  if ((D & 255) == 0 && D <= 2048) {
+  if (D == 2048 || D == 4096) {
+    const int R = D == 2048 ? 4 : 2;  // rows per iteration: bounded by the register budget
+    int g = (rows + R - 1) / R;
+    if (g > nblk) g = nblk;  // the partial scratch holds ceo_norm_bwd_blocks(rows) rows
+    if (g > 148 * 2) g = 148 * 2;
+    nblk = g;
+    if (D == 2048)
+      rmsnorm_bwd_rows_kernel<1, 4><<<g, NORM_THREADS, 0, stream>>>(dyp, xp, wp, rstd, rp, dxp,
+                                                                    partial_scratch, rows);
+    else
+      rmsnorm_bwd_rows_kernel<2, 2><<<g, NORM_THREADS, 0, stream>>>(dyp, xp, wp, rstd, rp, dxp,
+                                                                    partial_scratch, rows);
+  } else if ((D & 255) == 0 && D <= 2048) {
     int g = (rows + 7) / 8;
     if (g > 296) g = 296;
     nblk = g;
