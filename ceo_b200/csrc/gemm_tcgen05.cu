@@ -55,6 +55,7 @@ struct GemmParams {
   int m_rot, n_rot;        // tile traversal starts at this m / n block (local data first)
   int grp_m;               // row blocks per traversal group (see tile_coords)
   int split_k;             // >1: k-slices of a tile accumulate into fp32 C with atomics
+  int a_4d, b_4d;          // M/N-major operand mapped as (64, k, panel, batch): one TMA per stage
   // all-gather of one operand: the first `ag_ctas` CTAs pull the peers' row-shards into
   // the local gathered buffer (which the tensor map reads) and publish one flag per block
   // of BM (A) or BN (B) rows; the TMA producer waits for a block's flag before loading it.
@@ -187,6 +188,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int k0 = kb * BK;
           if (A_MN == 0) {
             tma_load_3d(sa, &tmA, &full_bar[s], k0, m0, b);
+          } else if (p.a_4d) {
+            tma_load_4d(sa, &tmA, &full_bar[s], 0, k0, m0 / 64, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
@@ -194,6 +197,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           if (B_MN == 0) {
             tma_load_3d(sb, &tmB, &full_bar[s], k0, n0, b);
+          } else if (p.b_4d) {
+            tma_load_4d(sb, &tmB, &full_bar[s], 0, k0, n0 / 64, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -733,6 +738,32 @@ static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t 
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// M/N-major operand whose contiguous extent is a multiple of 64: map it as
+// (64, k, panel, batch) so that one box {64, BK, panels, 1} brings a whole stage tile in the
+// [panel][k][64] layout the MMA descriptors expect (one TMA instruction instead of one per
+// 64-wide panel).  A partial last tile reads panels past the extent as zeros (out-of-bounds
+// fill), exactly like the per-panel loads.
+static int make_tmap_mn4(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer,
+                         uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                         uint32_t panels) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  cuuint64_t dims[4] = {64, outer, inner / 64, batch};
+  cuuint64_t strides[3] = {ld_elems * 2, 128,
+                           (batch > 1 ? batch_stride_elems : ld_elems * outer) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(ceo::BK), panels, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 static int g_num_sms = 0;
 static int g_deterministic = 0;  // 1: no split-K (its atomics make the fp32 sum order vary)
 
@@ -785,19 +816,27 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   }
   CUtensorMap ta, tb;
   int rc;
+  const bool a4 = a_mn_major && fz.kind == 0 && (M & 63) == 0;
+  const bool b4 = b_mn_major && fz.kind == 0 && (N & 63) == 0;
   if (a_mn_major == 0)
     rc = make_tmap(&ta, A, K, M, batch, lda, batch_stride_a, BM);
+  else if (a4)
+    rc = make_tmap_mn4(&ta, A, M, K, batch, lda, batch_stride_a, BM / 64);
   else
     rc = make_tmap(&ta, A, M, K, batch, lda, batch_stride_a, BK);
   if (rc) return -3;
   if (b_mn_major == 0)
     rc = make_tmap(&tb, B, K, N, batch, ldb, batch_stride_b, BN);
+  else if (b4)
+    rc = make_tmap_mn4(&tb, B, N, K, batch, ldb, batch_stride_b, BN / 64);
   else
     rc = make_tmap(&tb, B, N, K, batch, ldb, batch_stride_b, BK);
   if (rc) return -4;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.a_4d = a4;
+  p.b_4d = b4;
   p.C = C;
   p.residual = residual;
   p.bias = bias;

@@ -72,15 +72,18 @@ class EflaLayer(nn.Module):
         w_qkv = _param((self.P * hd, self.D), std, device, dtype, gen).data
         self.w_o = _param((self.D, hd), std, device, dtype, gen)
         if self.per_token_beta:
-            # the beta logits ride in the same projection: rows [q | k | v | beta (H) | zero pad]
+            # the beta logits ride in the same projection: rows [q | k | v | beta (H) | zero pad];
+            # padded to a multiple of 64 rows so the weight-gradient GEMM can fetch the operand
+            # tile with one TMA request per stage
             w_beta = _param((self.H, self.D), std, device, dtype, gen).data
-            pad = (-self.H) % 8
+            pad = (-(self.P * hd + self.H)) % 64
             w_qkv = torch.cat([w_qkv, w_beta, torch.zeros(pad, self.D, device=device, dtype=dtype)])
             self.beta_param = None
         else:
             self.beta_param = nn.Parameter(torch.full((1,), float(e.initial_beta), device=device,
                                                       dtype=torch.float32),
                                            requires_grad=e.learned_beta)
+        self.qkv_pad_rows = w_qkv.shape[0] - self.P * hd - (self.H if self.per_token_beta else 0)
         self.w_qkv = nn.Parameter(w_qkv)
 
     def forward(self, x_norm, residual, state=None, resets=None):
@@ -315,6 +318,7 @@ class EflaLM(nn.Module):
         c = self.cfg
         mat = sum(p.numel() for n, p in self.named_parameters() if p.dim() == 2
                   and "embed_tokens" not in n)
+        mat -= sum(b.efla.qkv_pad_rows * c.hidden_dim for b in self.blocks)  # zero padding rows
         if self.lm_head is None:
             mat += self.embed_tokens.numel()
         efla = c.num_layers * c.num_heads * (4 * c.head_dim * c.head_dim + 8 * 64 * c.head_dim)

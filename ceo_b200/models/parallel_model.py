@@ -71,10 +71,12 @@ class ParallelBlock(nn.Module):
         self.w_o = nn.Parameter(w_o.chunk(tp_world, dim=1)[tp_rank].contiguous().to(dt))
         if self.per_token_beta:
             w_beta = _full((H, D), std, device, gen).chunk(tp_world, dim=0)[tp_rank]
-            pad = (-self.H_loc) % 8
+            pad = (-(w_loc.shape[0] + self.H_loc)) % 64
             w_loc = torch.cat([w_loc, w_beta, torch.zeros(pad, D, device=device)])
+            self.qkv_pad_rows = pad
             self.beta_param = None
         else:
+            self.qkv_pad_rows = 0
             self.beta_param = nn.Parameter(torch.full((1,), float(e.initial_beta), device=device),
                                            requires_grad=e.learned_beta)
             self.beta_param.replicated = True
@@ -181,6 +183,7 @@ class ParallelEflaLM(nn.Module):
         c = self.cfg
         mat = sum(p.numel() for n, p in self.named_parameters() if p.dim() == 2
                   and "embed_tokens" not in n and not getattr(p, "replicated", False))
+        mat -= sum(b.qkv_pad_rows * c.hidden_dim for b in self.blocks)  # zero padding rows
         mat *= self.tp_world
         mat += (self.embed_tokens if self.lm_head is None else self.lm_head).numel()
         efla = c.num_layers * c.num_heads * (4 * c.head_dim * c.head_dim + 8 * 64 * c.head_dim)
