@@ -58,15 +58,28 @@ constexpr int PANEL = CH * 128;  // bytes of a 64-row x 64-column swizzled panel
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
 }
+// Whole tiles come through "panel" maps (the matrix seen as (64, rows, cols / 64), see
+// common/tmap.h): one request per tile whatever D is.  x0 = first column, a multiple of 64.
 template <int D>
 __device__ __forceinline__ void tma_tok_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar,
                                              int x0, int tok0) {
-#pragma unroll
-  for (int pnl = 0; pnl < D / 64; ++pnl) tma_load_2d(dst + pnl * PANEL, tm, bar, x0 + pnl * 64, tok0);
+  tma_load_3d(dst, tm, bar, 0, tok0, x0 >> 6);
 }
 template <int D>
 __device__ __forceinline__ void tma_state_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar,
                                                int row0) {
+  tma_load_3d(dst, tm, bar, 0, row0, 0);
+}
+// The same tiles through plain 2-D maps, one request per 64-column panel.
+template <int D>
+__device__ __forceinline__ void tma_tok_tile_2d(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar,
+                                                int x0, int tok0) {
+#pragma unroll
+  for (int pnl = 0; pnl < D / 64; ++pnl) tma_load_2d(dst + pnl * PANEL, tm, bar, x0 + pnl * 64, tok0);
+}
+template <int D>
+__device__ __forceinline__ void tma_state_tile_2d(uint8_t* dst, const CUtensorMap* tm,
+                                                  uint64_t* bar, int row0) {
 #pragma unroll
   for (int pnl = 0; pnl < D / 64; ++pnl) tma_load_2d(dst + pnl * D * 128, tm, bar, pnl * 64, row0);
 }
@@ -321,11 +334,8 @@ efla_state_fwd_kernel(const __grid_constant__ CUtensorMap tm_k,
     auto load_wk = [&](int c) {
       const int st = c & 1, tok0 = b * T + c * CH;
       mbar_arrive_expect_tx(&sy->full[st], 2 * TILE);
-#pragma unroll
-      for (int pnl = 0; pnl < D / 64; ++pnl) {
-        tma_load_2d(Wb + st * TILE + pnl * PANEL, &tm_w, &sy->full[st], h * D + pnl * 64, tok0);
-        tma_load_2d(Kb + st * TILE + pnl * PANEL, &tm_k, &sy->full[st], h * D + pnl * 64, tok0);
-      }
+      tma_tok_tile<D>(Wb + st * TILE, &tm_w, &sy->full[st], h * D, tok0);
+      tma_tok_tile<D>(Kb + st * TILE, &tm_k, &sy->full[st], h * D, tok0);
     };
     auto load_u = [&](int c) {
       mbar_arrive_expect_tx(&sy->full_u, PANEL);
@@ -558,8 +568,8 @@ efla_out_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_arrive_expect_tx(&bars[1], 2 * 16384 + 2 * 32768);
 #pragma unroll
     for (int ci = 0; ci < 2; ++ci) {
-      tma_tok_tile<D>(Ups + ci * 16384, &tm_up, &bars[1], h * D, tok0 + ci * CH);
-      tma_state_tile<D>(Sb + ci * 32768, &tm_states, &bars[1], (bh * n + c0 + ci) * D);
+      tma_tok_tile_2d<D>(Ups + ci * 16384, &tm_up, &bars[1], h * D, tok0 + ci * CH);
+      tma_state_tile_2d<D>(Sb + ci * 32768, &tm_states, &bars[1], (bh * n + c0 + ci) * D);
     }
     // P = Q K^T for the pair
     if (!waitb(&bars[0])) ok = false;
@@ -805,12 +815,9 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
       uint8_t* st = smem + (i & 1) * STAGE;
       uint64_t* bar = &sy->full[i & 1];
       mbar_arrive_expect_tx(bar, STAGE);
-#pragma unroll
-      for (int pnl = 0; pnl < D / 64; ++pnl) {
-        tma_load_2d(st + pnl * PANEL, &tm_k, bar, h * D + pnl * 64, tok0);
-        tma_load_2d(st + TILE + pnl * PANEL, &tm_q, bar, h * D + pnl * 64, tok0);
-        tma_load_2d(st + 2 * TILE + pnl * PANEL, &tm_w, bar, h * D + pnl * 64, tok0);
-      }
+      tma_tok_tile<D>(st, &tm_k, bar, h * D, tok0);
+      tma_tok_tile<D>(st + TILE, &tm_q, bar, h * D, tok0);
+      tma_tok_tile<D>(st + 2 * TILE, &tm_w, bar, h * D, tok0);
       tma_load_2d(st + 3 * TILE, &tm_dloc, bar, h * D + v0, tok0);
       tma_load_2d(st + 3 * TILE + PANEL, &tm_dO, bar, h * D + v0, tok0);
     };
@@ -1304,21 +1311,31 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
     if (!t.p[i] || (reinterpret_cast<uintptr_t>(t.p[i]) & 15)) return -2;
     return encode_tmap_2d_bf16(tm, t.p[i], D, srows, D, D) ? -3 : 0;
   };
+  // panel maps: one request per whole 64 x D token tile / D x D state
+  auto tokp = [&](CUtensorMap* tm, int i, long long stride) {
+    if (!t.p[i] || (reinterpret_cast<uintptr_t>(t.p[i]) & 15) || (stride & 7)) return -2;
+    return encode_tmap_panels_bf16(tm, t.p[i], static_cast<uint64_t>(HD), tokens, stride, CH,
+                                   D / 64) ? -3 : 0;
+  };
+  auto stap = [&](CUtensorMap* tm, int i) {
+    if (!t.p[i] || (reinterpret_cast<uintptr_t>(t.p[i]) & 15)) return -2;
+    return encode_tmap_panels_bf16(tm, t.p[i], D, srows, D, D, D / 64) ? -3 : 0;
+  };
   const dim3 gpar(n, B * H);
   CUtensorMap m[8];
   int rc = 0;
 #define MAP(call) if ((rc = (call)) != 0) return rc
   switch (stage) {
     case 0:
-      MAP(tok(&m[0], I_K, t.stride[1]));
-      MAP(tok(&m[1], I_V, t.stride[2]));
+      MAP(tokp(&m[0], I_K, t.stride[1]));
+      MAP(tokp(&m[1], I_V, t.stride[2]));
       if (!t.p[I_XINV]) return -5;
       efla_wy_kernel<D><<<gpar, 128, smem_wy<D>(), st>>>(m[0], m[1], f32(I_ALPHA), b16(I_W),
                                                          b16(I_U), b16(I_XINV), T, H, status);
       break;
     case 1:
-      MAP(tok(&m[0], I_K, t.stride[1]));
-      MAP(tok(&m[1], I_W, HD));
+      MAP(tokp(&m[0], I_K, t.stride[1]));
+      MAP(tokp(&m[1], I_W, HD));
       MAP(tok(&m[2], I_U, HD));
       MAP(tok(&m[3], I_UP, HD));
       MAP(sta(&m[4], I_STATES));
@@ -1328,30 +1345,35 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
           static_cast<const unsigned char*>(t.p[I_RESETS]), T, H, status);
       break;
     case 2:
-      MAP(tok(&m[0], I_Q, t.stride[0]));
-      MAP(tok(&m[1], I_K, t.stride[1]));
-      MAP(tok(&m[2], I_UP, HD));
-      MAP(sta(&m[3], I_STATES));
-      if (g_out_tcgen05 && D == 128 && (n & 1) == 0)  // chunk pairs on the tcgen05 path
+      if (g_out_tcgen05 && D == 128 && (n & 1) == 0) {  // chunk pairs on the tcgen05 path
+        MAP(tok(&m[0], I_Q, t.stride[0]));
+        MAP(tok(&m[1], I_K, t.stride[1]));
+        MAP(tok(&m[2], I_UP, HD));
+        MAP(sta(&m[3], I_STATES));
         efla_out_tc_kernel<<<dim3(n / 2, B * H), OUT_TC_THREADS, OUT_TC_SMEM, st>>>(
             m[0], m[1], m[2], m[3], b16(I_O), T, H, status);
-      else
+      } else {
+        MAP(tokp(&m[0], I_Q, t.stride[0]));
+        MAP(tokp(&m[1], I_K, t.stride[1]));
+        MAP(tokp(&m[2], I_UP, HD));
+        MAP(stap(&m[3], I_STATES));
         efla_out_kernel<D><<<gpar, 256, smem_out<D>(), st>>>(m[0], m[1], m[2], m[3], b16(I_O), T,
                                                              H, status);
+      }
       break;
     case 3:
-      MAP(tok(&m[0], I_Q, t.stride[0]));
-      MAP(tok(&m[1], I_K, t.stride[1]));
-      MAP(tok(&m[2], I_UP, HD));
-      MAP(tok(&m[3], I_DO, HD));
-      MAP(sta(&m[4], I_STATES));
+      MAP(tokp(&m[0], I_Q, t.stride[0]));
+      MAP(tokp(&m[1], I_K, t.stride[1]));
+      MAP(tokp(&m[2], I_UP, HD));
+      MAP(tokp(&m[3], I_DO, HD));
+      MAP(stap(&m[4], I_STATES));
       efla_bwd_local_kernel<D><<<gpar, 256, smem_bwd_local<D>(), st>>>(
           m[0], m[1], m[2], m[3], m[4], b16(I_DQ), b16(I_DLOC), T, H, t.stride[3], status);
       break;
     case 4:
-      MAP(tok(&m[0], I_Q, t.stride[0]));
-      MAP(tok(&m[1], I_K, t.stride[1]));
-      MAP(tok(&m[2], I_W, HD));
+      MAP(tokp(&m[0], I_Q, t.stride[0]));
+      MAP(tokp(&m[1], I_K, t.stride[1]));
+      MAP(tokp(&m[2], I_W, HD));
       MAP(tok(&m[3], I_DO, HD));
       MAP(tok(&m[4], I_DLOC, HD));
       MAP(tok(&m[5], I_DUP, HD));
@@ -1361,13 +1383,13 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
           static_cast<const unsigned char*>(t.p[I_RESETS]), T, H, status);
       break;
     case 5:
-      MAP(tok(&m[0], I_Q, t.stride[0]));
-      MAP(tok(&m[1], I_K, t.stride[1]));
-      MAP(tok(&m[2], I_UP, HD));
-      MAP(tok(&m[3], I_DO, HD));
-      MAP(tok(&m[4], I_DUP, HD));
-      MAP(sta(&m[5], I_STATES));
-      MAP(sta(&m[6], I_DSTATES));
+      MAP(tokp(&m[0], I_Q, t.stride[0]));
+      MAP(tokp(&m[1], I_K, t.stride[1]));
+      MAP(tokp(&m[2], I_UP, HD));
+      MAP(tokp(&m[3], I_DO, HD));
+      MAP(tokp(&m[4], I_DUP, HD));
+      MAP(stap(&m[5], I_STATES));
+      MAP(stap(&m[6], I_DSTATES));
       if (!t.p[I_XINV] || (reinterpret_cast<uintptr_t>(t.p[I_XINV]) & 15)) return -2;
       MAP(encode_tmap_2d_bf16(&m[7], t.p[I_XINV], CH, static_cast<uint64_t>(B) * H * n * CH, CH, CH)
               ? -3 : 0);
