@@ -172,6 +172,36 @@ def main():
         par.close()
         if rank == 0:
             print(f"OK {what}", lp, ls)
+    elif what == "pipeline":
+        # two pipeline stages over NCCL point-to-point against the whole model on one GPU
+        from ceo_b200.models.model import EflaLM
+        from ceo_b200.parallel.pipeline import PipelineRunner, PipelineStage
+        cfg = small_cfg(1)
+        m = cfg.model
+        m.num_heads, m.head_dim, m.num_layers = 4, 128, 3
+        dev = torch.device("cuda", torch.cuda.current_device())
+        stage = PipelineStage(m, dev, rank, world, seed=0)
+        runner = PipelineRunner(stage)
+        data = SyntheticTokens(m.vocab_size, "zipf", 1.1, 0, 0)
+        batches = [tuple(t.to(dev) for t in data.batch(2, 256)) for _ in range(3)]
+        loss = float(runner.run(batches))
+        runner.sync_tied_grads()
+        full = EflaLM(m, dev, seed=0)
+        ref = sum(full(t, y) for t, y in batches) / len(batches)
+        ref.backward()
+        assert abs(loss - float(ref)) < 2e-2 * abs(float(ref)), (loss, float(ref))
+        rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
+        errs = []
+        for i, blk in enumerate(stage.blocks):
+            for (n1, p1), (n2, p2) in zip(blk.named_parameters(),
+                                          full.blocks[stage.lo + i].named_parameters()):
+                if p1.grad is not None and p2.grad is not None and p2.grad.abs().max() > 0:
+                    errs.append(rel(p1.grad, p2.grad))
+        assert errs and max(errs) < 5e-2, errs
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        if rank == 0:
+            print("OK pipeline", loss, float(ref), max(errs))
     else:
         raise SystemExit(f"unknown test {what}")
     Comm().barrier()

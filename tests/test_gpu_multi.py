@@ -59,3 +59,9 @@ def test_context_parallel_efla_matches_single_gpu():
 def test_parallel_model_matches_single_gpu(what):
     out = _run(what, 2)
     assert f"OK {what}" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pipeline_stages_match_whole_model():
+    out = _run("pipeline", 2)
+    assert "OK pipeline" in out

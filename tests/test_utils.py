@@ -264,3 +264,29 @@ def test_topology_from_fake_nvml_and_sysfs(tmp_path):
     assert [a.pci_bus for a in t.gpu_affinity] == [0, 1, 2]
     assert DeviceInfo(0, "B200", 10, 0, 148, 1).is_blackwell
     assert not DeviceInfo(0, "H100", 9, 0, 132, 1).is_blackwell
+
+
+def test_runtime_queries_without_a_gpu_and_tracing_noop():
+    import pytest
+    import torch
+    from ceo_b200.parallel.pipeline import stage_bounds
+    from ceo_b200.runtime import device
+    from ceo_b200.utils import errors, tracing
+    if not torch.cuda.is_available():
+        assert device.device_count() == 0
+        with pytest.raises(errors.NoGpuAvailable):
+            device.device_info(0)
+        with pytest.raises(errors.NoGpuAvailable):
+            device.DistributedRuntime.init_single_gpu()
+        assert device.peer_access_matrix(0) == []
+    # uneven layer split: the first stages take the remainder
+    assert [stage_bounds(10, 4, s) for s in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert [stage_bounds(2, 4, s) for s in range(4)] == [(0, 1), (1, 2), (2, 2), (2, 2)]
+    # ranges are no-ops when tracing is off or there is no GPU
+    tracing.set_enabled(True)
+    with tracing.trace_range("x"):
+        pass
+    tracing.set_enabled(False)
+    assert not tracing.enabled()
+    t = tracing.format_table({"busy_ms": 2.0, "span_ms": 2.5, "kernels": [("k", 3, 1.5), ("j", 1, 0.5)]})
+    assert "75.0%" in t and "k" in t
