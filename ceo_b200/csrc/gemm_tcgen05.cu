@@ -284,6 +284,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t adesc0 = A_MN ? umma_smem_desc(smem0, PANEL_BYTES, 1024)
+                                   : umma_smem_desc(smem0, 16, 1024);
+      const uint64_t bdesc0 = B_MN ? umma_smem_desc(smem0 + A_STAGE_BYTES, PANEL_BYTES, 1024)
+                                   : umma_smem_desc(smem0 + A_STAGE_BYTES, 16, 1024);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -306,16 +311,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t sb = sa + A_STAGE_BYTES;
+          // descriptors of the stage's first k-step; the next ones differ only in the start
+          // address field (16-byte units in the low 14 bits, which cannot carry: shared
+          // memory addresses stay below 256 KB)
+          const uint64_t ad0 = adesc0 + static_cast<uint64_t>(s) * (STAGE_BYTES >> 4);
+          const uint64_t bd0 = bdesc0 + static_cast<uint64_t>(s) * (STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t ad = A_MN ? umma_smem_desc(sa + k * 2048, PANEL_BYTES, 1024)
-                                     : umma_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t bd = B_MN ? umma_smem_desc(sb + k * 2048, PANEL_BYTES, 1024)
-                                     : umma_smem_desc(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16(d_tmem, ad0 + static_cast<uint64_t>(k) * ((A_MN ? 2048 : 32) >> 4),
+                     bd0 + static_cast<uint64_t>(k) * ((B_MN ? 2048 : 32) >> 4), idesc,
+                     (kb > kb0 || k != 0) ? 1u : 0u);
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
