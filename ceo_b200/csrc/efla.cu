@@ -1129,6 +1129,15 @@ __device__ __forceinline__ float efla_coeff(float beta, float lam) {
   return -expm1f(-beta * lam) / lam;
 }
 
+// D / 8 lanes share one (token, head) row, eight elements (one 16-byte access) each, so a
+// warp covers 32 / (D / 8) rows at a time.
+template <int LPR>
+__device__ __forceinline__ float group_reduce_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <int D>
 __global__ void __launch_bounds__(256)
 efla_prep_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
@@ -1136,37 +1145,38 @@ efla_prep_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                      bf16* __restrict__ kn, float* __restrict__ rq, float* __restrict__ rk,
                      float* __restrict__ alpha, long long rows, int H, long long qs, long long ks,
                      int normalize) {
-  constexpr int E = D / 32;
-  const int lane = threadIdx.x & 31;
+  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
   const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long id = wid; id < rows * H; id += nw) {
-    const long long tok = id / H;
-    const int h = static_cast<int>(id - tok * H);
-    float qv[E], kv[E];
+  const long long total = rows * H;
+  for (long long id0 = wid * RPW; id0 < total; id0 += nw * RPW) {
+    const long long id = id0 + rw;
+    const bool live = id < total;
+    const long long tok = live ? id / H : 0;
+    const int h = live ? static_cast<int>(id - tok * H) : 0;
+    float qv[8], kv[8];
+    unpack8(*reinterpret_cast<const uint4*>(q + tok * qs + h * D + sub * 8), qv);
+    unpack8(*reinterpret_cast<const uint4*>(k + tok * ks + h * D + sub * 8), kv);
     float sq = 0.f, sk = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; e += 2) {
-      const float2 a = __bfloat1622float2(
-          *reinterpret_cast<const bf162*>(q + tok * qs + h * D + lane * E + e));
-      const float2 b = __bfloat1622float2(
-          *reinterpret_cast<const bf162*>(k + tok * ks + h * D + lane * E + e));
-      qv[e] = a.x; qv[e + 1] = a.y; kv[e] = b.x; kv[e + 1] = b.y;
-      sq += a.x * a.x + a.y * a.y;
-      sk += b.x * b.x + b.y * b.y;
+    for (int e = 0; e < 8; ++e) {
+      sq += qv[e] * qv[e];
+      sk += kv[e] * kv[e];
     }
-    sq = warp_reduce_sum(sq);
-    sk = warp_reduce_sum(sk);
+    sq = group_reduce_sum<LPR>(sq);
+    sk = group_reduce_sum<LPR>(sk);
     const float iq = normalize ? rsqrtf(sq + 1e-6f) : 1.f;
     const float ik = normalize ? rsqrtf(sk + 1e-6f) : 1.f;
+    if (!live) continue;
 #pragma unroll
-    for (int e = 0; e < E; e += 2) {
-      *reinterpret_cast<bf162*>(qn + id * D + lane * E + e) =
-          __floats2bfloat162_rn(qv[e] * iq, qv[e + 1] * iq);
-      *reinterpret_cast<bf162*>(kn + id * D + lane * E + e) =
-          __floats2bfloat162_rn(kv[e] * ik, kv[e + 1] * ik);
+    for (int e = 0; e < 8; ++e) {
+      qv[e] *= iq;
+      kv[e] *= ik;
     }
-    if (lane == 0) {
+    *reinterpret_cast<uint4*>(qn + id * D + sub * 8) = pack8(qv);
+    *reinterpret_cast<uint4*>(kn + id * D + sub * 8) = pack8(kv);
+    if (sub == 0) {
       const float b = beta_scalar ? beta[0] : beta[id];
       rq[id] = iq;
       rk[id] = ik;
@@ -1186,31 +1196,34 @@ efla_prep_bwd_kernel(const bf16* __restrict__ dqn, const bf16* __restrict__ dkn,
                      const float* __restrict__ dalpha, bf16* __restrict__ dq,
                      bf16* __restrict__ dk, float* __restrict__ dbeta, long long rows, int H,
                      long long dqs, long long dks, int normalize) {
-  constexpr int E = D / 32;
-  const int lane = threadIdx.x & 31;
+  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
   const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long id = wid; id < rows * H; id += nw) {
-    const long long tok = id / H;
-    const int h = static_cast<int>(id - tok * H);
-    float qv[E], kv[E], gq[E], gk[E];
+  const long long total = rows * H;
+  for (long long id0 = wid * RPW; id0 < total; id0 += nw * RPW) {
+    const long long id = id0 + rw;
+    const bool live = id < total;
+    const long long idc = live ? id : 0;
+    const long long tok = idc / H;
+    const int h = static_cast<int>(idc - tok * H);
+    float qv[8], kv[8], gq[8], gk[8];
+    const long long o = idc * D + sub * 8;
+    unpack8(*reinterpret_cast<const uint4*>(qn + o), qv);
+    unpack8(*reinterpret_cast<const uint4*>(kn + o), kv);
+    unpack8(*reinterpret_cast<const uint4*>(dqn + o), gq);
+    unpack8(*reinterpret_cast<const uint4*>(dkn + o), gk);
     float dq_dot = 0.f, dk_dot = 0.f, sk = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; e += 2) {
-      const long long o = id * D + lane * E + e;
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(qn + o));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(kn + o));
-      const float2 ga = __bfloat1622float2(*reinterpret_cast<const bf162*>(dqn + o));
-      const float2 gb = __bfloat1622float2(*reinterpret_cast<const bf162*>(dkn + o));
-      qv[e] = a.x; qv[e + 1] = a.y; kv[e] = b.x; kv[e + 1] = b.y;
-      gq[e] = ga.x; gq[e + 1] = ga.y; gk[e] = gb.x; gk[e + 1] = gb.y;
-      dq_dot += a.x * ga.x + a.y * ga.y;
-      dk_dot += b.x * gb.x + b.y * gb.y;
-      sk += b.x * b.x + b.y * b.y;
+    for (int e = 0; e < 8; ++e) {
+      dq_dot += qv[e] * gq[e];
+      dk_dot += kv[e] * gk[e];
+      sk += kv[e] * kv[e];
     }
-    dq_dot = warp_reduce_sum(dq_dot);
-    dk_dot = warp_reduce_sum(dk_dot);
-    sk = warp_reduce_sum(sk);
+    dq_dot = group_reduce_sum<LPR>(dq_dot);
+    dk_dot = group_reduce_sum<LPR>(dk_dot);
+    sk = group_reduce_sum<LPR>(sk);
+    if (!live) continue;
     const float b = beta_scalar ? beta[0] : beta[id];
     const float da = dalpha[id];
     float kcoef = 0.f, db;
@@ -1226,25 +1239,20 @@ efla_prep_bwd_kernel(const bf16* __restrict__ dqn, const bf16* __restrict__ dkn,
       kcoef = 2.f * da * dcdl;
     }
     const float iq = rq[id], ik = rk[id];
+    float oq[8], ok[8];
 #pragma unroll
-    for (int e = 0; e < E; e += 2) {
-      float o0, o1, p0, p1;
+    for (int e = 0; e < 8; ++e) {
       if (normalize) {
-        o0 = iq * (gq[e] - qv[e] * dq_dot);
-        o1 = iq * (gq[e + 1] - qv[e + 1] * dq_dot);
-        p0 = ik * (gk[e] - kv[e] * dk_dot);
-        p1 = ik * (gk[e + 1] - kv[e + 1] * dk_dot);
+        oq[e] = iq * (gq[e] - qv[e] * dq_dot);
+        ok[e] = ik * (gk[e] - kv[e] * dk_dot);
       } else {
-        o0 = gq[e]; o1 = gq[e + 1];
-        p0 = gk[e] + kcoef * kv[e];
-        p1 = gk[e + 1] + kcoef * kv[e + 1];
+        oq[e] = gq[e];
+        ok[e] = gk[e] + kcoef * kv[e];
       }
-      *reinterpret_cast<bf162*>(dq + tok * dqs + h * D + lane * E + e) =
-          __floats2bfloat162_rn(o0, o1);
-      *reinterpret_cast<bf162*>(dk + tok * dks + h * D + lane * E + e) =
-          __floats2bfloat162_rn(p0, p1);
     }
-    if (lane == 0) dbeta[id] = db;
+    *reinterpret_cast<uint4*>(dq + tok * dqs + h * D + sub * 8) = pack8(oq);
+    *reinterpret_cast<uint4*>(dk + tok * dks + h * D + sub * 8) = pack8(ok);
+    if (sub == 0) dbeta[id] = db;
   }
 }
 
@@ -1468,8 +1476,12 @@ extern "C" int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta
                                  void* qn, void* kn, float* rq, float* rk, float* alpha,
                                  long long rows, int H, int D, long long q_stride,
                                  long long k_stride, int normalize, cudaStream_t stream) {
-  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || (q_stride & 1) || (k_stride & 1)) return -5;
-  const int grid = grid_for(rows * H, 8, 148 * 16);
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128)) return -5;
+  if (((q_stride | k_stride) & 7) ||
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+        reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn)) & 15))
+    return -2;  // rows move as 16-byte accesses
+  const int grid = grid_for(rows * H, 8 * (D == 64 ? 4 : 2), 148 * 16);
   if (D == 64)
     efla_prep_fwd_kernel<64><<<grid, 256, 0, stream>>>(
         static_cast<const bf16*>(q), static_cast<const bf16*>(k), beta, beta_scalar,
@@ -1488,8 +1500,13 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
                                  int beta_scalar, const float* dalpha, void* dq, void* dk,
                                  float* dbeta, long long rows, int H, int D, long long dq_stride,
                                  long long dk_stride, int normalize, cudaStream_t stream) {
-  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || (dq_stride & 1) || (dk_stride & 1)) return -5;
-  const int grid = grid_for(rows * H, 8, 148 * 16);
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128)) return -5;
+  if (((dq_stride | dk_stride) & 7) ||
+      ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+        reinterpret_cast<uintptr_t>(dqn) | reinterpret_cast<uintptr_t>(dkn) |
+        reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn)) & 15))
+    return -2;  // rows move as 16-byte accesses
+  const int grid = grid_for(rows * H, 8 * (D == 64 ? 4 : 2), 148 * 16);
   if (D == 64)
     efla_prep_bwd_kernel<64><<<grid, 256, 0, stream>>>(
         static_cast<const bf16*>(dqn), static_cast<const bf16*>(dkn), static_cast<const bf16*>(qn),
