@@ -921,10 +921,10 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_dup,
                       const __grid_constant__ CUtensorMap tm_states,
                       const __grid_constant__ CUtensorMap tm_dstates,
-                      const __grid_constant__ CUtensorMap tm_xinv, const bf16* __restrict__ v,
-                      const float* __restrict__ alpha, bf16* __restrict__ dk,
-                      bf16* __restrict__ dv, float* __restrict__ dalpha, int T, int H,
-                      long long vs, long long dks, long long dvs, int* status) {
+                      const __grid_constant__ CUtensorMap tm_xinv,
+                      const __grid_constant__ CUtensorMap tm_v, const float* __restrict__ alpha,
+                      bf16* __restrict__ dk, bf16* __restrict__ dv, float* __restrict__ dalpha,
+                      int T, int H, long long dks, long long dvs, int* status) {
   constexpr int NT = D / 16, TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -938,7 +938,8 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* Xs = dSb + STILE;   // X = (I + diag(a) G)^-1 as the forward pass saved it
   uint8_t* dGs = Xs + PANEL;
   uint8_t* dPs = dGs + PANEL;
-  float* Gs = reinterpret_cast<float*>(dPs + PANEL);
+  uint8_t* Vs = dPs + PANEL;   // V, for R = V - K S_in
+  float* Gs = reinterpret_cast<float*>(Vs + TILE);
   float* al = Gs + CH * GLD;
   float* dal = al + CH;
   uint64_t* bars = reinterpret_cast<uint64_t*>(dal + CH);
@@ -949,7 +950,7 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   // every tile is requested up front, in the order the steps below need them
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 3);
+    mbar_init(&bars[1], 4);
     mbar_init(&bars[2], 2);
     mbar_init(&bars[3], 1);
     mbar_init(&bars[4], 1);
@@ -990,6 +991,10 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_arrive_expect_tx(&bars[4], STILE);
       tma_state_tile<D>(dSb, &tm_dstates, &bars[4], srow);
       break;
+    case 16:
+      mbar_arrive_expect_tx(&bars[1], TILE);
+      tma_tok_tile<D>(Vs, &tm_v, &bars[1], h * D, tok0);
+      break;
     default:
       break;
   }
@@ -1006,7 +1011,7 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   const SwzTile Qt = swz_tile(Qs, CH), Kt = swz_tile(Ks, CH), Upt = swz_tile(Ups, CH),
                 dOt = swz_tile(dOs, CH), Zt = swz_tile(Zs, CH), St = swz_tile(Sb, D),
                 dSt = swz_tile(dSb, D), Xt = swz_tile(Xs, CH), dGt = swz_tile(dGs, CH),
-                dPt = swz_tile(dPs, CH);
+                dPt = swz_tile(dPs, CH), Vt = swz_tile(Vs, CH);
 
   // 1. G = K K^T, strictly lower part, fp32 (step 4 needs it for d(alpha))
   {
@@ -1042,8 +1047,7 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int hf = 0; hf < 2; ++hf) {
         const int row = 16 * r + g + hf * 8, col = c0 + nt * 8 + 2 * tg;
         const long long tok = static_cast<long long>(tok0) + row;
-        const float2 vv =
-            __bfloat1622float2(*reinterpret_cast<const bf162*>(v + tok * vs + h * D + col));
+        const float2 vv = lds_bf162(Vt.at(row, col));
         p[hf] += zacc[nt][2 * hf] * (vv.x - racc[nt][2 * hf]) +
                  zacc[nt][2 * hf + 1] * (vv.y - racc[nt][2 * hf + 1]);
         const float a = al[row];
@@ -1265,7 +1269,7 @@ template <int D> constexpr int smem_state_fwd() { return 4 * tile_bytes<D>() + 2
 template <int D> constexpr int smem_out() { return 3 * tile_bytes<D>() + stile_bytes<D>() + PANEL + BAR_BYTES + 1024; }
 template <int D> constexpr int smem_bwd_local() { return 4 * tile_bytes<D>() + stile_bytes<D>() + BAR_BYTES + 1024; }
 template <int D> constexpr int smem_state_bwd() { return 2 * (3 * tile_bytes<D>() + 2 * PANEL) + D * 128 + PANEL + static_cast<int>(sizeof(SerialSync)) + 1024; }
-template <int D> constexpr int smem_bwd_final() { return 5 * tile_bytes<D>() + 2 * stile_bytes<D>() + 3 * PANEL + CH * GLD * 4 + 2 * CH * 4 + BAR_BYTES + 1024; }
+template <int D> constexpr int smem_bwd_final() { return 6 * tile_bytes<D>() + 2 * stile_bytes<D>() + 3 * PANEL + CH * GLD * 4 + 2 * CH * 4 + BAR_BYTES + 1024; }
 
 template <typename Kern>
 static cudaError_t set_smem(Kern kern, int bytes) {
@@ -1330,7 +1334,7 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
     return encode_tmap_panels_bf16(tm, t.p[i], D, srows, D, D, D / 64) ? -3 : 0;
   };
   const dim3 gpar(n, B * H);
-  CUtensorMap m[8];
+  CUtensorMap m[9];
   int rc = 0;
 #define MAP(call) if ((rc = (call)) != 0) return rc
   switch (stage) {
@@ -1401,9 +1405,10 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
       if (!t.p[I_XINV] || (reinterpret_cast<uintptr_t>(t.p[I_XINV]) & 15)) return -2;
       MAP(encode_tmap_2d_bf16(&m[7], t.p[I_XINV], CH, static_cast<uint64_t>(B) * H * n * CH, CH, CH)
               ? -3 : 0);
+      MAP(tokp(&m[8], I_V, t.stride[2]));
       efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
-          m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], b16(I_V), f32(I_ALPHA), b16(I_DK), b16(I_DV),
-          f32(I_DALPHA), T, H, t.stride[2], t.stride[4], t.stride[5], status);
+          m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], f32(I_ALPHA), b16(I_DK), b16(I_DV),
+          f32(I_DALPHA), T, H, t.stride[4], t.stride[5], status);
       break;
     default:
       return -5;
