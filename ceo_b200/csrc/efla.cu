@@ -140,14 +140,25 @@ __device__ __forceinline__ void solve_blocked(const float* Gs, const float* __re
   if (threadIdx.x < CH) {
     const int blk = threadIdx.x >> 4, cl = threadIdx.x & 15, o = 16 * blk;
     const float* gblk = Gs + o * GLD + o;
-    float sum[16], x[16];
+    float sum[16], x[16], av[16], gcur[16], gnext[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+    for (int i = 0; i < 16; ++i) {
+      sum[i] = 0.f;
+      av[i] = al[o + i];
+      gcur[i] = i > 0 ? gblk[i * GLD] : 0.f;
+      gnext[i] = 0.f;
+    }
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-      x[j] = (j == cl) ? 1.f : (j < cl ? 0.f : -al[o + j] * sum[j]);
+      // column j + 1 of G is requested before column j is consumed: no load sits on the
+      // x_j -> sum -> x_{j+1} chain
 #pragma unroll
-      for (int i = j + 1; i < 16; ++i) sum[i] += gblk[i * GLD + j] * x[j];
+      for (int i = j + 2; i < 16; ++i) gnext[i] = gblk[i * GLD + j + 1];
+      x[j] = (j == cl) ? 1.f : (j < cl ? 0.f : -av[j] * sum[j]);
+#pragma unroll
+      for (int i = j + 1; i < 16; ++i) sum[i] += gcur[i] * x[j];
+#pragma unroll
+      for (int i = j + 2; i < 16; ++i) gcur[i] = gnext[i];
     }
     __syncwarp();  // all of G's block has been read before X replaces it (Xf may be Gs)
     float* xcol = Xf + o * GLD + o + cl;
@@ -208,8 +219,10 @@ efla_wy_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     mbar_arrive_expect_tx(&bars[1], TILE);
     tma_tok_tile<D>(Vs, &tm_v, &bars[1], h * D, tok0);
   }
-  if (threadIdx.x < CH) al[threadIdx.x] = alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h];
-  __syncthreads();
+  // alpha is requested now and parked in shared memory only when the solve needs it, so its
+  // global latency hides behind the K tile and the Gram product
+  const float my_al =
+      threadIdx.x < CH ? alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h] : 0.f;
   tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
@@ -226,16 +239,24 @@ efla_wy_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         Gs[row * GLD + col] = col < row ? acc[nt][e] : 0.f;
       }
   }
+  if (threadIdx.x < CH) al[threadIdx.x] = my_al;
   __syncthreads();
   solve_blocked<128>(Gs, al, Gs);
   // T = X diag(a) feeds the two products below; X itself (bf16) is kept for the backward pass
   bf16* xg = xinv + (static_cast<long long>(bh) * (T / CH) + blockIdx.x) * CH * CH;
-  for (int e = threadIdx.x; e < CH * CH / 2; e += 128) {
-    const int i = e >> 5, c = (e & 31) * 2;
-    const float x0 = c <= i ? Gs[i * GLD + c] : 0.f;
-    const float x1 = c + 1 <= i ? Gs[i * GLD + c + 1] : 0.f;
-    sts_bf162(Tt.at(i, c), x0 * al[c], x1 * al[c + 1]);
-    *reinterpret_cast<bf162*>(xg + i * CH + c) = __floats2bfloat162_rn(x0, x1);
+#pragma unroll
+  for (int it = 0; it < CH * CH / 4 / 128; ++it) {
+    const int e = threadIdx.x + it * 128, i = e >> 4, c = (e & 15) * 4;
+    const float4 xr = *reinterpret_cast<const float4*>(Gs + i * GLD + c);
+    const float4 ar = *reinterpret_cast<const float4*>(al + c);
+    const float x0 = c <= i ? xr.x : 0.f, x1 = c + 1 <= i ? xr.y : 0.f;
+    const float x2 = c + 2 <= i ? xr.z : 0.f, x3 = c + 3 <= i ? xr.w : 0.f;
+    sts_bf162(Tt.at(i, c), x0 * ar.x, x1 * ar.y);
+    sts_bf162(Tt.at(i, c + 2), x2 * ar.z, x3 * ar.w);
+    uint2 xo;
+    *reinterpret_cast<bf162*>(&xo.x) = __floats2bfloat162_rn(x0, x1);
+    *reinterpret_cast<bf162*>(&xo.y) = __floats2bfloat162_rn(x2, x3);
+    *reinterpret_cast<uint2*>(xg + i * CH + c) = xo;
   }
   __syncthreads();
   const long long orow = (static_cast<long long>(tok0) + 16 * warp) * H + h;  // row of (B*T*H, D)
@@ -998,11 +1019,9 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
     default:
       break;
   }
-  if (threadIdx.x < CH) {
-    al[threadIdx.x] = alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h];
-    dal[threadIdx.x] = 0.f;
-  }
-  __syncthreads();
+  // alpha is requested now, parked in shared memory after the Gram product (first use: step 3)
+  const float my_al =
+      threadIdx.x < CH ? alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h] : 0.f;
   tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
@@ -1025,6 +1044,10 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int row = 16 * r + g + (e >> 1) * 8, col = 32 * half + nt * 8 + 2 * tg + (e & 1);
         Gs[row * GLD + col] = col < row ? acc[nt][e] : 0.f;
       }
+  }
+  if (threadIdx.x < CH) {
+    al[threadIdx.x] = my_al;
+    dal[threadIdx.x] = 0.f;
   }
   __syncthreads();
   tile_wait(&bars[1], status);
