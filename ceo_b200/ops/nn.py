@@ -322,7 +322,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
 
 
 def linear_cross_entropy(x, weight, targets, label_smoothing: float = 0.0,
-                         ignore_index: int = -100, chunk_rows: int = 8192):
+                         ignore_index: int = -100, chunk_rows: int = 16384):
     """Mean token cross-entropy of the LM head ``x @ weight.T`` without materialising the
     full logits.  With ``weight.main_grad`` set, dW is accumulated there during the forward
     pass assuming the loss is back-propagated with gradient 1 (the trainer folds its
