@@ -49,6 +49,11 @@ struct GemmParams {
   int out_f32;     // 1: C is fp32, 0: C is bf16
   int accumulate;  // C = alpha*acc + C
   float alpha;
+  // 8-bit float operands (K-major only): element formats (0 e4m3, 1 e5m2) and the device-side
+  // quantisation scales; the epilogue multiplies by alpha / (scale_a * scale_b)
+  int fp8_a, fp8_b;
+  const float* scale_a;
+  const float* scale_b;
   int num_m, num_n;
   int* status;
   // ---- collectives fused into the kernel (all zero for a plain GEMM) --------------------
@@ -98,7 +103,9 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int r, int& m_b
   n_blk = (rem / gsz + p.n_rot) % p.num_n;
 }
 
-template <int A_MN, int B_MN>
+// FP8 = 1: both operands are K-major 8-bit floats; a stage row is still 128 bytes, i.e. 128
+// elements of K, and one MMA covers 32 of them.
+template <int A_MN, int B_MN, int FP8 = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -140,7 +147,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int tiles_per_batch = p.num_m * p.num_n;
   const int total_tiles = tiles_per_batch * p.batch;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;  // elements of K per stage
+  const int num_kb = (p.K + BKE - 1) / BKE;
   // the first ag_ctas CTAs only copy (all-gather); the others walk the output tiles
   const bool copy_cta = static_cast<int>(blockIdx.x) < p.ag_ctas;
   const int tile_step = static_cast<int>(gridDim.x) - p.ag_ctas;
@@ -185,7 +193,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           if (A_MN == 0) {
             tma_load_3d(sa, &tmA, &full_bar[s], k0, m0, b);
           } else if (p.a_4d) {
@@ -283,7 +291,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? umma_idesc_f8(BM, BN, p.fp8_a, p.fp8_b)
+                                 : umma_idesc_bf16(BM, BN, A_MN, B_MN);
       const uint32_t smem0 = smem_u32(smem);
       const uint64_t adesc0 = A_MN ? umma_smem_desc(smem0, PANEL_BYTES, 1024)
                                    : umma_smem_desc(smem0, 16, 1024);
@@ -317,10 +326,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint64_t ad0 = adesc0 + static_cast<uint64_t>(s) * (STAGE_BYTES >> 4);
           const uint64_t bd0 = bdesc0 + static_cast<uint64_t>(s) * (STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16(d_tmem, ad0 + static_cast<uint64_t>(k) * ((A_MN ? 2048 : 32) >> 4),
-                     bd0 + static_cast<uint64_t>(k) * ((B_MN ? 2048 : 32) >> 4), idesc,
-                     (kb > kb0 || k != 0) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = ad0 + static_cast<uint64_t>(k) * ((A_MN ? 2048 : 32) >> 4);
+            const uint64_t bd = bd0 + static_cast<uint64_t>(k) * ((B_MN ? 2048 : 32) >> 4);
+            const uint32_t accf = (kb > kb0 || k != 0) ? 1u : 0u;
+            if (FP8) umma_f8(d_tmem, ad, bd, idesc, accf);
+            else umma_f16(d_tmem, ad, bd, idesc, accf);
+          }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -330,6 +342,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   } else {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const float alpha = (FP8 && p.scale_a) ? p.alpha / (__ldg(p.scale_a) * __ldg(p.scale_b))
+                                           : p.alpha;
     int it = 0;
     bool ok = true;
     for (int t = first_tile; t < total_units && ok; t += tile_step, ++it) {
@@ -383,8 +397,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                oh[j] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * j]) * p.alpha,
-                                              __uint_as_float(v[q4 * 8 + 2 * j + 1]) * p.alpha);
+                oh[j] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * j]) * alpha,
+                                              __uint_as_float(v[q4 * 8 + 2 * j + 1]) * alpha);
               *reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16) = o;
             }
           }
@@ -438,7 +452,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               uint4* slot = reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16);
               float f[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q4 * 8 + j]) * p.alpha;
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q4 * 8 + j]) * alpha;
               if (rbase) {
                 const uint4 u = *slot;
                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -482,9 +496,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int q = 0; q < 8; ++q)
             *reinterpret_cast<float4*>(sb + lane * EPI_ROW_BYTES + q * 16) =
-                make_float4(__uint_as_float(v[4 * q]) * p.alpha, __uint_as_float(v[4 * q + 1]) * p.alpha,
-                            __uint_as_float(v[4 * q + 2]) * p.alpha,
-                            __uint_as_float(v[4 * q + 3]) * p.alpha);
+                make_float4(__uint_as_float(v[4 * q]) * alpha, __uint_as_float(v[4 * q + 1]) * alpha,
+                            __uint_as_float(v[4 * q + 2]) * alpha,
+                            __uint_as_float(v[4 * q + 3]) * alpha);
           __syncwarp();
           const int ncol = n0 + c * 32 + (lane & 7) * 4;
 #pragma unroll
@@ -513,7 +527,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!row_ok || n >= p.N) continue;
         float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * alpha;
         const bool full = (n + 32 <= p.N);
         if (p.bias) {
 #pragma unroll
@@ -713,10 +727,11 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// bf16 tensor map over (batch, outer, inner) with a {64, box_outer, 1} box and 128B swizzle.
+// Tensor map over (batch, outer, inner) with a box of 128 bytes x box_outer rows and 128B
+// swizzle; elements are bf16 (esize 2) or 8-bit floats moved as bytes (esize 1).
 static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer,
                      uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
-                     uint32_t box_outer) {
+                     uint32_t box_outer, uint32_t esize = 2) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   // The driver entry point needs a current context; a thread that has made no runtime
@@ -727,19 +742,21 @@ static int make_tmap(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t 
     ctx_bound = true;
   }
   cuuint64_t dims[3] = {inner, outer, batch};
-  cuuint64_t strides[2] = {ld_elems * 2, (batch > 1 ? batch_stride_elems : ld_elems * outer) * 2};
-  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint64_t strides[2] = {ld_elems * esize,
+                           (batch > 1 ? batch_stride_elems : ld_elems * outer) * esize};
+  cuuint32_t box[3] = {128 / esize, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+  CUresult r = fn(tm, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                  3, const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     fprintf(stderr,
             "ceo: cuTensorMapEncodeTiled failed (%d): ptr=%p dims={%llu,%llu,%llu} strides={%llu,%llu} "
-            "box={64,%u,1}\n",
+            "box={%u,%u,1}\n",
             static_cast<int>(r), ptr, (unsigned long long)dims[0], (unsigned long long)dims[1],
             (unsigned long long)dims[2], (unsigned long long)strides[0],
-            (unsigned long long)strides[1], box_outer);
+            (unsigned long long)strides[1], box[0], box_outer);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
@@ -772,21 +789,29 @@ static int make_tmap_mn4(CUtensorMap* tm, const void* ptr, uint64_t inner, uint6
 static int g_num_sms = 0;
 static int g_deterministic = 0;  // 1: no split-K (its atomics make the fp32 sum order vary)
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int FP8 = 0>
 static cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                           int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<A_MN, B_MN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<A_MN, B_MN, FP8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  gemm_bf16_tcgen05_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  gemm_bf16_tcgen05_kernel<A_MN, B_MN, FP8><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }
 
 }  // namespace ceo
+
+// 8-bit float operands of a GEMM launch (see GemmParams).
+struct Fp8Desc {
+  int on = 0;
+  int kind_a = 0, kind_b = 0;  // 0 e4m3, 1 e5m2
+  const float* scale_a = nullptr;
+  const float* scale_b = nullptr;
+};
 
 // Host-side description of the collective fused into a GEMM launch (see GemmParams).
 struct FusedDesc {
@@ -807,12 +832,17 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
                     long long batch_stride_a, long long batch_stride_b, long long batch_stride_c,
                     int out_f32, int accumulate, float alpha, const float* bias,
                     const void* residual, long long ldr, long long batch_stride_r, int* status,
-                    int max_ctas, const FusedDesc& fz, cudaStream_t stream, int split_k_mode = 1) {
+                    int max_ctas, const FusedDesc& fz, cudaStream_t stream, int split_k_mode = 1,
+                    const Fp8Desc& f8 = Fp8Desc()) {
   using namespace ceo;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (f8.on && (a_mn_major || b_mn_major || fz.kind != 0)) return -5;
+  const uint32_t esize = f8.on ? 1 : 2;
+  const long long amask = 16 / esize - 1;
   // TMA needs 16-byte aligned bases and row strides
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
-      (lda & 7) || (ldb & 7) || (batch > 1 && ((batch_stride_a & 7) || (batch_stride_b & 7))))
+      (lda & amask) || (ldb & amask) ||
+      (batch > 1 && ((batch_stride_a & amask) || (batch_stride_b & amask))))
     return -2;
   if (g_num_sms == 0) {
     int dev = 0;
@@ -824,14 +854,14 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   const bool a4 = a_mn_major && fz.kind == 0 && (M & 63) == 0;
   const bool b4 = b_mn_major && fz.kind == 0 && (N & 63) == 0;
   if (a_mn_major == 0)
-    rc = make_tmap(&ta, A, K, M, batch, lda, batch_stride_a, BM);
+    rc = make_tmap(&ta, A, K, M, batch, lda, batch_stride_a, BM, esize);
   else if (a4)
     rc = make_tmap_mn4(&ta, A, M, K, batch, lda, batch_stride_a, BM / 64);
   else
     rc = make_tmap(&ta, A, M, K, batch, lda, batch_stride_a, BK);
   if (rc) return -3;
   if (b_mn_major == 0)
-    rc = make_tmap(&tb, B, K, N, batch, ldb, batch_stride_b, BN);
+    rc = make_tmap(&tb, B, K, N, batch, ldb, batch_stride_b, BN, esize);
   else if (b4)
     rc = make_tmap_mn4(&tb, B, N, K, batch, ldb, batch_stride_b, BN / 64);
   else
@@ -853,6 +883,10 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   p.out_f32 = out_f32;
   p.accumulate = accumulate;
   p.alpha = alpha;
+  p.fp8_a = f8.kind_a;
+  p.fp8_b = f8.kind_b;
+  p.scale_a = f8.scale_a;
+  p.scale_b = f8.scale_b;
   p.num_m = (M + BM - 1) / BM;
   p.num_n = (N + BN - 1) / BN;
   p.status = status;
@@ -908,7 +942,7 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
   p.split_k = 1;
   if (fz.kind == 0 && out_f32 && accumulate && !bias && !residual && split_k_mode != 0 &&
-      !ceo::g_deterministic) {
+      !f8.on && !ceo::g_deterministic) {
     // few tiles with a long K (weight gradients): pick the split that fills whole waves best
     const int num_kb = (K + BK - 1) / BK;
     // every extra slice re-sends the whole fp32 C through L2 atomics, so a split has to buy a
@@ -924,7 +958,8 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   total *= p.split_k;
   int grid = static_cast<int>(total + p.ag_ctas < cap ? total + p.ag_ctas : cap);
   cudaError_t e;
-  if (a_mn_major == 0 && b_mn_major == 0) e = launch<0, 0>(ta, tb, p, grid, stream);
+  if (f8.on) e = launch<0, 0, 1>(ta, tb, p, grid, stream);
+  else if (a_mn_major == 0 && b_mn_major == 0) e = launch<0, 0>(ta, tb, p, grid, stream);
   else if (a_mn_major == 0) e = launch<0, 1>(ta, tb, p, grid, stream);
   else if (b_mn_major == 0) e = launch<1, 0>(ta, tb, p, grid, stream);
   else e = launch<1, 1>(ta, tb, p, grid, stream);
@@ -942,6 +977,27 @@ extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, batch, batch_stride_a,
                   batch_stride_b, batch_stride_c, out_f32, accumulate, alpha, bias, residual, ldr,
                   batch_stride_r, status, max_ctas, fz, stream);
+}
+
+// C[M,N] = alpha / (scale_a * scale_b) * A[M,K] @ B[N,K]^T (+ bias) (+ residual) with 8-bit
+// float operands (kind 0 = e4m3, 1 = e5m2), both K-major, strides in elements (= bytes) and
+// multiples of 16.  scale_a / scale_b are the device-side scales the operands were quantised
+// with (q = x * scale); both null means no rescaling.  C is bf16 or fp32.
+extern "C" int ceo_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int kind_a, int kind_b,
+                            int out_f32, int accumulate, float alpha, const float* scale_a,
+                            const float* scale_b, const float* bias, const void* residual,
+                            long long ldr, int* status, cudaStream_t stream) {
+  if (kind_a < 0 || kind_a > 1 || kind_b < 0 || kind_b > 1 || (!scale_a != !scale_b)) return -5;
+  FusedDesc fz;
+  Fp8Desc f8;
+  f8.on = 1;
+  f8.kind_a = kind_a;
+  f8.kind_b = kind_b;
+  f8.scale_a = scale_a;
+  f8.scale_b = scale_b;
+  return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, 1, 0, 0, 0, out_f32, accumulate, alpha,
+                  bias, residual, ldr, 0, status, 0, fz, stream, 0, f8);
 }
 
 // All-gather fused into the GEMM that consumes the gathered operand.  `gathered` is the table

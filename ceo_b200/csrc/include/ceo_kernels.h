@@ -190,6 +190,15 @@ int ceo_transpose16(const void* src, void* dst, int rows, int cols, long long ld
                     cudaStream_t stream);
 int ceo_memset32(void* x, long long n, unsigned int value, cudaStream_t stream);
 
+/* C = alpha / (scale_a * scale_b) * A[M,K] @ B[N,K]^T (+ bias) (+ residual): 8-bit float
+ * operands (kind 0 e4m3, 1 e5m2), both K-major, strides multiples of 16; scale_a / scale_b
+ * are the device-side quantisation scales (both null: no rescaling). */
+int ceo_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int kind_a, int kind_b, int out_f32,
+                 int accumulate, float alpha, const float* scale_a, const float* scale_b,
+                 const float* bias, const void* residual, long long ldr, int* status,
+                 cudaStream_t stream);
+
 /* ---- peer-memory collectives (NVLink), fused with their compute --------------------------
  * Buffers are plain cudaMalloc allocations mapped into every rank through CUDA IPC; the
  * `void* const*` arguments are host arrays of `world` device pointers indexed by rank (this

@@ -70,12 +70,32 @@ fp8_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, long long 
                  const float* __restrict__ scale, float* amax_out, int kind) {
   __shared__ float red[33];
   const float s = *scale;
+  const __nv_fp8_interpretation_t fmt = kind == 0 ? __NV_E4M3 : __NV_E5M2;
   float am = 0.f;
-  CEO_GRID_STRIDE(i, n) {
+  // 8 elements per thread and step (16-byte load, 8-byte store) when the pointers allow it
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(q) & 7)) == 0;
+  const long long n8 = vec ? n >> 3 : 0;
+  CEO_GRID_STRIDE(i, n8) {
+    const uint4 in = __ldg(reinterpret_cast<const uint4*>(x) + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
+    uint2 o;
+    uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 v = __bfloat1622float2(h[j]);
+      am = fmaxf(am, fmaxf(fabsf(v.x), fabsf(v.y)));
+      const __nv_fp8x2_storage_t pr =
+          __nv_cvt_float2_to_fp8x2(make_float2(v.x * s, v.y * s), __NV_SATFINITE, fmt);
+      ob[2 * j] = static_cast<uint8_t>(pr & 0xff);
+      ob[2 * j + 1] = static_cast<uint8_t>(pr >> 8);
+    }
+    reinterpret_cast<uint2*>(q)[i] = o;
+  }
+  for (long long i = (n8 << 3) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float v = __bfloat162float(x[i]);
     am = fmaxf(am, fabsf(v));
-    q[i] = static_cast<uint8_t>(
-        __nv_cvt_float_to_fp8(v * s, __NV_SATFINITE, kind == 0 ? __NV_E4M3 : __NV_E5M2));
+    q[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v * s, __NV_SATFINITE, fmt));
   }
   am = block_reduce_max(am, red);
   if (threadIdx.x == 0 && amax_out) atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(am));

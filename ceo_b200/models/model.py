@@ -24,6 +24,7 @@ import torch.nn as nn
 
 from ..ops import efla as efla_ops
 from ..ops import nn as K
+from ..ops.fp8 import Fp8Recipe, fp8_linear
 from ..ops.matmul import linear
 from ..utils.config import ModelConfig
 from .prism import PrismLayer
@@ -36,6 +37,15 @@ def _param(shape, std, device, dtype, gen):
     else:
         t.normal_(0.0, std, generator=gen)
     return nn.Parameter(t.to(dtype))
+
+
+def _lin(mod, name, x, w, residual=None):
+    """The module's Linear ``name``: on e4m3 operands when FP8 training is enabled for it
+    (``EflaLM.enable_fp8``), in bf16 otherwise."""
+    st = mod.fp8
+    if st is None:
+        return linear(x, w, residual)
+    return fp8_linear(x, w, st[name], residual)
 
 
 class Norm(nn.Module):
@@ -85,12 +95,13 @@ class EflaLayer(nn.Module):
                                            requires_grad=e.learned_beta)
         self.qkv_pad_rows = w_qkv.shape[0] - self.P * hd - (self.H if self.per_token_beta else 0)
         self.w_qkv = nn.Parameter(w_qkv)
+        self.fp8 = None
 
     def forward(self, x_norm, residual, state=None, resets=None):
         B, T, _ = x_norm.shape
         if (-T) % efla_ops.CHUNK and x_norm.is_cuda:
             raise ValueError(f"sequence length {T} must be a multiple of {efla_ops.CHUNK} on GPU")
-        proj = linear(x_norm, self.w_qkv)
+        proj = _lin(self, "qkv", x_norm, self.w_qkv)
         if self.per_token_beta:
             o, s_final = efla_ops.efla_proj(proj, self.P, self.H, self.d, self.normalize, state,
                                             resets)
@@ -129,11 +140,12 @@ class MLP(nn.Module):
         n_up = 2 * F if self.act == "swiglu" else F
         self.w_up = _param((n_up, D), std, device, dtype, gen)  # [gate | up] rows when swiglu
         self.w_down = _param((D, F), std, device, dtype, gen)
+        self.fp8 = None
 
     def forward(self, x_norm, residual):
-        u = linear(x_norm, self.w_up)
+        u = _lin(self, "up", x_norm, self.w_up)
         a = K.swiglu(u) if self.act == "swiglu" else K.activation(u, self.act)
-        return linear(a, self.w_down, residual)
+        return _lin(self, "down", a, self.w_down, residual)
 
 
 class Block(nn.Module):
@@ -149,10 +161,10 @@ class Block(nn.Module):
         n1, h = self.ln1(h, skip=True)
         o, s_final = self.efla(n1, h, state, resets)
         if self.prism is not None:
-            a = linear(o, self.efla.w_o)
+            a = _lin(self.efla, "o", o, self.efla.w_o)
             h = h + self.prism(n1, a)
         else:
-            h = linear(o, self.efla.w_o, h)
+            h = _lin(self.efla, "o", o, self.efla.w_o, h)
         n2, h = self.ln2(h, skip=True)
         h = self.mlp(n2, h)
         return h, s_final
@@ -183,6 +195,21 @@ class EflaLM(nn.Module):
         self.final_norm = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
         self.lm_head = None if cfg.tie_embeddings else \
             _param((cfg.vocab_size, cfg.hidden_dim), init_std, device, dtype, gen)
+
+        self.fp8_recipe = None
+
+    def enable_fp8(self, history: int = 16, margin: int = 0) -> Fp8Recipe:
+        """Switches the four projections of every block (qkv, out, up / gate-up, down) to the
+        FP8 forward product with per-tensor delayed scaling; the embedding, the norms, EFLA
+        itself and the LM head stay in bf16.  The caller invokes ``recipe.step()`` after every
+        optimizer step."""
+        rec = Fp8Recipe(history, margin)
+        dev = self.embed_tokens.device
+        for blk in self.blocks:
+            blk.efla.fp8 = {"qkv": rec.new_state(dev), "o": rec.new_state(dev)}
+            blk.mlp.fp8 = {"up": rec.new_state(dev), "down": rec.new_state(dev)}
+        self.fp8_recipe = rec
+        return rec
 
     # ------------------------------------------------------------------ forward paths
     def head_weight(self):

@@ -33,6 +33,8 @@ class TrainEngine:
             from ..ops import _lib
             _lib.lib().ceo_set_deterministic(int(cfg.runtime.deterministic))
         self.model = EflaLM(cfg.model, self.device, dtype=dtype, seed=seed)
+        # training.fp8_training (src/util/config.zig:420): forward projections on e4m3 operands
+        self.fp8 = self.model.enable_fp8() if cfg.training.fp8_training else None
         self.flat = FlatParams(self.model, self.world, self.rank,
                                alloc=getattr(comm, "alloc", None))
         self.optimizer = build_optimizer(self.flat, cfg.training, comm)
@@ -82,6 +84,8 @@ class TrainEngine:
         # mean over micro-batches and data-parallel ranks (the collectives sum)
         with trace_range("optimizer"):
             gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.world))
+        if self.fp8 is not None:
+            self.fp8.step()
         self.scheduler.step()
         self.step_count += 1
         mean = total / n

@@ -104,6 +104,18 @@ def main(argv=None):
             time_ms(lambda: G.gemm(dy, xin, a_mn=True, b_mn=True, out=mg, accumulate=True)),
             fl_, 0, tb)
 
+    if want("fp8"):
+        # forward projections on e4m3 operands; flops / time is compared with the bf16 peak
+        from ..ops import fp8 as F8
+        for name, n_out, k_in in (("qkv", 3 * D, D), ("gate_up", 2 * Fh, D), ("down", D, Fh)):
+            xin = torch.randn(M, k_in, device=dev).bfloat16()
+            w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
+            mx, mw = F8.Fp8Meta(dev), F8.Fp8Meta(dev)
+            xq, wq = F8.quantize(xin, mx), F8.quantize(w, mw)
+            rec(f"fp8_quantize {M}x{k_in}", time_ms(lambda: F8.quantize(xin, mx)), 0,
+                3.0 * M * k_in)
+            rec(f"gemm_fp8_fwd_{name} {M}x{n_out}x{k_in}",
+                time_ms(lambda: F8.gemm_fp8(xq, wq, mx, mw)), 2.0 * M * n_out * k_in)
     if want("norm"):
         w = torch.ones(D, device=dev).bfloat16().requires_grad_()
         xr = x.clone().requires_grad_()
