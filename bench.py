@@ -107,6 +107,9 @@ def main(argv=None):
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--fp8", action="store_true",
+                    help="side measurement, never the headline: forward projections on e4m3 "
+                         "operands (training.fp8_training); reported with dtype bf16+fp8-forward")
     ap.add_argument("--tp", type=int, default=0,
                     help="tensor-parallel size (0: 1 for the default config, else the config's)")
     ap.add_argument("--cp", type=int, default=0, help="context-parallel size (0: the config's)")
@@ -155,6 +158,7 @@ def main(argv=None):
     gbs = a.global_batch or cfg.training.global_batch_size
     mbs = a.micro_batch or cfg.training.micro_batch_size
     cfg.training.micro_batch_size = mbs
+    cfg.training.fp8_training = bool(a.fp8)
     if world % (tp * cp) or gbs % (mbs * dp):
         raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x dp {dp}")
     n_micro = gbs // (mbs * dp)
@@ -226,7 +230,8 @@ def main(argv=None):
             "metric": "train tokens/sec (box, device-timed, max over ranks) " + cfg.model.name,
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16+fp8-forward" if a.fp8 else "bf16",
             "data": "synthetic (seeded Zipf(1.1) tokens, N(0,0.02) random-init weights)",
             "config": {"model": cfg.model.name, "global_batch": gbs, "seq_len": seq,
                        "tokens_per_step": tokens_per_step, "micro_batch": mbs,
