@@ -10,9 +10,12 @@ Recipe here: activations and weights are quantised to e4m3 with one scale per te
 ``q = sat(x * scale)``, where the scale comes from the largest magnitude seen over the last 16
 steps (``Fp8Meta``).  ``y = (q_x q_w^T) / (scale_x scale_w)`` is formed by the GEMM epilogue,
 which reads both scales from device memory, so no step of the recipe synchronises with the
-host.  The data- and weight-gradient products stay in bf16 (they read the saved bf16
-activation and the bf16 weight), which keeps the gradients those of the bf16 model evaluated
-at an fp8-perturbed forward.  Quantised weights are cached for the whole optimizer step.
+host.  By default the data- and weight-gradient products stay in bf16 (they read the saved
+bf16 activation and the bf16 weight), which keeps the gradients those of the bf16 model
+evaluated at an fp8-perturbed forward.  With ``Fp8Recipe(dgrad=True)`` the data gradient
+``dx = dy W`` also runs on 8-bit operands: dy in e5m2 (its own delayed scale) against an e4m3
+copy of ``W^T``, so that both operands are K-major.  Quantised weights (and their transposes)
+are cached for the whole optimizer step.
 
 Without a GPU the same arithmetic runs through ``torch.float8_e4m3fn`` casts in fp32.
 """
@@ -22,6 +25,7 @@ import torch
 
 from . import _lib
 from .matmul import _as2d, gemm
+from .tensor_ops import transpose2d
 
 E4M3, E5M2 = 0, 1
 _FMAX = {E4M3: 448.0, E5M2: 57344.0}
@@ -142,8 +146,11 @@ class Fp8LinearState:
     def __init__(self, device, recipe: "Fp8Recipe"):
         self.x_meta = Fp8Meta(device, E4M3, recipe.history, recipe.margin)
         self.w_meta = Fp8Meta(device, E4M3, recipe.history, recipe.margin)
+        self.g_meta = Fp8Meta(device, E5M2, recipe.history, recipe.margin)
         self.wq = None
         self.wq_step = -1
+        self.wtq = None
+        self.wtq_step = -1
         self.recipe = recipe
 
     def weight_q(self, weight: torch.Tensor) -> torch.Tensor:
@@ -152,13 +159,21 @@ class Fp8LinearState:
             self.wq_step = self.recipe.step_id
         return self.wq
 
+    def weight_t_q(self, weight: torch.Tensor) -> torch.Tensor:
+        """e4m3 codes of ``weight^T`` (in, out), on the scale of ``weight_q``."""
+        if self.wtq is None or self.wtq_step != self.recipe.step_id:
+            self.weight_q(weight)  # makes sure the weight's scale is calibrated
+            self.wtq = _quantize_raw(transpose2d(weight.detach()), self.w_meta)
+            self.wtq_step = self.recipe.step_id
+        return self.wtq
+
 
 class Fp8Recipe:
     """Owner of every ``Fp8LinearState`` of a model; ``step()`` is called once per optimizer
     step, after the parameters changed."""
 
-    def __init__(self, history: int = 16, margin: int = 0):
-        self.history, self.margin = history, margin
+    def __init__(self, history: int = 16, margin: int = 0, dgrad: bool = False):
+        self.history, self.margin, self.dgrad = history, margin, dgrad
         self.states: list[Fp8LinearState] = []
         self.step_id = 0
 
@@ -173,6 +188,8 @@ class Fp8Recipe:
                 st.x_meta.update()
             if st.w_meta.calibrated:
                 st.w_meta.update()
+            if st.g_meta.calibrated:
+                st.g_meta.update()
         self.step_id += 1
 
 
@@ -188,6 +205,7 @@ class _Fp8LinearFn(torch.autograd.Function):
                      residual=_as2d(residual) if residual is not None else None)
         ctx.save_for_backward(x2, weight)
         ctx.weight_ref = weight
+        ctx.state = state
         ctx.x_shape = x.shape
         ctx.has_res = residual is not None
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -196,12 +214,18 @@ class _Fp8LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, _ = ctx.saved_tensors
         weight = ctx.weight_ref
+        state = ctx.state
         dy2 = _as2d(dy)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+            if state.recipe.dgrad:
+                dyq = quantize(dy2, state.g_meta)
+                dx = gemm_fp8(dyq, state.weight_t_q(weight), state.g_meta, state.w_meta,
+                              out_dtype=dy.dtype).view(ctx.x_shape)
+            else:
+                dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
         dw = None
         if ctx.needs_input_grad[1]:
             mg = getattr(weight, "main_grad", None)

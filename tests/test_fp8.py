@@ -70,6 +70,22 @@ def test_fp8_linear_forward_close_and_backward_is_the_plain_linear():
     assert st.wq is not wq
 
 
+def test_fp8_data_gradient_option():
+    torch.manual_seed(2)
+    x = torch.randn(40, 64, requires_grad=True)
+    w = (torch.randn(48, 64) * 0.05).requires_grad_()
+    rec = F8.Fp8Recipe(dgrad=True)
+    st = rec.new_state("cpu")
+    y = F8.fp8_linear(x, w, st)
+    dy = torch.randn_like(y) * 1e-3
+    gx, gw = torch.autograd.grad(y, (x, w), dy)
+    rx, rw = dy @ w, dy.t() @ x
+    assert (gx - rx).norm() / rx.norm() < 0.08      # e5m2 dy x e4m3 W^T
+    assert (gx - rx).norm() > 0                     # and it did go through the 8-bit path
+    assert torch.allclose(gw, rw, atol=1e-6)        # the weight gradient stays exact
+    assert st.g_meta.calibrated and st.wtq.shape == (64, 48)
+
+
 def test_engine_trains_with_fp8_forward():
     from ceo_b200.runtime.engine import TrainEngine
     from ceo_b200.utils.config import Config
