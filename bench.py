@@ -112,6 +112,8 @@ def main(argv=None):
                          "operands (training.fp8_training); reported with dtype bf16+fp8-forward")
     ap.add_argument("--fp8-dgrad", action="store_true",
                     help="--fp8 plus the projections' data gradients on e5m2 x e4m3 operands")
+    ap.add_argument("--fp8-all", action="store_true",
+                    help="--fp8-dgrad plus the weight gradients on e5m2 x e4m3 operands")
     ap.add_argument("--tp", type=int, default=0,
                     help="tensor-parallel size (0: 1 for the default config, else the config's)")
     ap.add_argument("--cp", type=int, default=0, help="context-parallel size (0: the config's)")
@@ -160,7 +162,7 @@ def main(argv=None):
     gbs = a.global_batch or cfg.training.global_batch_size
     mbs = a.micro_batch or cfg.training.micro_batch_size
     cfg.training.micro_batch_size = mbs
-    cfg.training.fp8_training = bool(a.fp8 or a.fp8_dgrad)
+    cfg.training.fp8_training = bool(a.fp8 or a.fp8_dgrad or a.fp8_all)
     if world % (tp * cp) or gbs % (mbs * dp):
         raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x dp {dp}")
     n_micro = gbs // (mbs * dp)
@@ -175,8 +177,10 @@ def main(argv=None):
         data_rank = eng.pc.dp_rank
     else:
         eng = TrainEngine(cfg, dev, comm)
-        if a.fp8_dgrad:
+        if a.fp8_dgrad or a.fp8_all:
             eng.fp8.dgrad = True
+        if a.fp8_all:
+            eng.fp8.wgrad = True
         data_rank = rank
     data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
                            cfg.data.synthetic.s, cfg.data.synthetic.seed, data_rank)
@@ -235,7 +239,8 @@ def main(argv=None):
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": ("bf16+fp8-forward+dgrad" if a.fp8_dgrad else
+            "dtype": ("bf16+fp8-forward+dgrad+wgrad" if a.fp8_all else
+                      "bf16+fp8-forward+dgrad" if a.fp8_dgrad else
                       "bf16+fp8-forward" if a.fp8 else "bf16"),
             "data": "synthetic (seeded Zipf(1.1) tokens, N(0,0.02) random-init weights)",
             "config": {"model": cfg.model.name, "global_batch": gbs, "seq_len": seq,

@@ -942,9 +942,10 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
   p.split_k = 1;
   if (fz.kind == 0 && out_f32 && accumulate && !bias && !residual && split_k_mode != 0 &&
-      !f8.on && !ceo::g_deterministic) {
+      !ceo::g_deterministic) {
     // few tiles with a long K (weight gradients): pick the split that fills whole waves best
-    const int num_kb = (K + BK - 1) / BK;
+    const int bke = f8.on ? 2 * BK : BK;
+    const int num_kb = (K + bke - 1) / bke;
     // every extra slice re-sends the whole fp32 C through L2 atomics, so a split has to buy a
     // clear gain in wave efficiency (measured: 5 slices of the 2048x5632 gradient lose)
     double best = 0.0;
@@ -997,7 +998,7 @@ extern "C" int ceo_gemm_fp8(const void* A, const void* B, void* C, int M, int N,
   f8.scale_a = scale_a;
   f8.scale_b = scale_b;
   return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, 1, 0, 0, 0, out_f32, accumulate, alpha,
-                  bias, residual, ldr, 0, status, 0, fz, stream, 0, f8);
+                  bias, residual, ldr, 0, status, 0, fz, stream, 1, f8);
 }
 
 // All-gather fused into the GEMM that consumes the gathered operand.  `gathered` is the table

@@ -164,6 +164,10 @@ int ceo_reduce(const void* x, int dtype, long long n, int mode, float* out, floa
                cudaStream_t stream);
 int ceo_fp8_quantize(const void* x_bf16, void* q, long long n, const float* scale, float* amax_out,
                      int kind, cudaStream_t stream);
+/* codes of x (rows, cols; both multiples of 16) written transposed, qt (cols, rows), and, when q
+ * is not null, in the order of x as well; one read of x. */
+int ceo_fp8_quantize_t(const void* x_bf16, void* q, void* qt, int rows, int cols, long long ldx,
+                       const float* scale, float* amax_out, int kind, cudaStream_t stream);
 int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* scale, int kind,
                        cudaStream_t stream);
 int ceo_fp8_update_scale(float* history, int hist_len, int* cursor, float* amax, float* scale,

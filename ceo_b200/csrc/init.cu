@@ -100,6 +100,59 @@ fp8_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, long long 
   am = block_reduce_max(am, red);
   if (threadIdx.x == 0 && amax_out) atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(am));
 }
+// Quantise a (rows, cols) bf16 matrix and write the codes transposed, qt (cols, rows), and
+// optionally in place order too, q (rows, cols), from one read of x.  64 x 64 tiles go through
+// shared memory; rows and cols are multiples of 16 so every global access is a 16-byte one.
+__global__ void __launch_bounds__(256)
+fp8_quant_t_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ qt,
+                   int rows, int cols, long long ldx, const float* __restrict__ scale,
+                   float* amax_out, int kind) {
+  __shared__ __align__(16) uint8_t tile[64][80];
+  __shared__ float red[33];
+  const float s = *scale;
+  const __nv_fp8_interpretation_t fmt = kind == 0 ? __NV_E4M3 : __NV_E5M2;
+  const int t = threadIdx.x;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  float am = 0.f;
+  {
+    const int row = r0 + (t >> 2), col = c0 + (t & 3) * 16;
+    uint4 codes = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows && col < cols) {
+      uint8_t* cb = reinterpret_cast<uint8_t*>(&codes);
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx + col);
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint4 in = __ldg(src + h2);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = __bfloat1622float2(h[j]);
+          am = fmaxf(am, fmaxf(fabsf(v.x), fabsf(v.y)));
+          const __nv_fp8x2_storage_t pr =
+              __nv_cvt_float2_to_fp8x2(make_float2(v.x * s, v.y * s), __NV_SATFINITE, fmt);
+          cb[h2 * 8 + 2 * j] = static_cast<uint8_t>(pr & 0xff);
+          cb[h2 * 8 + 2 * j + 1] = static_cast<uint8_t>(pr >> 8);
+        }
+      }
+      if (q) *reinterpret_cast<uint4*>(q + static_cast<long long>(row) * cols + col) = codes;
+    }
+    *reinterpret_cast<uint4*>(&tile[t >> 2][(t & 3) * 16]) = codes;
+  }
+  __syncthreads();
+  {
+    // a warp reads 32 neighbouring columns of the same 16 tile rows: conflict-free
+    const int c = t & 63, rseg = (t >> 6) * 16;
+    if (c0 + c < cols && r0 + rseg < rows) {
+      uint4 o;
+      uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ob[i] = tile[rseg + i][c];
+      *reinterpret_cast<uint4*>(qt + static_cast<long long>(c0 + c) * rows + r0 + rseg) = o;
+    }
+  }
+  am = block_reduce_max(am, red);
+  if (t == 0 && amax_out) atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(am));
+}
 __global__ void fp8_dequant_kernel(const uint8_t* __restrict__ q, bf16* __restrict__ x,
                                    long long n, const float* __restrict__ scale, int kind) {
   const float inv = 1.f / *scale;
@@ -169,6 +222,22 @@ extern "C" int ceo_fp8_quantize(const void* x_bf16, void* q, long long n, const 
   if (n <= 0 || kind < 0 || kind > 1) return -5;
   fp8_quant_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(
       static_cast<const bf16*>(x_bf16), static_cast<uint8_t*>(q), n, scale, amax_out, kind);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_fp8_quantize_t(const void* x_bf16, void* q, void* qt, int rows, int cols,
+                                  long long ldx, const float* scale, float* amax_out, int kind,
+                                  cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || kind < 0 || kind > 1 || !qt) return -5;
+  if ((rows & 15) || (cols & 15) || (ldx & 7)) return -5;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(q) |
+       reinterpret_cast<uintptr_t>(qt)) & 15)
+    return -2;
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  if (grid.y > 65535) return -5;
+  fp8_quant_t_kernel<<<grid, 256, 0, stream>>>(static_cast<const bf16*>(x_bf16),
+                                               static_cast<uint8_t*>(q),
+                                               static_cast<uint8_t*>(qt), rows, cols, ldx, scale,
+                                               amax_out, kind);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int ceo_fp8_dequantize(const void* q, void* x_bf16, long long n, const float* scale,

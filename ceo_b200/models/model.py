@@ -198,13 +198,14 @@ class EflaLM(nn.Module):
 
         self.fp8_recipe = None
 
-    def enable_fp8(self, history: int = 16, margin: int = 0, dgrad: bool = False) -> Fp8Recipe:
+    def enable_fp8(self, history: int = 16, margin: int = 0, dgrad: bool = False,
+                   wgrad: bool = False) -> Fp8Recipe:
         """Switches the four projections of every block (qkv, out, up / gate-up, down) to the
         FP8 forward product with per-tensor delayed scaling; the embedding, the norms, EFLA
-        itself and the LM head stay in bf16; ``dgrad`` also moves their data gradients to
-        8-bit operands (e5m2 dy).  The caller invokes ``recipe.step()`` after every optimizer
+        itself and the LM head stay in bf16; ``dgrad`` / ``wgrad`` also move their data /
+        weight gradients to 8-bit operands (e5m2 dy).  The caller invokes ``recipe.step()`` after every optimizer
         step."""
-        rec = Fp8Recipe(history, margin, dgrad)
+        rec = Fp8Recipe(history, margin, dgrad, wgrad)
         dev = self.embed_tokens.device
         for blk in self.blocks:
             blk.efla.fp8 = {"qkv": rec.new_state(dev), "o": rec.new_state(dev)}

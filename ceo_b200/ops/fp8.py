@@ -14,8 +14,11 @@ host.  By default the data- and weight-gradient products stay in bf16 (they read
 bf16 activation and the bf16 weight), which keeps the gradients those of the bf16 model
 evaluated at an fp8-perturbed forward.  With ``Fp8Recipe(dgrad=True)`` the data gradient
 ``dx = dy W`` also runs on 8-bit operands: dy in e5m2 (its own delayed scale) against an e4m3
-copy of ``W^T``, so that both operands are K-major.  Quantised weights (and their transposes)
-are cached for the whole optimizer step.
+copy of ``W^T``, so that both operands are K-major.  With ``wgrad=True`` the weight gradient
+``dW = dy^T x`` does too: one kernel writes the codes of a tensor and of its transpose from a
+single read, the forward keeps ``q(x)^T`` (one byte per element) for the backward instead of
+the bf16 activation, and the GEMM accumulates into the fp32 gradient buffer as the bf16 one
+does.  Quantised weights (and their transposes) are cached for the whole optimizer step.
 
 Without a GPU the same arithmetic runs through ``torch.float8_e4m3fn`` casts in fp32.
 """
@@ -85,6 +88,28 @@ def _quantize_raw(x: torch.Tensor, meta: Fp8Meta) -> torch.Tensor:
                                            meta.scale.data_ptr(), meta.amax.data_ptr(),
                                            meta.kind, _lib.stream()), "ceo_fp8_quantize")
     return q
+
+
+def quantize_t(x: torch.Tensor, meta: Fp8Meta, want_q: bool = True):
+    """Codes of the 2-D tensor ``x`` and of its transpose from one read: ``(q or None, qt)``
+    with ``q`` of shape (rows, cols) and ``qt`` of shape (cols, rows)."""
+    assert x.dim() == 2
+    x = x.contiguous()
+    if not meta.calibrated:
+        _quantize_raw(x, meta)
+        meta.update()
+    rows, cols = x.shape
+    if not x.is_cuda or rows % 16 or cols % 16:
+        q = _quantize_raw(x, meta)
+        return (q if want_q else None), q.t().contiguous()
+    assert x.dtype == torch.bfloat16
+    q = torch.empty(rows, cols, dtype=torch.uint8, device=x.device) if want_q else None
+    qt = torch.empty(cols, rows, dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.lib().ceo_fp8_quantize_t(x.data_ptr(), _lib.ptr(q), qt.data_ptr(), rows, cols,
+                                             x.stride(0), meta.scale.data_ptr(),
+                                             meta.amax.data_ptr(), meta.kind, _lib.stream()),
+               "ceo_fp8_quantize_t")
+    return q, qt
 
 
 def gemm_fp8(aq: torch.Tensor, bq: torch.Tensor, a_meta: Fp8Meta | None = None,
@@ -172,8 +197,9 @@ class Fp8Recipe:
     """Owner of every ``Fp8LinearState`` of a model; ``step()`` is called once per optimizer
     step, after the parameters changed."""
 
-    def __init__(self, history: int = 16, margin: int = 0, dgrad: bool = False):
-        self.history, self.margin, self.dgrad = history, margin, dgrad
+    def __init__(self, history: int = 16, margin: int = 0, dgrad: bool = False,
+                 wgrad: bool = False):
+        self.history, self.margin, self.dgrad, self.wgrad = history, margin, dgrad, wgrad
         self.states: list[Fp8LinearState] = []
         self.step_id = 0
 
@@ -194,16 +220,24 @@ class Fp8Recipe:
 
 
 class _Fp8LinearFn(torch.autograd.Function):
-    """y = dequant(q(x) q(W)^T) (+ residual); gradients as in the bf16 Linear."""
+    """y = dequant(q(x) q(W)^T) (+ residual); gradients as in the bf16 Linear, or on 8-bit
+    operands where the recipe says so."""
 
     @staticmethod
     def forward(ctx, x, weight, residual, state):
         x2 = _as2d(x)
-        xq = quantize(x2, state.x_meta)
+        rec = state.recipe
+        fp8_w = rec.wgrad and x2.shape[0] % 16 == 0 and x2.shape[1] % 16 == 0 \
+            and weight.shape[0] % 16 == 0
+        if fp8_w:
+            xq, xqt = quantize_t(x2, state.x_meta)
+        else:
+            xq, xqt = quantize(x2, state.x_meta), None
         wq = state.weight_q(weight)
         y = gemm_fp8(xq, wq, state.x_meta, state.w_meta, out_dtype=x.dtype,
                      residual=_as2d(residual) if residual is not None else None)
-        ctx.save_for_backward(x2, weight)
+        ctx.save_for_backward(xqt if fp8_w else x2, weight)
+        ctx.fp8_w = fp8_w
         ctx.weight_ref = weight
         ctx.state = state
         ctx.x_shape = x.shape
@@ -212,28 +246,42 @@ class _Fp8LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, _ = ctx.saved_tensors
+        xs, _ = ctx.saved_tensors
         weight = ctx.weight_ref
         state = ctx.state
+        rec = state.recipe
         dy2 = _as2d(dy)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        fp8_d = rec.dgrad and need_x
+        fp8_w = ctx.fp8_w and need_w
+        dyq = dyqt = None
+        if fp8_w:
+            dyq, dyqt = quantize_t(dy2, state.g_meta, want_q=fp8_d)
+        elif fp8_d:
+            dyq = quantize(dy2, state.g_meta)
         dx = None
-        if ctx.needs_input_grad[0]:
-            if state.recipe.dgrad:
-                dyq = quantize(dy2, state.g_meta)
+        if need_x:
+            if fp8_d:
                 dx = gemm_fp8(dyq, state.weight_t_q(weight), state.g_meta, state.w_meta,
                               out_dtype=dy.dtype).view(ctx.x_shape)
             else:
                 dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
         dw = None
-        if ctx.needs_input_grad[1]:
+        if need_w:
             mg = getattr(weight, "main_grad", None)
-            if mg is not None:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
-                weight.grad_touched = True
+            if fp8_w:
+                if mg is not None:
+                    gemm_fp8(dyqt, xs, state.g_meta, state.x_meta, out=mg, accumulate=True)
+                else:
+                    dw = gemm_fp8(dyqt, xs, state.g_meta, state.x_meta, out_dtype=weight.dtype)
+            elif mg is not None:
+                gemm(dy2, xs, a_mn=True, b_mn=True, out=mg, accumulate=True)
             else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+                dw = gemm(dy2, xs, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+            if mg is not None:
+                weight.grad_touched = True
         return dx, dw, (dy if ctx.has_res else None), None
 
 

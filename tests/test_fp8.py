@@ -86,6 +86,27 @@ def test_fp8_data_gradient_option():
     assert st.g_meta.calibrated and st.wtq.shape == (64, 48)
 
 
+def test_fp8_weight_gradient_option():
+    torch.manual_seed(4)
+    x = torch.randn(64, 48, requires_grad=True)
+    w = (torch.randn(32, 48) * 0.05).requires_grad_()
+    w.main_grad = torch.ones(32, 48)
+    rec = F8.Fp8Recipe(dgrad=True, wgrad=True)
+    st = rec.new_state("cpu")
+    y = F8.fp8_linear(x, w, st)
+    assert y.grad_fn.saved_tensors[0].dtype == torch.uint8      # q(x)^T, not the activation
+    assert y.grad_fn.saved_tensors[0].shape == (48, 64)
+    dy = torch.randn_like(y) * 1e-2
+    y.backward(dy)
+    gx = x.grad
+    rw = (dy.t() @ x).detach()
+    got = w.main_grad - 1
+    assert 0 < (got - rw).norm() / rw.norm() < 0.08
+    assert (gx - (dy @ w).detach()).norm() / (dy @ w).norm() < 0.08
+    q, qt = F8.quantize_t(torch.randn(32, 16), F8.Fp8Meta("cpu"))
+    assert torch.equal(q.t(), qt)
+
+
 def test_engine_trains_with_fp8_forward():
     from ceo_b200.runtime.engine import TrainEngine
     from ceo_b200.utils.config import Config

@@ -114,6 +114,49 @@ def test_fp8_data_gradient_option_on_gpu():
     assert (gx.float() - want).norm() / want.norm() < 4e-3
 
 
+@pytest.mark.parametrize("rows,cols,kind", [(64, 64, 0), (4096, 2048, 0), (1008, 784, 1),
+                                            (16, 6208, 1)])
+def test_transposing_quantiser(rows, cols, kind):
+    from ceo_b200.ops import fp8 as F8
+    torch.manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, device=DEV) * 3).bfloat16()
+    meta = F8.Fp8Meta(DEV, kind)
+    meta.calibrated = True
+    meta.scale.fill_(1.7)
+    q, qt = F8.quantize_t(x, meta)
+    lim = F8._FMAX[kind]
+    want = (x.float() * 1.7).clamp(-lim, lim).to(F8._TORCH[kind]).view(torch.uint8)
+    assert torch.equal(q, want) and torch.equal(qt, want.t().contiguous())
+    assert abs(meta.amax.item() - x.float().abs().max().item()) < 1e-6
+    q2, qt2 = F8.quantize_t(x, meta, want_q=False)
+    assert q2 is None and torch.equal(qt2, qt)
+
+
+def test_fp8_weight_gradient_option_on_gpu():
+    from ceo_b200.ops import _lib
+    from ceo_b200.ops import fp8 as F8
+    torch.manual_seed(8)
+    x = torch.randn(2048, 512, device=DEV).bfloat16().requires_grad_()
+    w = (torch.randn(784 + 16, 512, device=DEV) * 0.03).bfloat16().requires_grad_()
+    w.main_grad = torch.ones(800, 512, device=DEV)
+    st = F8.Fp8Recipe(dgrad=True, wgrad=True).new_state(DEV)
+    y = F8.fp8_linear(x, w, st)
+    dy = (torch.randn_like(y.float()) * 1e-3).bfloat16()
+    y.backward(dy)
+    rw = dy.float().t() @ x.float()
+    got = w.main_grad - 1
+    assert 0 < (got - rw).norm() / rw.norm() < 0.08
+    rx = dy.float() @ w.float()
+    assert (x.grad.float() - rx).norm() / rx.norm() < 0.08
+    # the same codes through an fp32 product
+    dyq, dyqt = F8.quantize_t(dy, st.g_meta)
+    xq, xqt = F8.quantize_t(x.detach(), st.x_meta)
+    want = (dyqt.view(torch.float8_e5m2).float() @ xqt.view(torch.float8_e4m3fn).float().t()) \
+        / (st.g_meta.scale * st.x_meta.scale)
+    assert (got - want).norm() / want.norm() < 1e-4
+    assert _lib.read_status() == 0
+
+
 def test_engine_trains_with_fp8_forward_on_gpu():
     from ceo_b200.ops import _lib
     from ceo_b200.runtime.engine import TrainEngine
@@ -123,6 +166,7 @@ def test_engine_trains_with_fp8_forward_on_gpu():
     cfg.training.fp8_training = True
     cfg.model.prism.enabled = False
     eng = TrainEngine(cfg, torch.device(DEV))
+    eng.fp8.dgrad = eng.fp8.wgrad = True
     ref_cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke.yaml"))
     ref_cfg.training.optimizer = "adamw"
     ref_cfg.model.prism.enabled = False
