@@ -64,6 +64,18 @@ class Fp8Meta:
             self.amax.zero_()
         self.calibrated = True
 
+    def state_dict(self) -> dict:
+        return {"scale": float(self.scale), "cursor": int(self.cursor),
+                "history": [float(v) for v in self.history.tolist()],
+                "calibrated": bool(self.calibrated)}
+
+    def load_state_dict(self, d: dict) -> None:
+        self.scale.fill_(float(d["scale"]))
+        self.cursor.fill_(int(d["cursor"]))
+        self.history.copy_(torch.tensor(d["history"], dtype=torch.float32))
+        self.amax.zero_()
+        self.calibrated = bool(d["calibrated"])
+
 
 def quantize(x: torch.Tensor, meta: Fp8Meta) -> torch.Tensor:
     """``sat(x * meta.scale)`` as raw 8-bit codes (uint8, same shape); ``meta.amax`` takes the
@@ -217,6 +229,21 @@ class Fp8Recipe:
             if st.g_meta.calibrated:
                 st.g_meta.update()
         self.step_id += 1
+
+    def state_dict(self) -> dict:
+        """Scales and amax histories of every tensor (plain numbers: goes into a checkpoint's
+        metadata); cached weight codes are rebuilt on the next use."""
+        return {"history": self.history, "margin": self.margin,
+                "states": [[m.state_dict() for m in (st.x_meta, st.w_meta, st.g_meta)]
+                           for st in self.states]}
+
+    def load_state_dict(self, d: dict) -> None:
+        if len(d["states"]) != len(self.states) or d["history"] != self.history:
+            raise ValueError("FP8 state of a different model or recipe")
+        for st, ms in zip(self.states, d["states"]):
+            for m, md in zip((st.x_meta, st.w_meta, st.g_meta), ms):
+                m.load_state_dict(md)
+            st.wq = st.wtq = None
 
 
 class _Fp8LinearFn(torch.autograd.Function):

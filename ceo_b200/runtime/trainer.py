@@ -173,6 +173,8 @@ class Trainer:
         rng = torch.get_rng_state().numpy().tobytes()
         extra = {"scheduler": eng.scheduler.state_dict(),
                  "loader": self.loader.state_dict() if self.loader is not None else None}
+        if eng.fp8 is not None:
+            extra["fp8"] = eng.fp8.state_dict()
         path = self.ckpt.save(eng.step_count, eng.model.state_dict_reference(), md, opt, rng,
                               self.cfg.to_yaml(), extra)
         self.telemetry.log("info", "checkpoint", f"saved {path}")
@@ -219,6 +221,8 @@ class Trainer:
             eng.scheduler.load_state_dict(extra["scheduler"])
         else:
             eng.scheduler.current_step = eng.step_count
+        if extra.get("fp8") and eng.fp8 is not None:
+            eng.fp8.load_state_dict(extra["fp8"])
         self._resume_loader = extra.get("loader")
         if self._resume_loader and not self.cfg.data.synthetic.kind:
             self._open_data()

@@ -121,3 +121,26 @@ def test_engine_trains_with_fp8_forward():
     losses = [float(eng.train_step(batch, lr=3e-3)[0]) for _ in range(5)]
     assert all(l == l for l in losses) and losses[-1] < losses[0]
     assert eng.fp8.step_id == 5
+
+
+def test_recipe_state_roundtrip():
+    torch.manual_seed(9)
+    rec = F8.Fp8Recipe(dgrad=True)
+    st = rec.new_state("cpu")
+    x = torch.randn(32, 32, requires_grad=True)
+    w = (torch.randn(16, 32) * 0.1).requires_grad_()
+    for _ in range(3):
+        F8.fp8_linear(x * (1 + _), w, st).sum().backward()
+        rec.step()
+    d = rec.state_dict()
+    import json
+    d = json.loads(json.dumps(d))
+    rec2 = F8.Fp8Recipe(dgrad=True)
+    st2 = rec2.new_state("cpu")
+    rec2.load_state_dict(d)
+    for a, b in ((st.x_meta, st2.x_meta), (st.w_meta, st2.w_meta), (st.g_meta, st2.g_meta)):
+        assert float(a.scale) == float(b.scale) and torch.equal(a.history, b.history)
+        assert int(a.cursor) == int(b.cursor) and a.calibrated == b.calibrated
+    y1 = F8.fp8_linear(x, w, st)
+    y2 = F8.fp8_linear(x, w, st2)
+    assert torch.equal(y1, y2)
