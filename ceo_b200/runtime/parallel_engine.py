@@ -54,6 +54,11 @@ class ParallelEngine:
         self.rep_group = _group_for(None, rep_sets) if world > 1 else None
         self.tp_size, self.cp_size, self.dp_size = tp, cp, dp
         self.rank, self.world = rank, world
+        self.fp8 = None
+        if cfg.training.fp8_training and rank == 0:
+            import warnings
+            warnings.warn("training.fp8_training is ignored by the tensor / context parallel "
+                          "engine: its projections run in bf16", stacklevel=2)
 
         def make_comm(group, size):
             if size == 1:

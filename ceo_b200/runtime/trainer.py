@@ -49,6 +49,10 @@ class Trainer:
         self.engine = TrainEngine(cfg, self.device, comm)
         self.telemetry = telemetry or Telemetry(rank=self.rank, log_file=None,
                                                 log_level=cfg.telemetry.log_level)
+        if self.engine.fp8 is not None:
+            self.telemetry.log("info", "trainer", "FP8 forward projections enabled "
+                               f"({len(self.engine.fp8.states)} linears, delayed scaling, "
+                               f"history {self.engine.fp8.history})")
         ck = cfg.checkpoint
         self.ckpt = CheckpointManager(checkpoint_dir or ck.dir, ck.keep_last_n, ck.save_optimizer,
                                       ck.async_save, self.rank, self.world)

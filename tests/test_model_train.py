@@ -189,6 +189,26 @@ def test_trainer_checkpoint_resume_is_exact(tmp_path):
         Trainer(cfg, "cpu", checkpoint_dir=str(tmp_path / "ck")).resume(a.ckpt.path_for(6))
 
 
+def test_trainer_resume_restores_fp8_scaling_state(tmp_path):
+    cfg = smoke_cfg()
+    cfg.data.synthetic.kind = ""
+    cfg.data.seq_len = 32
+    cfg.training.global_batch_size = cfg.training.micro_batch_size = 4
+    cfg.training.fp8_training = True
+    cfg.checkpoint.save_interval = 2
+    cfg.checkpoint.async_save = False
+    _write_data(tmp_path / "d.bin")
+    a = Trainer(cfg, "cpu", data_path=str(tmp_path / "d.bin"), checkpoint_dir=str(tmp_path / "ck"))
+    a.run(max_steps=4)
+    ref_params = a.engine.flat.params.clone()
+    b = Trainer(cfg, "cpu", data_path=str(tmp_path / "d.bin"), checkpoint_dir=str(tmp_path / "ck"))
+    b.resume(b.ckpt.path_for(2))
+    st = b.engine.fp8.states[0]
+    assert st.x_meta.calibrated and float(st.x_meta.history.max()) > 0
+    b.run(max_steps=2)
+    assert torch.allclose(b.engine.flat.params, ref_params, atol=1e-6)
+
+
 def test_evaluator_generator_and_top_p(tmp_path):
     cfg = smoke_cfg()
     cfg.data.synthetic.kind = ""
