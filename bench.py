@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 
 REFERENCE_UNAVAILABLE = (
     "reference is a Zig project with no setup.py/pyproject.toml: `pip install --no-index "
-    "--target baseline/_ref /root/reference` answers 'not installable', Zig is not in the "
+    "--target baseline/_ref <reference tree>` answers 'not installable', Zig is not in the "
     "image, and its model forward rejects non-CPU devices (src/model/model.zig:378-380)")
 
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
