@@ -230,6 +230,12 @@ class Fp8Recipe:
                 st.g_meta.update()
         self.step_id += 1
 
+    def invalidate(self) -> None:
+        """Drops the cached weight codes (call after the parameters were replaced, e.g. by a
+        checkpoint load, outside an optimizer step)."""
+        for st in self.states:
+            st.wq = st.wtq = None
+
     def state_dict(self) -> dict:
         """Scales and amax histories of every tensor (plain numbers: goes into a checkpoint's
         metadata); cached weight codes are rebuilt on the next use."""
@@ -243,7 +249,7 @@ class Fp8Recipe:
         for st, ms in zip(self.states, d["states"]):
             for m, md in zip((st.x_meta, st.w_meta, st.g_meta), ms):
                 m.load_state_dict(md)
-            st.wq = st.wtq = None
+        self.invalidate()
 
 
 class _Fp8LinearFn(torch.autograd.Function):

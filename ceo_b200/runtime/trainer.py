@@ -225,8 +225,10 @@ class Trainer:
             eng.scheduler.load_state_dict(extra["scheduler"])
         else:
             eng.scheduler.current_step = eng.step_count
-        if extra.get("fp8") and eng.fp8 is not None:
-            eng.fp8.load_state_dict(extra["fp8"])
+        if eng.fp8 is not None:
+            eng.fp8.invalidate()
+            if extra.get("fp8"):
+                eng.fp8.load_state_dict(extra["fp8"])
         self._resume_loader = extra.get("loader")
         if self._resume_loader and not self.cfg.data.synthetic.kind:
             self._open_data()
