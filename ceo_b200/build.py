@@ -23,6 +23,9 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 OBJ = ROOT / "lib" / "obj"
 LIB = ROOT / "lib" / "libceo_b200.so"
+# debug variant with checked indexing (csrc/common/check.cuh); loaded when CEO_B200_BOUNDS_CHECK=1
+OBJ_CHK = ROOT / "lib" / "obj_chk"
+LIB_CHK = ROOT / "lib" / "libceo_b200_chk.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -49,8 +52,9 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def _compile(src: Path, hdr_mtime: float, verbose: bool, extra: list[str]) -> tuple[Path, str]:
-    obj = OBJ / (src.stem + ".o")
+def _compile(src: Path, hdr_mtime: float, verbose: bool, extra: list[str],
+             objdir: Path = OBJ) -> tuple[Path, str]:
+    obj = objdir / (src.stem + ".o")
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime) and not extra:
         return obj, ""
     cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
@@ -63,34 +67,41 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra: list[str]) -> tu
     return obj, r.stderr
 
 
-def build(verbose: bool = False, force: bool = False, extra: list[str] | None = None) -> Path:
-    """Compile every CUDA source for sm_100a and link the shared library."""
-    extra = extra or []
-    OBJ.mkdir(parents=True, exist_ok=True)
+def build(verbose: bool = False, force: bool = False, extra: list[str] | None = None,
+          bounds_check: bool = False) -> Path:
+    """Compile every CUDA source for sm_100a and link the shared library
+    (``bounds_check``: the debug variant with checked indexing, a separate file)."""
+    extra = list(extra or [])
+    objdir, lib = (OBJ_CHK, LIB_CHK) if bounds_check else (OBJ, LIB)
+    if bounds_check:
+        extra.append("-DCEO_BOUNDS_CHECK")
+        force = True
+    objdir.mkdir(parents=True, exist_ok=True)
     if force:
-        for o in OBJ.glob("*.o"):
+        for o in objdir.glob("*.o"):
             o.unlink()
     hdr_mtime = _deps_mtime()
     srcs = sources()
     objs: list[Path] = []
     logs: list[str] = []
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
-        for obj, log in ex.map(lambda s: _compile(s, hdr_mtime, verbose, extra), srcs):
+        for obj, log in ex.map(lambda s: _compile(s, hdr_mtime, verbose, extra, objdir), srcs):
             objs.append(obj)
             if log:
                 logs.append(log)
     newest = max(o.stat().st_mtime for o in objs)
-    if force or not LIB.exists() or LIB.stat().st_mtime < newest:
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs),
+    if force or not lib.exists() or lib.stat().st_mtime < newest:
+        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     if verbose:
         print("\n".join(logs))
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    p = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    p = build(verbose="-v" in sys.argv, force="-f" in sys.argv,
+              bounds_check="--bounds-check" in sys.argv)
     print(p)

@@ -3,7 +3,10 @@
 // SwiGLU exist there as CPU loops (src/nn/layers.zig:337-383) and its softmax takes
 // the row max with an integer atomic on float bits (layernorm.cu:277).
 #include "common/util.cuh"
+#include "common/check.cuh"
 #include "include/ceo_kernels.h"
+
+CEO_BOUNDS_TU(act)
 
 namespace ceo {
 
@@ -20,11 +23,11 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
     const int c = static_cast<int>(i - r * fv);
     const uint4* row = reinterpret_cast<const uint4*>(gu + r * 2 * F);
     float g[8], u[8], o[8];
-    unpack8(row[c], g);
-    unpack8(row[fv + c], u);
+    unpack8(row[CEO_IDX(c, fv, 201)], g);
+    unpack8(row[CEO_IDX(fv + c, 2 * fv, 202)], u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j];
-    reinterpret_cast<uint4*>(out + r * F)[c] = pack8(o);
+    reinterpret_cast<uint4*>(out)[CEO_IDX(r * fv + c, rows * fv, 203)] = pack8(o);
   }
 }
 

@@ -3,7 +3,10 @@
 // embedding_forward_cuda (kernels/cuda/include/kernels.h:366) without a source and
 // gathers rows on the CPU (src/nn/layers.zig:659-686).
 #include "common/util.cuh"
+#include "common/check.cuh"
 #include "include/ceo_kernels.h"
+
+CEO_BOUNDS_TU(embed)
 
 namespace ceo {
 
@@ -23,8 +26,10 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids,
       for (int c = lane; c < nv; c += 32) o[c] = make_uint4(0, 0, 0, 0);
       continue;
     }
-    const uint4* s = reinterpret_cast<const uint4*>(table + id * D);
-    for (int c = lane; c < nv; c += 32) o[c] = s[c];
+    const uint4* s = reinterpret_cast<const uint4*>(table);
+    for (int c = lane; c < nv; c += 32)
+      reinterpret_cast<uint4*>(out)[CEO_IDX(r * nv + c, n * nv, 301)] =
+          s[CEO_IDX(id * nv + c, vocab * nv, 302)];
   }
 }
 

@@ -153,6 +153,13 @@ int ceo_ns_poly(void* g_bf16, const void* g2_bf16, int n, float a, float b, floa
 int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long long n, float lr,
                    float weight_decay, float scale, cudaStream_t stream);
 
+/* Bounds-checked debug build only (-DCEO_BOUNDS_CHECK; -1 otherwise): out[4] = {violations,
+ * site, index, extent} of the first out-of-range index recorded since the last reset. */
+int ceo_bounds_status(long long* out, int reset);
+/* Checked build only: indexes buf[0 .. n + extra) through the checked accessor (the `extra`
+ * indices are recorded and redirected, nothing outside buf is touched). */
+int ceo_bounds_selftest(float* buf, int n, int extra, cudaStream_t stream);
+
 /* ---- fill / cast / copy / reduce / fp8 (dtype: 0 fp32, 1 fp16, 2 bf16) ---------- */
 int ceo_fill(void* x, int dtype, long long n, float value, cudaStream_t stream);
 int ceo_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,

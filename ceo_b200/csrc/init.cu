@@ -178,6 +178,38 @@ constexpr int GEN_CAP = 148 * 8;
 }  // namespace ceo
 using namespace ceo;
 
+#ifdef CEO_BOUNDS_CHECK
+extern "C" int ceo_bounds_collect_scan(unsigned long long*, int);
+extern "C" int ceo_bounds_collect_act(unsigned long long*, int);
+extern "C" int ceo_bounds_collect_embed(unsigned long long*, int);
+#endif
+// Checked build: synchronises the device, then out[0..3] = {violations, site, index, extent} of
+// the first recorded violation (sites: 1xx scan / gather / scatter / transpose, 2xx
+// activations, 3xx embedding) and returns 0; `reset` clears the records.  Normal build:
+// returns -1 (no checks compiled in).
+extern "C" int ceo_bounds_status(long long* out, int reset) {
+#ifdef CEO_BOUNDS_CHECK
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  int (*const fns[])(unsigned long long*, int) = {ceo_bounds_collect_scan, ceo_bounds_collect_act,
+                                                  ceo_bounds_collect_embed};
+  unsigned long long total = 0, first[4] = {0, 0, 0, 0};
+  for (auto fn : fns) {
+    unsigned long long rec[4];
+    const int rc = fn(rec, reset);
+    if (rc) return rc;
+    if (rec[0] && !first[0]) for (int i = 0; i < 4; ++i) first[i] = rec[i];
+    total += rec[0];
+  }
+  out[0] = static_cast<long long>(total);
+  for (int i = 1; i < 4; ++i) out[i] = static_cast<long long>(first[i]);
+  return 0;
+#else
+  (void)out; (void)reset;
+  return -1;
+#endif
+}
+
 extern "C" int ceo_fill(void* x, int dtype, long long n, float value, cudaStream_t stream) {
   if (n <= 0 || dtype < 0 || dtype > 2) return -5;
   fill_kernel<<<grid_for(n, 1024, GEN_CAP), 256, 0, stream>>>(x, dtype, n, value);

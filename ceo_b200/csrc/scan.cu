@@ -2,7 +2,10 @@
 // 2-D transpose and 32-bit fill.  The reference only names these units in its build list
 // (build.zig:149-161: scan, gather, scatter, memory) and ships no source for them.
 #include "common/util.cuh"
+#include "common/check.cuh"
 #include "include/ceo_kernels.h"
+
+CEO_BOUNDS_TU(scan)
 
 namespace ceo {
 
@@ -110,7 +113,8 @@ __global__ void gather_rows_kernel(const long long* __restrict__ idx, const uint
     const long long id = idx[r];
     const bool ok = id >= 0 && id < src_rows;
     for (int c = lane; c < units; c += 32)
-      dst[r * units + c] = ok ? src[id * units + c] : make_uint4(0, 0, 0, 0);
+      dst[CEO_IDX(r * units + c, n * units, 101)] =
+          ok ? src[CEO_IDX(id * units + c, src_rows * units, 102)] : make_uint4(0, 0, 0, 0);
   }
 }
 // dst[idx[r]] = src[r]  (duplicate indices: one of the writers wins)
@@ -123,7 +127,8 @@ __global__ void scatter_rows_kernel(const long long* __restrict__ idx,
   for (long long r = w; r < n; r += nw) {
     const long long id = idx[r];
     if (id < 0 || id >= dst_rows) continue;
-    for (int c = lane; c < units; c += 32) dst[id * units + c] = src[r * units + c];
+    for (int c = lane; c < units; c += 32)
+      dst[CEO_IDX(id * units + c, dst_rows * units, 103)] = src[CEO_IDX(r * units + c, n * units, 104)];
   }
 }
 // dst[idx[r]] += src[r], fp32 rows of D (multiple of 4) floats
@@ -137,8 +142,9 @@ __global__ void scatter_add_f32_kernel(const long long* __restrict__ idx,
     const long long id = idx[r];
     if (id < 0 || id >= dst_rows) continue;
     for (int c = lane * 4; c < D; c += 128) {
-      const float4 f = *reinterpret_cast<const float4*>(src + r * D + c);
-      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + id * D + c),
+      const float4 f = *reinterpret_cast<const float4*>(src + CEO_IDX(r * D + c, n * D - 3, 105));
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                       dst + CEO_IDX(id * D + c, dst_rows * D - 3, 106)),
                    "f"(f.x), "f"(f.y), "f"(f.z), "f"(f.w)
                    : "memory");
     }
@@ -167,10 +173,12 @@ transpose16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   for (int j = ty; j < 64; j += 4)
-    if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(r0 + j) * lds + c0 + tx];
+    if (r0 + j < rows && c0 + tx < cols)
+      tile[j][tx] = src[CEO_IDX((r0 + j) * lds + c0 + tx, (rows - 1) * lds + cols, 107)];
   __syncthreads();
   for (int j = ty; j < 64; j += 4)
-    if (c0 + j < cols && r0 + tx < rows) dst[(c0 + j) * ldd + r0 + tx] = tile[tx][j];
+    if (c0 + j < cols && r0 + tx < rows)
+      dst[CEO_IDX((c0 + j) * ldd + r0 + tx, (cols - 1) * ldd + rows, 108)] = tile[tx][j];
 }
 
 __global__ void memset32_kernel(uint32_t* __restrict__ x, long long n, uint32_t value) {
@@ -257,6 +265,27 @@ extern "C" int ceo_transpose16(const void* src, void* dst, int rows, int cols, l
                                             static_cast<uint16_t*>(dst), rows, cols, lds, ldd);
   return static_cast<int>(cudaGetLastError());
 }
+// Exercises the recorder of the checked build: reads buf[i] for i in [0, n + extra) through
+// the checked accessor (indices past n are recorded and redirected to element 0, so nothing
+// outside buf is touched) and writes the sum to buf[0].  Normal build: returns -1.
+#ifdef CEO_BOUNDS_CHECK
+__global__ void bounds_selftest_kernel(float* buf, int n, int extra) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n + extra; i += blockDim.x) s += buf[CEO_IDX(i, n, 199)];
+  atomicAdd(&buf[0], s);
+}
+#endif
+extern "C" int ceo_bounds_selftest(float* buf, int n, int extra, cudaStream_t stream) {
+#ifdef CEO_BOUNDS_CHECK
+  if (n <= 0 || extra < 0) return -5;
+  bounds_selftest_kernel<<<1, 64, 0, stream>>>(buf, n, extra);
+  return static_cast<int>(cudaGetLastError());
+#else
+  (void)buf; (void)n; (void)extra; (void)stream;
+  return -1;
+#endif
+}
+
 extern "C" int ceo_memset32(void* x, long long n, unsigned int value, cudaStream_t stream) {
   if (n <= 0) return -5;
   if (!aligned16(x)) return -2;

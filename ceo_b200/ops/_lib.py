@@ -13,13 +13,17 @@ src/kernels/{efla,nn,optim,prism}_kernels.zig.
 from __future__ import annotations
 
 import ctypes
+import os
 import re
 from pathlib import Path
 
 import torch
 
 _PKG = Path(__file__).resolve().parent.parent
-LIB_PATH = _PKG / "lib" / "libceo_b200.so"
+# CEO_B200_BOUNDS_CHECK=1 selects the debug build with checked indexing
+# (`python -m ceo_b200.build --bounds-check`); see bounds_status().
+BOUNDS_CHECK = os.environ.get("CEO_B200_BOUNDS_CHECK", "0") not in ("", "0")
+LIB_PATH = _PKG / "lib" / ("libceo_b200_chk.so" if BOUNDS_CHECK else "libceo_b200.so")
 HEADER_PATH = _PKG / "csrc" / "include" / "ceo_kernels.h"
 
 _lib = None
@@ -29,7 +33,8 @@ _scratch = {}
 # kernels launched per entry point (everything not listed launches exactly one)
 _LAUNCHES = {"ceo_efla_fwd": 3, "ceo_efla_bwd": 3, "ceo_rmsnorm_bwd": 2, "ceo_layernorm_bwd": 4,
              "ceo_sumsq": 2, "ceo_reduce": 2, "ceo_muon_momentum": 2, "ceo_norm_bwd_blocks": 0,
-             "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0, "ceo_cumsum_scratch_floats": 0, "ceo_efla_set_tcgen05": 0}
+             "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0, "ceo_cumsum_scratch_floats": 0,
+             "ceo_efla_set_tcgen05": 0, "ceo_bounds_status": 0, "ceo_fp8_quantize": 1}
 launch_count = 0
 
 
@@ -140,6 +145,17 @@ def read_status(device: torch.device | None = None) -> int:
     """Host read (synchronises) of the wait-status word; 0 means no wait ever gave up."""
     device = device or torch.device("cuda", torch.cuda.current_device())
     return int(status_word(device).item())
+
+
+def bounds_status(reset: bool = True):
+    """Checked build: ``(violations, site, index, extent)`` of the first out-of-range index the
+    kernels recorded (synchronises the device).  Normal build: ``None``."""
+    out = (ctypes.c_longlong * 4)()
+    rc = lib().ceo_bounds_status(ctypes.addressof(out), int(reset))
+    if rc == -1:
+        return None
+    check(rc, "ceo_bounds_status")
+    return tuple(int(v) for v in out)
 
 
 def scratch(device: torch.device, nfloats: int, tag: str = "f32") -> torch.Tensor:

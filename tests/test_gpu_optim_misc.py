@@ -195,3 +195,29 @@ def test_gather_scatter_copy_transpose_memset():
     z = torch.empty(100_003, dtype=torch.int32, device="cuda")
     T.memset32(z, 0xDEADBEEF)
     assert (z.view(torch.int32) == (0xDEADBEEF - 2 ** 32)).all()
+
+
+def test_bounds_checked_build_is_clean_and_its_recorder_works():
+    """The debug build of the library (checked indexing) runs tile-edge shapes without a
+    recorded violation, and its recorder reports indices past an extent (which it redirects,
+    so nothing outside the buffer is touched)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "ceo_b200", "lib", "libceo_b200_chk.so")
+    if not os.path.exists(lib):
+        from ceo_b200 import build as b
+        b.build(bounds_check=True)
+    env = dict(os.environ, CEO_B200_BOUNDS_CHECK="1")
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "bounds_worker.py")], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("BOUNDS ")][-1]
+    out = json.loads(line[len("BOUNDS "):])
+    assert out["clean"] == [0, 0, 0, 0]
+    n, site, idx, extent = out["selftest"]
+    assert n == 5 and site == 199 and 100 <= idx < 105 and extent == 100
+    assert out["after_reset"] == [0, 0, 0, 0]
+    assert out["buf0"] == 1.0 + 100.0 + 5.0      # the five redirected reads saw element 0

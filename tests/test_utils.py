@@ -290,3 +290,12 @@ def test_runtime_queries_without_a_gpu_and_tracing_noop():
     assert not tracing.enabled()
     t = tracing.format_table({"busy_ms": 2.0, "span_ms": 2.5, "kernels": [("k", 3, 1.5), ("j", 1, 0.5)]})
     assert "75.0%" in t and "k" in t
+
+
+def test_normal_build_has_no_bounds_checks_compiled_in():
+    from ceo_b200.ops import _lib
+    if not _lib.available():
+        pytest.skip("kernel library not built")
+    assert not _lib.BOUNDS_CHECK
+    assert _lib.bounds_status() is None
+    assert _lib.lib().ceo_bounds_selftest(None, 4, 1, None) == -1
