@@ -157,7 +157,8 @@ int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long lo
  * site, index, extent} of the first out-of-range index recorded since the last reset. */
 int ceo_bounds_status(long long* out, int reset);
 /* Checked build only: indexes buf[0 .. n + extra) through the checked accessor (the `extra`
- * indices are recorded and redirected, nothing outside buf is touched). */
+ * indices are recorded and redirected, nothing outside buf is touched); buf holds n + 1
+ * floats, the sum is added to buf[n]. */
 int ceo_bounds_selftest(float* buf, int n, int extra, cudaStream_t stream);
 
 /* ---- fill / cast / copy / reduce / fp8 (dtype: 0 fp32, 1 fp16, 2 bf16) ---------- */

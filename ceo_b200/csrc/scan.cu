@@ -267,12 +267,13 @@ extern "C" int ceo_transpose16(const void* src, void* dst, int rows, int cols, l
 }
 // Exercises the recorder of the checked build: reads buf[i] for i in [0, n + extra) through
 // the checked accessor (indices past n are recorded and redirected to element 0, so nothing
-// outside buf is touched) and writes the sum to buf[0].  Normal build: returns -1.
+// outside buf is touched) and adds the sum to buf[n]: buf holds n + 1 floats.  Normal build:
+// returns -1.
 #ifdef CEO_BOUNDS_CHECK
 __global__ void bounds_selftest_kernel(float* buf, int n, int extra) {
   float s = 0.f;
   for (int i = threadIdx.x; i < n + extra; i += blockDim.x) s += buf[CEO_IDX(i, n, 199)];
-  atomicAdd(&buf[0], s);
+  atomicAdd(&buf[n], s);  // one element past the indexed range holds the sum
 }
 #endif
 extern "C" int ceo_bounds_selftest(float* buf, int n, int extra, cudaStream_t stream) {

@@ -40,12 +40,13 @@ def main():
     assert (K.swiglu(gu).float() - g * torch.sigmoid(g) * u).abs().max() < 0.05
     out["clean"] = _lib.bounds_status()
     # the recorder itself: 5 indices past the end of a 100-element buffer, redirected to 0
-    buf = torch.ones(100, device=dev)
+    buf = torch.ones(101, device=dev)
+    buf[100] = 0
     rc = _lib.lib().ceo_bounds_selftest(buf.data_ptr(), 100, 5, _lib.stream())
     assert rc == 0
     out["selftest"] = _lib.bounds_status()
     out["after_reset"] = _lib.bounds_status()
-    out["buf0"] = float(buf[0])
+    out["sum"] = float(buf[100])
     print("BOUNDS " + json.dumps(out))
 
 

@@ -220,4 +220,4 @@ def test_bounds_checked_build_is_clean_and_its_recorder_works():
     n, site, idx, extent = out["selftest"]
     assert n == 5 and site == 199 and 100 <= idx < 105 and extent == 100
     assert out["after_reset"] == [0, 0, 0, 0]
-    assert out["buf0"] == 1.0 + 100.0 + 5.0      # the five redirected reads saw element 0
+    assert out["sum"] == 100.0 + 5.0             # the five redirected reads saw element 0
