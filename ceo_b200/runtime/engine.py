@@ -34,7 +34,8 @@ class TrainEngine:
             _lib.lib().ceo_set_deterministic(int(cfg.runtime.deterministic))
         self.model = EflaLM(cfg.model, self.device, dtype=dtype, seed=seed)
         # training.fp8_training (src/util/config.zig:420): forward projections on e4m3 operands
-        self.fp8 = self.model.enable_fp8() if cfg.training.fp8_training else None
+        g8 = bool(getattr(cfg.training, "fp8_gradients", False))
+        self.fp8 = self.model.enable_fp8(dgrad=g8, wgrad=g8) if cfg.training.fp8_training else None
         self.flat = FlatParams(self.model, self.world, self.rank,
                                alloc=getattr(comm, "alloc", None))
         self.optimizer = build_optimizer(self.flat, cfg.training, comm)

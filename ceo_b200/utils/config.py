@@ -199,6 +199,7 @@ class TrainingConfig:  # config.zig:356-464
     adam_beta1: float = 0.9
     adam_beta2: float = 0.95
     adam_eps: float = 1e-8
+    fp8_gradients: bool = False  # with fp8_training: data / weight gradients on 8-bit operands too
 
     def validate(self) -> None:
         _enum(self.optimizer, OPTIMIZERS, "training.optimizer")

@@ -120,7 +120,12 @@ def test_engine_trains_with_fp8_forward():
     batch = [(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())]
     losses = [float(eng.train_step(batch, lr=3e-3)[0]) for _ in range(5)]
     assert all(l == l for l in losses) and losses[-1] < losses[0]
-    assert eng.fp8.step_id == 5
+    assert eng.fp8.step_id == 5 and not eng.fp8.wgrad
+    cfg.training.fp8_gradients = True
+    eng2 = TrainEngine(cfg, "cpu", seed=0)
+    assert eng2.fp8.dgrad and eng2.fp8.wgrad
+    l2 = [float(eng2.train_step(batch, lr=3e-3)[0]) for _ in range(5)]
+    assert all(l == l for l in l2) and l2[-1] < l2[0]
 
 
 def test_recipe_state_roundtrip():
