@@ -116,6 +116,20 @@ def main(argv=None):
                 3.0 * M * k_in)
             rec(f"gemm_fp8_fwd_{name} {M}x{n_out}x{k_in}",
                 time_ms(lambda: F8.gemm_fp8(xq, wq, mx, mw)), 2.0 * M * n_out * k_in)
+            # gradients: e5m2 dy against e4m3 W^T (data) and e5m2 dy^T against e4m3 x^T (weight,
+            # accumulated into an fp32 buffer), operands from the transposing quantiser
+            dy = torch.randn(M, n_out, device=dev).bfloat16()
+            mg_, mgrad = F8.Fp8Meta(dev, F8.E5M2), torch.zeros(n_out, k_in, device=dev)
+            dyq, dyqt = F8.quantize_t(dy, mg_)
+            _, xqt = F8.quantize_t(xin, mx)
+            wtq = F8.quantize(w.t().contiguous(), mw)
+            rec(f"fp8_quantize_t (codes + transposed codes) {M}x{n_out}",
+                time_ms(lambda: F8.quantize_t(dy, mg_)), 0, 4.0 * M * n_out)
+            rec(f"gemm_fp8_dgrad_{name}", time_ms(lambda: F8.gemm_fp8(dyq, wtq, mg_, mw)),
+                2.0 * M * n_out * k_in)
+            rec(f"gemm_fp8_wgrad_{name} (fp32 accumulate)",
+                time_ms(lambda: F8.gemm_fp8(dyqt, xqt, mg_, mx, out=mgrad, accumulate=True)),
+                2.0 * M * n_out * k_in)
     if want("norm"):
         w = torch.ones(D, device=dev).bfloat16().requires_grad_()
         xr = x.clone().requires_grad_()
