@@ -27,7 +27,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .matmul import _as2d, gemm
+from .matmul import _as2d, gemm, linear
 from .tensor_ops import transpose2d
 
 E4M3, E5M2 = 0, 1
@@ -287,7 +287,7 @@ class _Fp8LinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        fp8_d = rec.dgrad and need_x
+        fp8_d = rec.dgrad and need_x and weight.shape[0] % 16 == 0
         fp8_w = ctx.fp8_w and need_w
         dyq = dyqt = None
         if fp8_w:
@@ -320,5 +320,8 @@ class _Fp8LinearFn(torch.autograd.Function):
 
 def fp8_linear(x: torch.Tensor, weight: torch.Tensor, state: Fp8LinearState,
                residual: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ residual)`` with the product taken on e4m3 operands."""
+    """``x @ weight.T (+ residual)`` with the product taken on e4m3 operands (rows of 8-bit
+    operands must be multiples of 16 bytes: other widths take the bf16 Linear)."""
+    if x.shape[-1] % 16:
+        return linear(x, weight, residual)
     return _Fp8LinearFn.apply(x, weight, residual, state)
