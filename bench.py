@@ -114,6 +114,9 @@ def main(argv=None):
                     help="--fp8 plus the projections' data gradients on e5m2 x e4m3 operands")
     ap.add_argument("--fp8-all", action="store_true",
                     help="--fp8-dgrad plus the weight gradients on e5m2 x e4m3 operands")
+    ap.add_argument("--fp8-margin", type=int, default=-1,
+                    help="FP8 scales leave 2^margin of headroom above the recorded amax "
+                         "(-1: the engine's default, 2)")
     ap.add_argument("--tp", type=int, default=0,
                     help="tensor-parallel size (0: 1 for the default config, else the config's)")
     ap.add_argument("--cp", type=int, default=0, help="context-parallel size (0: the config's)")
@@ -181,6 +184,11 @@ def main(argv=None):
             eng.fp8.dgrad = True
         if a.fp8_all:
             eng.fp8.wgrad = True
+        if eng.fp8 is not None and a.fp8_margin >= 0:
+            eng.fp8.margin = a.fp8_margin
+            for st in eng.fp8.states:
+                for m in (st.x_meta, st.w_meta, st.g_meta):
+                    m.margin = a.fp8_margin
         data_rank = rank
     data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
                            cfg.data.synthetic.s, cfg.data.synthetic.seed, data_rank)

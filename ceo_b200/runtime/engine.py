@@ -35,7 +35,10 @@ class TrainEngine:
         self.model = EflaLM(cfg.model, self.device, dtype=dtype, seed=seed)
         # training.fp8_training (src/util/config.zig:420): forward projections on e4m3 operands
         g8 = bool(getattr(cfg.training, "fp8_gradients", False))
-        self.fp8 = self.model.enable_fp8(dgrad=g8, wgrad=g8) if cfg.training.fp8_training else None
+        # two bits of headroom above the recorded amax: with margin 0 the delayed scales clip
+        # while activations and gradients still grow quickly (first steps of a run)
+        self.fp8 = self.model.enable_fp8(margin=2, dgrad=g8, wgrad=g8) \
+            if cfg.training.fp8_training else None
         self.flat = FlatParams(self.model, self.world, self.rank,
                                alloc=getattr(comm, "alloc", None))
         self.optimizer = build_optimizer(self.flat, cfg.training, comm)
