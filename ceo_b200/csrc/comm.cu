@@ -4,8 +4,10 @@
 // the host), so one kernel per rank can load from and store to its peers directly:
 //
 //   zero_step_kernel   gradient reduce-scatter (peer loads, fp32 sum) + global-norm clip +
-//                      AdamW on the rank's fp32 master slice + bf16 parameter all-gather
-//                      (peer stores) + gradient zeroing, in ONE cooperative launch.
+//                      AdamW or Lion on the rank's fp32 master shard + bf16 parameter
+//                      all-gather (peer stores) + gradient zeroing, in ONE cooperative launch.
+//   zero_bucket_reduce_kernel   the reduce-scatter of one bucket of parameters, launched on a
+//                      side stream as soon as the backward pass has finished that bucket.
 //   symm_barrier_kernel / symm_allreduce_kernel   flag barrier and small all-reduce.
 //
 // Cross-rank synchronisation uses per-rank flag words in peer-mapped memory written with
@@ -19,6 +21,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "common/ptx.cuh"
 #include "common/util.cuh"
 #include "include/ceo_kernels.h"
 
@@ -52,12 +55,13 @@ __device__ bool peer_barrier(const PeerPtrs& flags, int rank, int world, int slo
   for (int r = 0; r < world; ++r)
     st_release_sys(reinterpret_cast<unsigned*>(flags.p[r]) + slot * MAXR + rank, epoch);
   const unsigned* mine = reinterpret_cast<const unsigned*>(flags.p[rank]) + slot * MAXR;
+  const unsigned limit = wait_limit(CEO_PEER_WAIT_LIMIT);
   bool ok = true;
   for (int r = 0; r < world; ++r) {
     unsigned it = 0;
     // epochs only grow; a signed difference tolerates wrap-around
     while (static_cast<int>(ld_acquire_sys(mine + r) - epoch) < 0) {
-      if (++it > CEO_PEER_WAIT_LIMIT) {
+      if (++it > limit) {
         atomicCAS(status, 0, 100 + slot * 10 + r);
         ok = false;
         break;
@@ -69,22 +73,63 @@ __device__ bool peer_barrier(const PeerPtrs& flags, int rank, int world, int slo
   return ok;
 }
 
+// One range of the flat parameter space owned rank by rank: rank r owns the elements
+// [goff + r * len, goff + (r + 1) * len) of the flat buffers and keeps their fp32 master
+// weights and moments at [loff, loff + len) of its shard-local buffers.  `gather`: the updated
+// bf16 values are stored into every rank's parameter buffer by the update itself (otherwise
+// only into this rank's own; a later all-gather fused into the consuming GEMM moves them).
+struct ZRange {
+  long long goff, len, loff;
+  int gather, pad;
+};
+
 struct ZeroStepArgs {
   PeerPtrs grads;    // float*  full gradient buffers (one per rank)
   PeerPtrs params;   // bf16*   full parameter buffers
-  PeerPtrs flags;    // unsigned* flag arrays (4 slots x MAXR)
+  PeerPtrs flags;    // unsigned* flag arrays (slots x MAXR)
   PeerPtrs slots;    // float*  MAXR floats per rank: partial squared norms
-  float* master;     // this rank's fp32 master slice
+  float* master;     // this rank's fp32 master shard
   float* m;
-  float* v;
-  float* local_acc;  // 1 float of local scratch (zeroed by the kernel)
+  float* v;          // AdamW only
+  float* local_acc;  // [0] partial squared norm of this rank's shard, [1] scratch
   float* norm_out;
+  float* clip_out;   // the clip scale the update used (0 = the step was skipped)
   int* status;
-  long long lo, n, total, decay_end;
+  const ZRange* ranges;
+  int nranges;
+  long long total, decay_end;
   int rank, world;
   unsigned epoch;
+  int kind;        // 0 AdamW, 1 Lion
+  int do_reduce;   // 1: reduce the gradients here; 0: zero_bucket_reduce launches did it
   float lr, b1, b2, eps, wd, bc1_inv, bc2_inv, gscale, max_norm;
 };
+
+// Sum of every rank's gradients over this rank's slice of ranges [r0, r1), left in this rank's
+// own gradient buffer; returns the thread's share of the squared norm of the sums.
+__device__ __forceinline__ float reduce_ranges(const PeerPtrs& grads, const ZRange* ranges, int r0,
+                                               int r1, int rank, int world, long long tid,
+                                               long long nth) {
+  float ss = 0.f;
+  for (int ri = r0; ri < r1; ++ri) {
+    const ZRange rg = ranges[ri];
+    const long long base = rg.goff + rank * rg.len;
+    float* gl = reinterpret_cast<float*>(grads.p[rank]) + base;
+    const long long n4 = rg.len >> 2;
+    for (long long i = tid; i < n4; i += nth) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        // L2-only load: peer data must never be served from a stale L1 line
+        const float4 g = __ldcg(reinterpret_cast<const float4*>(
+                                    reinterpret_cast<const float*>(grads.p[r]) + base) + i);
+        s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
+      }
+      reinterpret_cast<float4*>(gl)[i] = s;
+      ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+  }
+  return ss;
+}
 
 __global__ void __launch_bounds__(512)
 zero_step_kernel(const ZeroStepArgs a) {
@@ -93,92 +138,140 @@ zero_step_kernel(const ZeroStepArgs a) {
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
   const bool leader = (blockIdx.x == 0 && threadIdx.x == 0);
+  // local_acc[1] carries the leader's verdict on each peer barrier to the whole grid: when a
+  // bounded wait ran out (a peer never arrived) nothing below touches master weights,
+  // moments, parameters or gradients; the status word says which peer was missing.
+  volatile float* okw = a.local_acc + 1;
 
   // ---- barrier 0: every rank has finished its backward pass --------------------------
   if (leader) {
-    *a.local_acc = 0.f;
-    peer_barrier(a.flags, a.rank, a.world, 0, a.epoch, a.status);
+    if (a.do_reduce) a.local_acc[0] = 0.f;
+    // an earlier wait of this step that ran out (a bucket reduction's barrier) stops the step
+    const bool clean = *reinterpret_cast<volatile int*>(a.status) == 0;
+    const bool ok = clean && peer_barrier(a.flags, a.rank, a.world, 0, a.epoch, a.status);
+    *okw = ok ? 1.f : 0.f;
   }
   grid.sync();
+  if (*okw == 0.f) return;
 
-  // ---- phase 1: reduce this rank's slice over all ranks, keep the sum locally ----------
-  float* gl = reinterpret_cast<float*>(a.grads.p[a.rank]) + a.lo;
-  float ss = 0.f;
-  const long long n4 = a.n >> 2;
-  for (long long i = tid; i < n4; i += nth) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < a.world; ++r) {
-      // L2-only load: peer data must never be served from a stale L1 line
-      const float4 g = __ldcg(reinterpret_cast<const float4*>(
-                                  reinterpret_cast<const float*>(a.grads.p[r]) + a.lo) + i);
-      s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-    }
-    reinterpret_cast<float4*>(gl)[i] = s;
-    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  // ---- phase 1: reduce this rank's slices over all ranks, keep the sums locally ---------
+  if (a.do_reduce) {
+    float ss = reduce_ranges(a.grads, a.ranges, 0, a.nranges, a.rank, a.world, tid, nth);
+    ss = block_reduce_sum(ss, red);
+    if (threadIdx.x == 0) atomicAdd(a.local_acc, ss);
   }
-  ss = block_reduce_sum(ss, red);
-  if (threadIdx.x == 0) atomicAdd(a.local_acc, ss);
   grid.sync();
 
   // ---- exchange the partial squared norms; barrier 1 also means "all slices reduced" ---
   if (leader) {
-    const float mine = *a.local_acc;
+    const float mine = a.local_acc[0];
+    a.local_acc[0] = 0.f;  // ready for the next step's bucket reductions
     for (int r = 0; r < a.world; ++r)
       reinterpret_cast<volatile float*>(a.slots.p[r])[a.rank] = mine;
-    peer_barrier(a.flags, a.rank, a.world, 1, a.epoch, a.status);
+    const bool ok = peer_barrier(a.flags, a.rank, a.world, 1, a.epoch, a.status);
+    *okw = ok ? 1.f : 0.f;
   }
   grid.sync();
+  if (*okw == 0.f) return;
   float tot = 0.f;
   for (int r = 0; r < a.world; ++r)
     tot += reinterpret_cast<volatile const float*>(a.slots.p[a.rank])[r];
   const float nrm = sqrtf(tot) * a.gscale;
   float clip = 1.f;
   if (a.max_norm > 0.f && nrm > a.max_norm) clip = a.max_norm / (nrm + 1e-6f);
-  if (!isfinite(nrm)) clip = 0.f;
-  if (leader && a.norm_out) *a.norm_out = nrm;
+  // a non-finite norm skips the step: states and parameters stay, gradients are dropped
+  const bool skip = !isfinite(nrm);
+  if (skip) clip = 0.f;
+  if (leader) {
+    if (a.norm_out) *a.norm_out = nrm;
+    if (a.clip_out) *a.clip_out = clip;
+  }
   const float gs = a.gscale * clip;
 
-  // ---- phase 2: AdamW on the slice; bf16 result stored into every rank's parameters ----
-  for (long long i = tid; i < n4; i += nth) {
-    const float4 g4 = reinterpret_cast<const float4*>(gl)[i];
-    reinterpret_cast<float4*>(gl)[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // consumed: zero it
-    float4 m4 = reinterpret_cast<float4*>(a.m)[i];
-    float4 v4 = reinterpret_cast<float4*>(a.v)[i];
-    float4 p4 = reinterpret_cast<float4*>(a.master)[i];
-    const float wd = (a.lo + 4 * i < a.decay_end) ? a.wd : 0.f;
-    const float gg[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
-    float* mp = reinterpret_cast<float*>(&m4);
-    float* vp = reinterpret_cast<float*>(&v4);
-    float* pp = reinterpret_cast<float*>(&p4);
+  // ---- phase 2: update the slices; bf16 results stored into the parameter buffers --------
+  for (int ri = 0; ri < a.nranges; ++ri) {
+    const ZRange rg = a.ranges[ri];
+    const long long base = rg.goff + a.rank * rg.len;
+    float* gl = reinterpret_cast<float*>(a.grads.p[a.rank]) + base;
+    float4* mm = reinterpret_cast<float4*>(a.m + rg.loff);
+    float4* vv = reinterpret_cast<float4*>(a.v ? a.v + rg.loff : nullptr);
+    float4* ms = reinterpret_cast<float4*>(a.master + rg.loff);
+    const long long n4 = rg.len >> 2;
+    for (long long i = tid; i < n4; i += nth) {
+      const float4 g4 = reinterpret_cast<const float4*>(gl)[i];
+      reinterpret_cast<float4*>(gl)[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // consumed: zero it
+      if (skip) continue;
+      float4 m4 = mm[i];
+      float4 p4 = ms[i];
+      const float wd = (base + 4 * i < a.decay_end) ? a.wd : 0.f;
+      const float gg[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
+      float* mp = reinterpret_cast<float*>(&m4);
+      float* pp = reinterpret_cast<float*>(&p4);
+      if (a.kind == 0) {
+        float4 v4 = vv[i];
+        float* vp = reinterpret_cast<float*>(&v4);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      mp[j] = a.b1 * mp[j] + (1.f - a.b1) * gg[j];
-      vp[j] = a.b2 * vp[j] + (1.f - a.b2) * gg[j] * gg[j];
-      pp[j] = pp[j] * (1.f - a.lr * wd) -
-              a.lr * (mp[j] * a.bc1_inv) / (sqrtf(vp[j] * a.bc2_inv) + a.eps);
+        for (int j = 0; j < 4; ++j) {
+          mp[j] = a.b1 * mp[j] + (1.f - a.b1) * gg[j];
+          vp[j] = a.b2 * vp[j] + (1.f - a.b2) * gg[j] * gg[j];
+          pp[j] = pp[j] * (1.f - a.lr * wd) -
+                  a.lr * (mp[j] * a.bc1_inv) / (sqrtf(vp[j] * a.bc2_inv) + a.eps);
+        }
+        vv[i] = v4;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float u = a.b1 * mp[j] + (1.f - a.b1) * gg[j];
+          pp[j] = pp[j] * (1.f - a.lr * wd) - a.lr * (u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f));
+          mp[j] = a.b2 * mp[j] + (1.f - a.b2) * gg[j];
+        }
+      }
+      mm[i] = m4;
+      ms[i] = p4;
+      uint2 packed;
+      bf162* h = reinterpret_cast<bf162*>(&packed);
+      h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
+      h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
+      if (rg.gather) {
+        for (int r = 0; r < a.world; ++r)
+          reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[r]) + base)[i] = packed;
+      } else {
+        reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[a.rank]) + base)[i] = packed;
+      }
     }
-    reinterpret_cast<float4*>(a.m)[i] = m4;
-    reinterpret_cast<float4*>(a.v)[i] = v4;
-    reinterpret_cast<float4*>(a.master)[i] = p4;
-    uint2 packed;
-    bf162* h = reinterpret_cast<bf162*>(&packed);
-    h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
-    h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
-    for (int r = 0; r < a.world; ++r)
-      reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[r]) + a.lo)[i] = packed;
   }
-  // every rank is past barrier 1, so nobody reads this rank's gradients any more: zero them
+  // every rank is past barrier 1, so nobody reads this rank's gradients any more: zero the
+  // parts other ranks own (the owned slices were zeroed above by the threads that read them)
   float4* gz = reinterpret_cast<float4*>(a.grads.p[a.rank]);
-  const long long t4 = a.total >> 2;
-  // (the owned slice is zeroed above by the thread that consumed it)
-  const long long s4 = a.lo >> 2, e4 = (a.lo + a.n) >> 2;
-  for (long long i = tid; i < t4; i += nth)
-    if (i < s4 || i >= e4) gz[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int ri = 0; ri < a.nranges; ++ri) {
+    const ZRange rg = a.ranges[ri];
+    const long long s4 = rg.goff >> 2, n4 = (rg.len * a.world) >> 2;
+    const long long o4 = (a.rank * rg.len) >> 2, l4 = rg.len >> 2;
+    for (long long i = tid; i < n4; i += nth)
+      if (i < o4 || i >= o4 + l4) gz[s4 + i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 
   // ---- barrier 2: all parameter slices have landed everywhere -------------------------
   grid.sync();
   if (leader) peer_barrier(a.flags, a.rank, a.world, 2, a.epoch, a.status);
   grid.sync();
+}
+
+// Gradient reduce-scatter of one bucket of ranges, launched on a side stream while the rest
+// of the backward pass still runs: the sums land in this rank's own gradient buffer and their
+// squared norm is added to local_acc[0].  The launch is preceded by a flag barrier (its own
+// kernel on the same stream) that tells every rank the bucket's gradients are final
+// everywhere; when that barrier's wait ran out the status word is set and nothing is reduced.
+__global__ void __launch_bounds__(512)
+zero_bucket_reduce_kernel(PeerPtrs grads, const ZRange* ranges, int r0, int r1, int rank,
+                          int world, float* local_acc, const int* status) {
+  __shared__ float red[33];
+  if (*reinterpret_cast<const volatile int*>(status) != 0) return;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
+  float ss = reduce_ranges(grads, ranges, r0, r1, rank, world, tid, nth);
+  ss = block_reduce_sum(ss, red);
+  if (threadIdx.x == 0) atomicAdd(local_acc, ss);
 }
 
 __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, unsigned epoch,
@@ -233,7 +326,7 @@ static void fill_peers(PeerPtrs& d, void* const* src, int world) {
 
 extern "C" int ceo_symm_barrier(void* const* flags, int rank, int world, int slot,
                                 unsigned int epoch, int* status, cudaStream_t stream) {
-  if (world < 1 || world > MAXR || slot < 0 || slot > 3) return -5;
+  if (world < 1 || world > MAXR || slot < 0 || slot > 7) return -5;
   PeerPtrs f;
   fill_peers(f, flags, world);
   symm_barrier_kernel<<<1, 32, 0, stream>>>(f, rank, world, slot, epoch, status);
@@ -253,12 +346,14 @@ extern "C" int ceo_symm_allreduce(void* const* bufs, void* const* flags, float* 
 
 extern "C" int ceo_zero_step(void* const* grads, void* const* params, void* const* flags,
                              void* const* slots, float* master, float* m, float* v,
-                             float* local_acc, float* norm_out, int* status, long long lo,
-                             long long n, long long total, long long decay_end, int rank,
-                             int world, unsigned int epoch, float lr, float beta1, float beta2,
+                             float* local_acc, float* norm_out, float* clip_out, int* status,
+                             const void* ranges, int nranges, long long total,
+                             long long decay_end, int rank, int world, unsigned int epoch,
+                             int kind, int do_reduce, float lr, float beta1, float beta2,
                              float eps, float weight_decay, int step, float gscale,
-                             float max_norm, cudaStream_t stream) {
-  if (world < 1 || world > MAXR || n <= 0 || (n & 3) || (lo & 3) || (total & 3) || step < 1)
+                             float max_norm, int max_ctas, cudaStream_t stream) {
+  if (world < 1 || world > MAXR || nranges <= 0 || (total & 3) || step < 1 || kind < 0 ||
+      kind > 1 || (kind == 0 && !v))
     return -5;
   ZeroStepArgs a;
   fill_peers(a.grads, grads, world);
@@ -266,25 +361,60 @@ extern "C" int ceo_zero_step(void* const* grads, void* const* params, void* cons
   fill_peers(a.flags, flags, world);
   fill_peers(a.slots, slots, world);
   a.master = master; a.m = m; a.v = v; a.local_acc = local_acc; a.norm_out = norm_out;
+  a.clip_out = clip_out;
   a.status = status;
-  a.lo = lo; a.n = n; a.total = total; a.decay_end = decay_end;
+  a.ranges = static_cast<const ZRange*>(ranges); a.nranges = nranges;
+  a.total = total; a.decay_end = decay_end;
   a.rank = rank; a.world = world; a.epoch = epoch;
+  a.kind = kind; a.do_reduce = do_reduce;
   a.lr = lr; a.b1 = beta1; a.b2 = beta2; a.eps = eps; a.wd = weight_decay;
   a.bc1_inv = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
   a.bc2_inv = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
   a.gscale = gscale; a.max_norm = max_norm;
-  static int grid = 0;
-  if (grid == 0) {
+  static int full_grid = 0;
+  if (full_grid == 0) {
     int dev = 0, sms = 0, occ = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zero_step_kernel, 512, 0);
     if (occ < 1) return -5;
-    grid = sms * (occ > 2 ? 2 : occ);
+    full_grid = sms * (occ > 2 ? 2 : occ);
   }
+  int grid = full_grid;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   void* kargs[] = {&a};
   return static_cast<int>(cudaLaunchCooperativeKernel(
       reinterpret_cast<void*>(zero_step_kernel), dim3(grid), dim3(512), kargs, 0, stream));
+}
+
+// Flag barrier (slot 4) + reduce-scatter of ranges [r0, r1) on `stream` (see
+// zero_bucket_reduce_kernel).  `ctas` bounds the grid so the reduction shares the GPU with
+// the backward pass it overlaps.
+extern "C" int ceo_zero_bucket_reduce(void* const* grads, void* const* flags, const void* ranges,
+                                      int r0, int r1, int rank, int world, unsigned int epoch,
+                                      float* local_acc, int* status, int ctas,
+                                      cudaStream_t stream) {
+  if (world < 1 || world > MAXR || r0 < 0 || r1 <= r0) return -5;
+  PeerPtrs g, f;
+  fill_peers(g, grads, world);
+  fill_peers(f, flags, world);
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(f, rank, world, 4, epoch, status);
+  if (ctas <= 0) ctas = 32;
+  zero_bucket_reduce_kernel<<<ctas, 512, 0, stream>>>(g, static_cast<const ZRange*>(ranges), r0,
+                                                      r1, rank, world, local_acc, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Run-time override of every bounded wait's iteration limit in the library (0 restores the
+// compile-time defaults).  Tests use a small value to make a wait that nothing will ever
+// satisfy run out quickly; production code never calls this.
+extern "C" int ceo_gemm_set_wait_limit(unsigned int iterations);
+extern "C" int ceo_efla_set_wait_limit(unsigned int iterations);
+extern "C" int ceo_set_wait_limit(unsigned int iterations) {
+  int rc = set_wait_limit_override(iterations);
+  if (rc == 0) rc = ceo_gemm_set_wait_limit(iterations);
+  if (rc == 0) rc = ceo_efla_set_wait_limit(iterations);
+  return rc;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -58,8 +58,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #ifndef CEO_WAIT_LIMIT
 #define CEO_WAIT_LIMIT (1u << 22)
 #endif
+// Run-time override of every wait limit of the translation unit that includes this header
+// (0 = the compile-time defaults).  ceo_set_wait_limit() writes it on the host side; tests
+// use a small value to make a wait that nothing satisfies run out quickly.
+static __device__ unsigned ceo_wait_limit_override = 0;
+__device__ __forceinline__ unsigned wait_limit(unsigned dflt) {
+  const unsigned v = ceo_wait_limit_override;
+  return v ? v : dflt;
+}
+static inline int set_wait_limit_override(unsigned iterations) {
+  return static_cast<int>(
+      cudaMemcpyToSymbol(ceo_wait_limit_override, &iterations, sizeof(unsigned)));
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < CEO_WAIT_LIMIT; ++it) {
+  const uint32_t limit = wait_limit(CEO_WAIT_LIMIT);
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) __nanosleep(32);
   }
@@ -162,7 +175,8 @@ __device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
 // Bounded wait until *p (monotonic counter, wrap-tolerant) reaches `target`.
 template <bool SYS>
 __device__ __forceinline__ bool flag_wait_ge(const unsigned* p, unsigned target) {
-  for (unsigned it = 0; it < CEO_FLAG_WAIT_LIMIT; ++it) {
+  const unsigned limit = wait_limit(CEO_FLAG_WAIT_LIMIT);
+  for (unsigned it = 0; it < limit; ++it) {
     const unsigned v = SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu(p);
     if (static_cast<int>(v - target) >= 0) return true;
     __nanosleep(100);

@@ -1448,6 +1448,10 @@ static bool efla_args_ok(int B, int T, int H, int D, long long qs, long long ks,
 }  // namespace ceo
 using namespace ceo;
 
+extern "C" int ceo_efla_set_wait_limit(unsigned int iterations) {
+  return ceo::set_wait_limit_override(iterations);
+}
+
 extern "C" int ceo_efla_set_tcgen05(int on) {
   ceo::g_out_tcgen05 = on != 0;
   return 0;

@@ -67,11 +67,17 @@ struct GemmParams {
   int ag_operand;          // 0 none, 1 A, 2 B
   int ag_ctas;
   int ag_rows_per_shard;   // rows of the gathered operand owned by each rank
+  int ag_blk_rows;         // rows per flag (a divisor of ag_rows_per_shard)
   long long ag_row_bytes;  // bytes per row (dense rows)
   const void* ag_src[8];   // rank r's shard, as mapped on this rank (entry `rank` unused)
   void* ag_dst;            // local gathered buffer
   unsigned* ag_flags;      // local, one per row block, counts up by 1 per call
   unsigned ag_target;
+  // a second tensor gathered by the same copy CTAs after the operand (no flags: it is complete
+  // when the kernel ends); rank r's shard of it is ag_extra_bytes at ag_extra_src[r]
+  const void* ag_extra_src[8];
+  void* ag_extra_dst;      // local buffer, shard r at r * ag_extra_bytes
+  long long ag_extra_bytes;
   // reduce-scatter of C over M: the epilogue stores each partial tile into the staging
   // area of the rank that owns those rows and bumps a counter there; after its last tile a
   // CTA reduces its share of this rank's own rows from the staged partials of all ranks.
@@ -174,15 +180,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         if (p.ag_operand) {
           // rows pulled from a peer become loadable once the copy CTAs have published them
           const int row0 = p.ag_operand == 1 ? m0 : n0;
-          const int blk = p.ag_operand == 1 ? m0 / BM : n0 / BN;
-          if (row0 / p.ag_rows_per_shard != p.rank) {
+          const int rows = p.ag_operand == 1 ? p.M : p.N;
+          const int row1 = min(rows, row0 + (p.ag_operand == 1 ? BM : BN));
+          const int bps = p.ag_rows_per_shard / p.ag_blk_rows;
+          bool waited = false;
+          for (int blk = row0 / p.ag_blk_rows; blk * p.ag_blk_rows < row1 && ok; ++blk) {
+            if (blk / bps == p.rank) continue;
+            waited = true;
             if (!flag_wait_ge<false>(p.ag_flags + blk, p.ag_target)) {
               atomicCAS(p.status, 0, ST_AG_WAIT);
               ok = false;
-              break;
             }
-            fence_proxy_async_all();
           }
+          if (!ok) break;
+          if (waited) fence_proxy_async_all();
         }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -224,7 +235,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         // Pulls row blocks of the peers' shards through a ring of shared-memory buffers with
         // bulk async copies (peer -> smem -> local gathered buffer), nearest peer first, and
         // publishes a block's flag once its bytes have landed in local memory.
-        const int blk_rows = p.ag_operand == 1 ? BM : BN;
+        const int blk_rows = p.ag_blk_rows;
         const int blks_per_shard = p.ag_rows_per_shard / blk_rows;
         const long long blk_bytes = p.ag_row_bytes * blk_rows;
         constexpr uint32_t CHUNK = 32768;
@@ -235,11 +246,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                       p.ag_ctas
                                 : 0;
         const int per_peer = my_blks * cpb;
-        const int total = (p.world - 1) * per_peer;
+        const int total_main = (p.world - 1) * per_peer;
+        // the extra tensor: 32 KB chunks of every peer's shard, dealt round-robin to the copy CTAs
+        const int xchunks = static_cast<int>((p.ag_extra_bytes + CHUNK - 1) / CHUNK);
+        const int per_peer_x = static_cast<int>(blockIdx.x) < xchunks
+                                   ? (xchunks - static_cast<int>(blockIdx.x) + p.ag_ctas - 1) / p.ag_ctas
+                                   : 0;
+        const int total = total_main + (p.world - 1) * per_peer_x;
         uint32_t ring_ph = 0;  // bit i = phase of ring barrier i (bars[0..RING) are count-1)
         // chunk idx -> peer (nearest first), block, byte offset
         auto locate = [&](int idx, const uint8_t*& src, uint8_t*& dst, uint32_t& nb, int& flag,
                           bool& last) {
+          if (idx >= total_main) {
+            const int e = idx - total_main;
+            const int peer = (p.rank + 1 + e / per_peer_x) % p.world;
+            const long long off =
+                (static_cast<long long>(blockIdx.x) + static_cast<long long>(e % per_peer_x) * p.ag_ctas) *
+                CHUNK;
+            const long long left = p.ag_extra_bytes - off;
+            nb = static_cast<uint32_t>(left < CHUNK ? left : CHUNK);
+            src = reinterpret_cast<const uint8_t*>(p.ag_extra_src[peer]) + off;
+            dst = reinterpret_cast<uint8_t*>(p.ag_extra_dst) + peer * p.ag_extra_bytes + off;
+            flag = 0;
+            last = false;
+            return;
+          }
           const int peer = (p.rank + 1 + idx / per_peer) % p.world;
           const int rem = idx % per_peer;
           const int bi = static_cast<int>(blockIdx.x) + (rem / cpb) * p.ag_ctas;
@@ -822,6 +853,9 @@ struct FusedDesc {
   void* const* counters = nullptr; // RS: counters per rank
   unsigned* flags = nullptr;       // AG: local flags
   unsigned target = 0;
+  int blk_rows = 0;                // AG: rows per flag (0: the tile height of the operand)
+  void* const* extra = nullptr;    // AG: a second tensor's buffers per rank (optional)
+  long long extra_shard_bytes = 0;
   void* rs_out = nullptr;
   const void* rs_residual = nullptr;
   long long rs_ldo = 0;
@@ -900,24 +934,39 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   if (fz.kind == 1 || fz.kind == 2) {
     // gathered operand: K-major rows only, shards of whole row blocks, dense rows
     const int rows = fz.kind == 1 ? M : N;
-    const int blk = fz.kind == 1 ? BM : BN;
+    const int tile = fz.kind == 1 ? BM : BN;
+    const int blk = fz.blk_rows > 0 ? fz.blk_rows : tile;
     const long long ld = fz.kind == 1 ? lda : ldb;
     if ((fz.kind == 1 ? a_mn_major : b_mn_major) || batch != 1 || ld != K ||
-        rows % fz.world || (rows / fz.world) % blk || fz.world < 2 || fz.world > 8)
+        rows % fz.world || (rows / fz.world) % blk || fz.world < 2 || fz.world > 8 ||
+        (fz.extra_shard_bytes & 15) || (fz.extra_shard_bytes > 0 && !fz.extra))
       return -5;
     p.ag_operand = fz.kind;
     p.ag_ctas = fz.copy_ctas > 0 ? fz.copy_ctas : 8;
     if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
     p.ag_rows_per_shard = rows / fz.world;
+    p.ag_blk_rows = blk;
     p.ag_row_bytes = static_cast<long long>(K) * 2;
+    if (fz.extra_shard_bytes > 0) {
+      p.ag_extra_bytes = fz.extra_shard_bytes;
+      for (int r = 0; r < fz.world; ++r)
+        p.ag_extra_src[r] = static_cast<const uint8_t*>(fz.extra[r]) + r * fz.extra_shard_bytes;
+      p.ag_extra_dst = fz.extra[fz.rank];
+    }
     for (int r = 0; r < fz.world; ++r)
       p.ag_src[r] = static_cast<const uint8_t*>(fz.peers[r]) +
                     static_cast<long long>(r) * p.ag_rows_per_shard * p.ag_row_bytes;
     p.ag_dst = const_cast<void*>(fz.kind == 1 ? A : B);
     p.ag_flags = fz.flags;
     p.ag_target = fz.target;
-    const int rot = fz.rank * (p.ag_rows_per_shard / blk);
-    if (fz.kind == 1) { p.m_rot = rot; p.grp_m = p.ag_rows_per_shard / blk; } else p.n_rot = rot;
+    // the traversal starts at the tile that holds this rank's first row
+    const int rot = static_cast<int>(static_cast<long long>(fz.rank) * p.ag_rows_per_shard / tile);
+    if (fz.kind == 1) {
+      p.m_rot = rot;
+      if (p.ag_rows_per_shard % tile == 0) p.grp_m = p.ag_rows_per_shard / tile;
+    } else {
+      p.n_rot = rot;
+    }
   } else if (fz.kind == 3) {
     if (batch != 1 || out_f32 || accumulate || bias || residual || M % fz.world ||
         (M / fz.world) % BM || (N & 7) || fz.world < 2 || fz.world > 8)
@@ -1006,12 +1055,18 @@ extern "C" int ceo_gemm_fp8(const void* A, const void* B, void* C, int M, int N,
 // rows [r*rows/world, (r+1)*rows/world) of ITS buffer, and copy CTAs of this launch pull the
 // other shards from the peers while the remaining CTAs compute, local rows first.
 // operand: 1 = A (M rows gathered), 2 = B (N rows gathered).  The non-gathered operand and C
-// are ordinary local tensors.  `flags`: local unsigned[rows/block]; target grows by 1 per call.
+// are ordinary local tensors.  `flags`: local unsigned[rows/blk_rows]; target grows by 1 per
+// call.  blk_rows (0 = 128 for A, 256 for B) is the row granularity of the flags: shards must
+// be whole multiples of it, which lets a weight matrix whose row count is not a multiple of
+// world x 256 be gathered (FSDP weight shards).  `extra` (optional): the per-rank buffers of
+// a second tensor sharded the same way (extra_shard_bytes per rank, shard r at byte offset
+// r * extra_shard_bytes); the copy CTAs gather it after the operand, complete at kernel end.
 extern "C" int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void* C,
                                 int M, int N, int K, long long ld_other, long long ldc,
                                 int other_mn_major, int out_f32, int accumulate, float alpha,
                                 const void* residual, long long ldr, void* flags,
                                 unsigned int target, int rank, int world, int copy_ctas,
+                                int blk_rows, void* const* extra, long long extra_shard_bytes,
                                 int* status, cudaStream_t stream) {
   if (operand != 1 && operand != 2) return -5;
   FusedDesc fz;
@@ -1022,6 +1077,9 @@ extern "C" int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* 
   fz.peers = gathered;
   fz.flags = static_cast<unsigned*>(flags);
   fz.target = target;
+  fz.blk_rows = blk_rows;
+  fz.extra = extra;
+  fz.extra_shard_bytes = extra_shard_bytes;
   const void* A = operand == 1 ? gathered[rank] : other;
   const void* B = operand == 2 ? gathered[rank] : other;
   return gemm_run(A, B, C, M, N, K, operand == 1 ? K : ld_other, operand == 2 ? K : ld_other, ldc,
@@ -1050,6 +1108,10 @@ extern "C" int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int 
   fz.rs_ldo = ldo;
   return gemm_run(A, B, stage[rank], M, N, K, lda, ldb, N, a_mn_major, b_mn_major, 1, 0, 0, 0, 0,
                   0, alpha, nullptr, nullptr, 0, 0, status, 0, fz, stream);
+}
+
+extern "C" int ceo_gemm_set_wait_limit(unsigned int iterations) {
+  return ceo::set_wait_limit_override(iterations);
 }
 
 // 1 = bit-reproducible GEMM results (weight-gradient GEMMs then never split K).

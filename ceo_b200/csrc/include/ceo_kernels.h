@@ -150,8 +150,11 @@ int ceo_muon_normalize(const float* m, const float* sumsq, void* y_bf16, long lo
                        cudaStream_t stream);
 int ceo_ns_poly(void* g_bf16, const void* g2_bf16, int n, float a, float b, float c,
                 cudaStream_t stream);
+/* gscale_ptr (optional): the device clip scale of the step; exactly 0 marks a step whose
+ * gradient norm was not finite, which every update kernel above and this one then skip. */
 int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long long n, float lr,
-                   float weight_decay, float scale, cudaStream_t stream);
+                   float weight_decay, float scale, const float* gscale_ptr,
+                   cudaStream_t stream);
 
 /* Bounds-checked debug build only (-DCEO_BOUNDS_CHECK; -1 otherwise): out[4] = {violations,
  * site, index, extent} of the first out-of-range index recorded since the last reset. */
@@ -214,7 +217,7 @@ int ceo_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, lon
 /* ---- peer-memory collectives (NVLink), fused with their compute --------------------------
  * Buffers are plain cudaMalloc allocations mapped into every rank through CUDA IPC; the
  * `void* const*` arguments are host arrays of `world` device pointers indexed by rank (this
- * rank's own entry is its local pointer).  flags: 4 slots x 8 unsigned per rank, zeroed once;
+ * rank's own entry is its local pointer).  flags: 8 slots x 8 unsigned per rank, zeroed once;
  * `epoch` must grow by at least 2 between uses of the same slot set.  world <= 8. */
 int ceo_dev_malloc(void** out, long long bytes);
 int ceo_dev_free(void* p);
@@ -230,12 +233,16 @@ int ceo_symm_allreduce(void* const* bufs, void* const* flags, float* out, int n,
  * with bulk async copies while the other CTAs compute, local rows first; the TMA producer
  * waits on per-row-block flags).  gathered[r] = rank r's (rows x K) bf16 buffer whose own
  * shard is already in place; operand 1 = A (M rows), 2 = B (N rows).  flags: local
- * unsigned[rows / (128 for A, 256 for B)], zeroed once; target grows by 1 per call.
+ * unsigned[rows / blk_rows], zeroed once; target grows by 1 per call.  blk_rows: rows per
+ * flag, a divisor of rows / world (0 = 128 for A, 256 for B).  extra (optional): per-rank
+ * buffers of a second tensor sharded into extra_shard_bytes per rank that the copy CTAs
+ * gather after the operand (complete when the kernel ends).
  * Call ceo_symm_barrier first so every rank's shard is complete. */
 int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void* C, int M, int N,
                      int K, long long ld_other, long long ldc, int other_mn_major, int out_f32,
                      int accumulate, float alpha, const void* residual, long long ldr, void* flags,
-                     unsigned int target, int rank, int world, int copy_ctas, int* status,
+                     unsigned int target, int rank, int world, int copy_ctas, int blk_rows,
+                     void* const* extra, long long extra_shard_bytes, int* status,
                      cudaStream_t stream);
 /* GEMM fused with the reduce-scatter of its output over M (epilogue stores partial tiles
  * into the owner's staging area over NVLink and bumps its counters; each rank then reduces
@@ -253,14 +260,35 @@ int ceo_cp_exchange(const float* src, void* const* gather, void* const* flags, l
                     int rank, int world, unsigned int epoch, unsigned int* done_counter,
                     int* status, cudaStream_t stream);
 /* One cooperative launch per rank: reduce-scatter of the fp32 gradients (peer loads) ->
- * global-norm clip -> AdamW on the rank's fp32 master slice [lo, lo+n) -> bf16 parameters
- * stored into every rank's buffer -> this rank's gradient buffer zeroed. */
+ * global-norm clip -> AdamW (kind 0) or Lion (kind 1; v unused) on the rank's fp32 master
+ * shard -> bf16 parameters stored into every rank's buffer -> this rank's gradient buffer
+ * zeroed.  `ranges`: device array of nranges records {long long goff, len, loff; int gather,
+ * pad}: rank r owns flat elements [goff + r*len, goff + (r+1)*len), its master weights and
+ * moments for them sit at [loff, loff + len) of master / m / v; gather = 0 keeps the updated
+ * bf16 values local (a later fused all-gather moves them).  do_reduce = 0: the gradients
+ * were already reduced by ceo_zero_bucket_reduce launches, whose squared norms are in
+ * local_acc[0].  local_acc: 2 floats.  clip_out receives the clip scale used; 0 means the
+ * gradient norm was not finite and the step was skipped (states and parameters untouched,
+ * gradients zeroed).  When a peer barrier's bounded wait runs out the kernel writes the
+ * status word and returns without touching any state. */
 int ceo_zero_step(void* const* grads, void* const* params, void* const* flags, void* const* slots,
                   float* master, float* m, float* v, float* local_acc, float* norm_out,
-                  int* status, long long lo, long long n, long long total, long long decay_end,
-                  int rank, int world, unsigned int epoch, float lr, float beta1, float beta2,
-                  float eps, float weight_decay, int step, float gscale, float max_norm,
+                  float* clip_out, int* status, const void* ranges, int nranges, long long total,
+                  long long decay_end, int rank, int world, unsigned int epoch, int kind,
+                  int do_reduce, float lr, float beta1, float beta2, float eps,
+                  float weight_decay, int step, float gscale, float max_norm, int max_ctas,
                   cudaStream_t stream);
+/* Flag barrier (slot 4) + reduce-scatter of ranges [r0, r1) on `stream`, for overlap with the
+ * rest of the backward pass: the sums stay in this rank's gradient buffer, their squared norm
+ * is added to local_acc[0].  ctas bounds the grid (0 = 32). */
+int ceo_zero_bucket_reduce(void* const* grads, void* const* flags, const void* ranges, int r0,
+                           int r1, int rank, int world, unsigned int epoch, float* local_acc,
+                           int* status, int ctas, cudaStream_t stream);
+/* Run-time override of the iteration limit of every bounded wait in the library (0 = the
+ * compile-time defaults).  For tests that make a wait run out; not for production use. */
+int ceo_set_wait_limit(unsigned int iterations);
+int ceo_gemm_set_wait_limit(unsigned int iterations);
+int ceo_efla_set_wait_limit(unsigned int iterations);
 
 #ifdef __cplusplus
 }

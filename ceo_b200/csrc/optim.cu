@@ -80,6 +80,24 @@ __global__ void clip_value_kernel(float* x, long long n, float c) {
     x[i] = fminf(fmaxf(x[i], -c), c);
 }
 
+// A clip scale of exactly zero marks a step whose gradient norm was not finite
+// (clip_scale_kernel): every update kernel then leaves master weights, moments and shadow
+// parameters untouched and only zeroes the gradients it was asked to zero.
+__device__ __forceinline__ bool step_skipped(const float* gscale_ptr) {
+  return gscale_ptr != nullptr && *gscale_ptr == 0.f;
+}
+template <typename G>
+__device__ __forceinline__ void zero_range(G* grad, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    grad[i] = static_cast<G>(0.f);
+}
+__device__ __forceinline__ void zero_range4(float4* grad, long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    grad[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 // ------------------------------------------------------------------------ AdamW
 template <typename G>
 __global__ void __launch_bounds__(256)
@@ -87,6 +105,10 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
              G* __restrict__ grad, bf16* __restrict__ shadow, long long n, float lr, float b1,
              float b2, float eps, float wd, float bc1_inv, float bc2_inv,
              const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  if (step_skipped(gscale_ptr)) {
+    if (zero_grad) zero_range<G>(grad, n);
+    return;
+  }
   const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -110,6 +132,10 @@ __global__ void __launch_bounds__(256)
 lion_kernel(float* __restrict__ master, float* __restrict__ m, G* __restrict__ grad,
             bf16* __restrict__ shadow, long long n, float lr, float b1, float b2, float wd,
             const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  if (step_skipped(gscale_ptr)) {
+    if (zero_grad) zero_range<G>(grad, n);
+    return;
+  }
   const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -134,12 +160,14 @@ muon_momentum_kernel(float* __restrict__ m, G* __restrict__ grad, long long n, f
                      const float* __restrict__ gscale_ptr, float gscale, int zero_grad,
                      float* __restrict__ partial) {
   __shared__ float red[33];
+  const bool skip = step_skipped(gscale_ptr);
   const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   float s = 0.f;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float mi = beta * m[i] + ldg_f<G>(grad, i) * gs;
-    m[i] = mi;
+    // a skipped step keeps the momentum (the apply kernel skips too); the sum is still formed
+    const float mi = skip ? m[i] : beta * m[i] + ldg_f<G>(grad, i) * gs;
+    if (!skip) m[i] = mi;
     s += mi * mi;
     if (zero_grad) grad[i] = static_cast<G>(0.f);
   }
@@ -169,7 +197,8 @@ __global__ void ns_poly_kernel(bf16* __restrict__ g, const bf16* __restrict__ g2
 // p = p*(1-lr*wd) - lr*scale*y
 __global__ void muon_apply_kernel(float* __restrict__ master, const bf16* __restrict__ y,
                                   bf16* __restrict__ shadow, long long n, float lr, float wd,
-                                  float scale) {
+                                  float scale, const float* __restrict__ gscale_ptr) {
+  if (step_skipped(gscale_ptr)) return;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float p = master[i];
@@ -186,6 +215,10 @@ adamw_vec4_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* _
                   float4* __restrict__ grad, uint2* __restrict__ shadow, long long n4, float lr,
                   float b1, float b2, float eps, float wd, float bc1_inv, float bc2_inv,
                   const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  if (step_skipped(gscale_ptr)) {
+    if (zero_grad) zero_range4(grad, n4);
+    return;
+  }
   const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   const float decay = 1.f - lr * wd;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
@@ -220,6 +253,10 @@ __global__ void __launch_bounds__(256)
 lion_vec4_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ grad,
                  uint2* __restrict__ shadow, long long n4, float lr, float b1, float b2, float wd,
                  const float* __restrict__ gscale_ptr, float gscale, int zero_grad) {
+  if (step_skipped(gscale_ptr)) {
+    if (zero_grad) zero_range4(grad, n4);
+    return;
+  }
   const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   const float decay = 1.f - lr * wd;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
@@ -384,10 +421,11 @@ extern "C" int ceo_ns_poly(void* g_bf16, const void* g2_bf16, int n, float a, fl
 }
 
 extern "C" int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long long n,
-                              float lr, float weight_decay, float scale, cudaStream_t stream) {
+                              float lr, float weight_decay, float scale,
+                              const float* gscale_ptr, cudaStream_t stream) {
   if (n <= 0) return -5;
   muon_apply_kernel<<<grid_for(n, 256 * 4, OPT_GRID_CAP), 256, 0, stream>>>(
       master, static_cast<const bf16*>(y_bf16), static_cast<bf16*>(shadow_bf16), n, lr,
-      weight_decay, scale);
+      weight_decay, scale, gscale_ptr);
   return static_cast<int>(cudaGetLastError());
 }

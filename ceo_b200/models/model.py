@@ -16,6 +16,7 @@ the per-matrix (in, out) tensors of the checkpoint format (src/nn/layers.zig:509
 """
 from __future__ import annotations
 
+import functools
 import math
 from collections import OrderedDict
 
@@ -197,6 +198,8 @@ class EflaLM(nn.Module):
             _param((cfg.vocab_size, cfg.hidden_dim), init_std, device, dtype, gen)
 
         self.fp8_recipe = None
+        # optional callable (block index, grad) -> grad, registered on every block's input
+        self.block_input_hook = None
 
     def enable_fp8(self, history: int = 16, margin: int = 0, dgrad: bool = False,
                    wgrad: bool = False) -> Fp8Recipe:
@@ -221,6 +224,9 @@ class EflaLM(nn.Module):
         h = K.embedding(tokens, self.embed_tokens)
         finals = []
         for i, blk in enumerate(self.blocks):
+            if self.block_input_hook is not None and h.requires_grad:
+                # fires in the backward pass once block i has produced all its gradients
+                h.register_hook(functools.partial(self.block_input_hook, i))
             h, s = blk(h, None if states is None else states[i], resets)
             finals.append(s)
         return self.final_norm(h), finals

@@ -34,7 +34,10 @@ _scratch = {}
 _LAUNCHES = {"ceo_efla_fwd": 3, "ceo_efla_bwd": 3, "ceo_rmsnorm_bwd": 2, "ceo_layernorm_bwd": 4,
              "ceo_sumsq": 2, "ceo_reduce": 2, "ceo_muon_momentum": 2, "ceo_norm_bwd_blocks": 0,
              "ceo_sumsq_blocks": 0, "ceo_reduce_blocks": 0, "ceo_cumsum_scratch_floats": 0,
-             "ceo_efla_set_tcgen05": 0, "ceo_bounds_status": 0, "ceo_fp8_quantize": 1}
+             "ceo_efla_set_tcgen05": 0, "ceo_bounds_status": 0, "ceo_fp8_quantize": 1,
+             "ceo_zero_bucket_reduce": 2, "ceo_set_wait_limit": 0, "ceo_gemm_set_wait_limit": 0,
+             "ceo_efla_set_wait_limit": 0, "ceo_set_deterministic": 0, "ceo_dev_malloc": 0,
+             "ceo_dev_free": 0, "ceo_ipc_get_handle": 0, "ceo_ipc_open": 0, "ceo_ipc_close": 0}
 launch_count = 0
 
 

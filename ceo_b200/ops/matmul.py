@@ -97,7 +97,13 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, residual):
         x2 = _as2d(x)
-        y = gemm(x2, weight, residual=_as2d(residual) if residual is not None else None)
+        res2 = _as2d(residual) if residual is not None else None
+        fg = getattr(weight, "fsdp_gather", None)
+        if fg is not None and fg.pending:
+            # FSDP: the weight is still row shards; its all-gather rides inside this GEMM
+            y = fg.gemm(x2 if x2.is_contiguous() else x2.contiguous(), res2)
+        else:
+            y = gemm(x2, weight, residual=res2)
         ctx.save_for_backward(x2, weight)
         ctx.weight_ref = weight  # the Parameter object itself (carries .main_grad)
         ctx.x_shape = x.shape

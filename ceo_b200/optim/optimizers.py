@@ -114,6 +114,9 @@ class ShardedOptimizer:
         self.extra_norm_group = None
         self.replicated_names: set = set()
         self.use_fused_step = True
+        # set by the engine when the bucket reductions of the backward pass have already
+        # reduce-scattered this step's gradients (ZeRO stage 2 / 3)
+        self.grads_reduced = False
         self.uses_matrices = kind in ("muon", "lion_muon")
         if self.uses_matrices:
             self._matrix_segs = [s for s in flat.segments if len(s.shape) == 2 and s.decay]
@@ -123,6 +126,13 @@ class ShardedOptimizer:
     # -------------------------------------------------------------- gradient plumbing
     def _world(self):
         return self.flat.world
+
+    def fused_step_available(self) -> bool:
+        """True when one peer-memory kernel does the whole step (``FusedComm.zero_step``)."""
+        f = self.flat
+        return (self.use_fused_step and self.kind in ("adamw", "lion") and self._world() > 1
+                and getattr(self.comm, "fused", False) and f.grads_symm is not None
+                and f.param_dtype == torch.bfloat16 and f.grads.dtype == torch.float32)
 
     def _reduce_grads(self):
         """Returns the fp32 gradient tensor the update reads, aligned with the owned slice."""
@@ -268,8 +278,8 @@ class ShardedOptimizer:
                                             seg.numel, 1e-7, _lib.stream()), "ceo_muon_normalize")
             y = self._newton_schulz(y)
             _lib.check(L.ceo_muon_apply(st["master"].data_ptr(), y.data_ptr(), p.data_ptr(),
-                                        seg.numel, float(lr), 0.0, 1.0, _lib.stream()),
-                       "ceo_muon_apply")
+                                        seg.numel, float(lr), 0.0, 1.0, self._scale.data_ptr(),
+                                        _lib.stream()), "ceo_muon_apply")
         else:
             st["momentum"].mul_(self.muon_momentum).add_(g.float() * (gscale * float(self._scale)))
             mm = st["momentum"].view(seg.shape)
@@ -279,21 +289,27 @@ class ShardedOptimizer:
             p.copy_(st["master"])
 
     def _side_update(self, side, lr, gscale):
-        s = gscale * float(self._scale) if side else 1.0
-        for (name, p), g in zip([(n, p) for n, p in self.flat.side if p.grad is not None
-                                 and p.requires_grad], side):
+        """The few parameters outside the flat buffers (fp32 scalars).  The clip scale stays a
+        device tensor (no host read); a scale of exactly zero marks a skipped step, which
+        leaves parameter and moments as they were."""
+        if not side:
+            return
+        sc = self._scale.reshape(()) if self.cuda else self._scale.reshape(()).clone()
+        skip = sc == 0
+        live = [(n, p) for n, p in self.flat.side if p.grad is not None and p.requires_grad]
+        for (name, p), g in zip(live, side):
             st = self._side_state.setdefault(name, {"m": torch.zeros_like(p, dtype=torch.float32),
                                                     "v": torch.zeros_like(p, dtype=torch.float32)})
-            gg = g.float() * s
+            gg = torch.where(skip, torch.zeros_like(g, dtype=torch.float32), g.float() * gscale * sc)
+            pf, m, v = p.data.float(), st["m"].clone(), st["v"].clone()
             if self.kind == "adamw":
-                pf = p.data.float()
-                ref.adamw_step(pf, st["m"], st["v"], gg, lr, self.betas[0], self.betas[1],
-                               self.eps, 0.0, self.step_count)
-                p.data.copy_(pf)
+                ref.adamw_step(pf, m, v, gg, lr, self.betas[0], self.betas[1], self.eps, 0.0,
+                               self.step_count)
             else:
-                pf = p.data.float()
-                ref.lion_step(pf, st["m"], gg, lr, self.lion_betas[0], self.lion_betas[1], 0.0)
-                p.data.copy_(pf)
+                ref.lion_step(pf, m, gg, lr, self.lion_betas[0], self.lion_betas[1], 0.0)
+            p.data.copy_(torch.where(skip, p.data.float(), pf))
+            st["m"].copy_(torch.where(skip, st["m"], m))
+            st["v"].copy_(torch.where(skip, st["v"], v))
 
     # -------------------------------------------------------------------------- step
     def step(self, lr: float, grad_scale: float = 1.0) -> torch.Tensor:
@@ -302,24 +318,33 @@ class ShardedOptimizer:
         gradient norm as a device scalar (no host synchronisation)."""
         f = self.flat
         self.step_count += 1
-        if (self.use_fused_step and self.kind == "adamw" and self._world() > 1
-                and getattr(self.comm, "fused", False)
-                and f.grads_symm is not None and f.param_dtype == torch.bfloat16
-                and f.grads.dtype == torch.float32):
-            # one kernel: reduce-scatter + clip + AdamW + all-gather + zero-grad over NVLink
+        if self.fused_step_available():
+            # one kernel: reduce-scatter (unless the bucket reductions of the backward pass
+            # already did it) + clip + AdamW / Lion + all-gather + zero-grad over NVLink
             side = self._side_grads()
-            norm = self.comm.zero_step(f, f.buffer("exp_avg"), f.buffer("exp_avg_sq"), lr=lr,
-                                       betas=self.betas, eps=self.eps, weight_decay=self.wd,
-                                       step=self.step_count, grad_scale=grad_scale,
-                                       max_norm=self.max_norm)
-            self._scale.fill_(1.0)
+            adam = self.kind == "adamw"
+            norm = self.comm.zero_step(
+                f, f.buffer("exp_avg" if adam else "momentum"),
+                f.buffer("exp_avg_sq") if adam else None, lr=lr,
+                betas=self.betas if adam else self.lion_betas, eps=self.eps,
+                weight_decay=self.wd, step=self.step_count, grad_scale=grad_scale,
+                max_norm=self.max_norm, kind=self.kind, do_reduce=not self.grads_reduced,
+                clip_out=self._scale)
+            self.grads_reduced = False
             self._side_update(side, lr, grad_scale)
             for _, p in f.side:
                 p.grad = None
             return norm
+        if f.layout != "contiguous":
+            raise RuntimeError("the segment ownership layout needs the fused optimizer step "
+                               "(peer-memory communicator, AdamW or Lion, bf16 parameters)")
         g = self._reduce_grads()
         side = self._side_grads()
         self._global_norm(g, side, grad_scale)
+        if not self.cuda and float(self._scale) == 0.0:
+            # non-finite gradient norm: skip the step (the CUDA kernels test the device scale)
+            f.zero_grads()
+            return self._norm
         if self.uses_matrices:
             # Tensors that are not Muon matrices take Lion (the reference's Muon class only
             # handles matrices: optimizer.zig:331-441), on the slice this rank owns; the

@@ -5,8 +5,10 @@ collectives and as the measured baseline) and adds:
 
 * ``alloc``: symmetric allocation for the flat parameter / gradient buffers,
 * ``zero_step``: ONE cooperative kernel per rank doing gradient reduce-scatter (peer loads),
-  global-norm clipping, AdamW on the rank's fp32 master slice, the bf16 parameter
+  global-norm clipping, AdamW or Lion on the rank's fp32 master shard, the bf16 parameter
   all-gather (peer stores) and gradient zeroing,
+* ``bucket_reduce``: the reduce-scatter of one bucket of parameters on a side stream, so it
+  overlaps the rest of the backward pass (ZeRO stage 2 and 3),
 * ``barrier`` / ``all_reduce_small`` on device flags.
 
 Launch requirement: every rank launches its kernel on its own GPU (one process per GPU);
@@ -32,11 +34,11 @@ class FusedComm(Comm):
         if not torch.cuda.is_available():
             raise RuntimeError("FusedComm needs CUDA")
         self.dev = torch.device("cuda", torch.cuda.current_device())
-        # control block: 4 flag slots x 8 ranks (u32) | 8 floats norm slots | 64 floats all-reduce
+        # control block: 8 flag slots x 8 ranks (u32) | 8 floats norm slots | 64 floats all-reduce
         self.ctrl = SymmetricBuffer(4096, group)
         self.epoch = 2
         self._buffers = [self.ctrl]
-        self._local_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self._local_acc = torch.zeros(2, dtype=torch.float32, device=self.dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=self.dev)
 
     # ---- allocation ---------------------------------------------------------------------
@@ -73,19 +75,36 @@ class FusedComm(Comm):
         return out
 
     # ---- the fused optimizer step -----------------------------------------------------------
-    def zero_step(self, flat, m, v, *, lr, betas, eps, weight_decay, step, grad_scale, max_norm):
-        """Reduce-scatter + clip + AdamW + all-gather + zero-grad for a ``FlatParams`` whose
-        parameter and gradient buffers came from ``alloc``.  Returns the gradient norm (device)."""
+    def zero_step(self, flat, m, v, *, lr, betas, eps, weight_decay, step, grad_scale, max_norm,
+                  kind: str = "adamw", do_reduce: bool = True, clip_out=None, max_ctas: int = 0):
+        """Reduce-scatter (unless the bucket reductions already ran) + clip + AdamW / Lion +
+        all-gather + zero-grad for a ``FlatParams`` whose parameter and gradient buffers came
+        from ``alloc``.  Returns the gradient norm (device); ``clip_out`` (1 float, device)
+        receives the clip scale, 0 when the step was skipped for a non-finite norm."""
         L = _lib.lib()
+        rg = flat.ranges_device()
         _lib.check(L.ceo_zero_step(
             flat.grads_symm.table(), flat.params_symm.table(), self.ctrl.table(),
-            self.ctrl.table(512), flat.master.data_ptr(), m.data_ptr(), v.data_ptr(),
-            self._local_acc.data_ptr(), self._norm.data_ptr(),
-            _lib.status_word(self.dev).data_ptr(), flat.lo, flat.shard, flat.total,
-            flat.decay_end, self.rank, self.world, self._next_epoch(), float(lr), betas[0],
-            betas[1], eps, weight_decay, step, float(grad_scale), float(max_norm),
+            self.ctrl.table(512), flat.master.data_ptr(), m.data_ptr(), _lib.ptr(v),
+            self._local_acc.data_ptr(), self._norm.data_ptr(), _lib.ptr(clip_out),
+            _lib.status_word(self.dev).data_ptr(), rg.data_ptr(), rg.shape[0], flat.total,
+            flat.decay_end, self.rank, self.world, self._next_epoch(),
+            {"adamw": 0, "lion": 1}[kind], int(do_reduce), float(lr), betas[0],
+            betas[1], eps, weight_decay, step, float(grad_scale), float(max_norm), int(max_ctas),
             _lib.stream()), "ceo_zero_step")
         return self._norm
+
+    def bucket_reduce(self, flat, r0: int, r1: int, stream, ctas: int = 24):
+        """Flag barrier + reduce-scatter of ownership ranges [r0, r1) of ``flat`` on
+        ``stream`` (a side stream that already waits for the bucket's last gradient kernel).
+        Every rank must call this for the same buckets in the same order."""
+        L = _lib.lib()
+        rg = flat.ranges_device()
+        _lib.check(L.ceo_zero_bucket_reduce(
+            flat.grads_symm.table(), self.ctrl.table(), rg.data_ptr(), r0, r1, self.rank,
+            self.world, self._next_epoch(), self._local_acc.data_ptr(),
+            _lib.status_word(self.dev).data_ptr(), ctas, stream.cuda_stream),
+            "ceo_zero_bucket_reduce")
 
     def close(self):
         torch.cuda.synchronize()

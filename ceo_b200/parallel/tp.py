@@ -73,7 +73,7 @@ class TPContext:
                                       w.stride(0), out.stride(0), int(w_mn),
                                       int(out_dtype == torch.float32), 0, 1.0, None, 0,
                                       self.ag_flags.data_ptr(), self.ag_calls, self.rank,
-                                      self.world, copy_ctas,
+                                      self.world, copy_ctas, 0, None, 0,
                                       _lib.status_word(self.dev).data_ptr(), _lib.stream()),
                    "ceo_ag_gemm_bf16")
         saved = full.clone() if keep_gathered else None

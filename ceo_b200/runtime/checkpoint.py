@@ -10,7 +10,7 @@ per-tensor SHA-256, optimizer state (fp32 master + moments, one file per rank so
 run writes in parallel), RNG, loader cursor and scheduler step, retention of the newest
 ``keep_last_n`` directories (manager.zig:382-423), asynchronous save from a host snapshot
 (``checkpoint.async_save``), ``convert`` to safetensors / torch, and re-sharding of the
-optimizer state when the world size changes between save and load.
+optimizer state when the world size or the ownership layout changes between save and load.
 """
 from __future__ import annotations
 
@@ -61,9 +61,12 @@ class CheckpointManager:
     # --------------------------------------------------------------------------- save
     def save(self, step: int, tensors: dict, metadata: dict, optimizer_state: dict | None = None,
              rng_state: bytes | None = None, config_yaml: str | None = None,
-             extra: dict | None = None) -> str:
+             extra: dict | None = None, shard_timeout: float = 600.0) -> str:
         """``tensors``: name -> tensor (reference names/orientation), written by rank 0.
-        ``optimizer_state``: name -> tensor, this rank's slice, written by every rank."""
+        ``optimizer_state``: name -> tensor, this rank's slice, written by every rank.
+        Every rank drops a ``rank{r}.done`` marker once its files are complete; rank 0 commits
+        ``metadata.json`` (and prunes older checkpoints) only after all markers are there, so a
+        directory that ``latest()`` returns always holds every shard."""
         self.wait()
         path = self.path_for(step)
         host_tensors = {k: v.detach().to("cpu", copy=True) for k, v in tensors.items()} \
@@ -79,6 +82,8 @@ class CheckpointManager:
                     name = "optimizer.bin" if self.world == 1 else f"optimizer.rank{self.rank}.bin"
                     formats.write_tensor_file(os.path.join(path, name), host_opt,
                                               formats.MAGIC_OPTIMIZER)
+                with open(os.path.join(path, f"rank{self.rank}.done"), "w") as f:
+                    f.write(str(int(step)))
                 if self.rank == 0:
                     formats.write_tensor_file(os.path.join(path, "tensors.bin"), host_tensors)
                     if rng_state is not None:
@@ -92,8 +97,19 @@ class CheckpointManager:
                           "git_revision": "0" * 40, "config_hash": "0" * 64,
                           "world_size": self.world}
                     md.update(metadata)
+                    md["has_optimizer"] = host_opt is not None
                     if extra:
                         md["extra"] = extra
+                    deadline = time.time() + shard_timeout
+                    missing = list(range(self.world))
+                    while missing:
+                        missing = [r for r in missing
+                                   if not os.path.exists(os.path.join(path, f"rank{r}.done"))]
+                        if missing and time.time() > deadline:
+                            raise TimeoutError(f"checkpoint {path}: ranks {missing} never "
+                                               "finished writing their shards")
+                        if missing:
+                            time.sleep(0.05)
                     tmp = os.path.join(path, "metadata.json.tmp")
                     with open(tmp, "w") as f:
                         json.dump(md, f, indent=1)
@@ -137,31 +153,53 @@ class CheckpointManager:
     def load_tensors(path, verify: bool = True) -> dict:
         return formats.read_tensor_file(os.path.join(path, "tensors.bin"), verify=verify)
 
-    def load_optimizer(self, path, shard_numel: int | None = None) -> dict | None:
-        """This rank's optimizer slice.  If the checkpoint was written with another world size
-        the per-rank files are concatenated and re-split evenly (flat buffers only)."""
-        single = os.path.join(path, "optimizer.bin")
-        mine = os.path.join(path, f"optimizer.rank{self.rank}.bin")
-        saved_world = self.read_metadata(path).get("world_size", 1)
-        if saved_world == self.world:
-            p = single if self.world == 1 else mine
-            if not os.path.exists(p):
-                return None
-            return formats.read_tensor_file(p, formats.MAGIC_OPTIMIZER)
-        files = [single] if saved_world == 1 else \
+    def load_optimizer(self, path, flat=None) -> dict | None:
+        """This rank's optimizer state.  Saved with the same world size and ownership layout:
+        this rank's own file.  Otherwise (``flat``: the new run's ``FlatParams``) the flat-shard
+        tensors (master weights, moments: everything as long as ``master``) are rebuilt from
+        all ranks' files through the saved ownership map and re-split; replicated entries
+        (``step_count``, ``side.*``) come from one file unchanged; ``muon.*`` entries are the
+        union over all files (the caller keeps the matrices it now owns).
+        Returns None when the checkpoint carries no optimizer state; raises
+        ``CheckpointCorrupted`` when it says it does and a shard is missing."""
+        from ..utils import errors
+        md = self.read_metadata(path)
+        saved_world = int(md.get("world_size", 1))
+        saved_layout = (md.get("extra") or {}).get("flat_layout") or \
+            {"layout": "contiguous", "world": saved_world}
+        files = [os.path.join(path, "optimizer.bin")] if saved_world == 1 else \
             [os.path.join(path, f"optimizer.rank{r}.bin") for r in range(saved_world)]
-        if not all(os.path.exists(p) for p in files):
+        present = [os.path.exists(p) for p in files]
+        if not any(present) and not md.get("has_optimizer", False):
             return None
+        same = saved_world == self.world and (
+            flat is None or saved_layout.get("layout", "contiguous") == flat.layout)
+        if same:
+            mine = files[0] if self.world == 1 else files[self.rank]
+            if not os.path.exists(mine):
+                raise errors.CheckpointCorrupted(f"{path}: optimizer shard of rank {self.rank} "
+                                                 "is missing")
+            return formats.read_tensor_file(mine, formats.MAGIC_OPTIMIZER)
+        if not all(present):
+            gone = [os.path.basename(p) for p, ok in zip(files, present) if not ok]
+            raise errors.CheckpointCorrupted(f"{path}: optimizer shards missing: {gone}")
+        if flat is None:
+            raise ValueError("re-sharding optimizer state needs the new run's FlatParams")
         parts = [formats.read_tensor_file(p, formats.MAGIC_OPTIMIZER) for p in files]
+        shard_len = parts[0]["master"].numel()
         out = {}
-        for k in parts[0]:
-            full = torch.cat([p[k].reshape(-1) for p in parts])
-            if shard_numel is None:
-                shard_numel = -(-full.numel() // self.world)
-            need = shard_numel * self.world
-            if full.numel() < need:
-                full = torch.cat([full, full.new_zeros(need - full.numel())])
-            out[k] = full[self.rank * shard_numel:(self.rank + 1) * shard_numel].clone()
+        for k, v in parts[0].items():
+            if k.startswith(("muon.", "side.")) or k == "step_count":
+                continue
+            if v.numel() == shard_len and all(k in p for p in parts):
+                out[k] = flat.reshard([p[k] for p in parts], saved_layout)
+        for k, v in parts[0].items():
+            if k == "step_count" or k.startswith("side."):
+                out[k] = v
+        for p in parts:
+            for k, v in p.items():
+                if k.startswith("muon."):
+                    out.setdefault(k, v)
         return out
 
     @staticmethod
@@ -184,7 +222,13 @@ class CheckpointManager:
         if problems:
             return problems
         try:
-            json.load(open(os.path.join(path, "metadata.json")))
+            md = json.load(open(os.path.join(path, "metadata.json")))
+            if md.get("has_optimizer"):
+                w = int(md.get("world_size", 1))
+                names = ["optimizer.bin"] if w == 1 else [f"optimizer.rank{r}.bin" for r in range(w)]
+                for n in names:
+                    if not os.path.exists(os.path.join(path, n)):
+                        problems.append(f"missing {n}")
         except Exception as e:  # noqa: BLE001
             problems.append(f"metadata.json: {e}")
         try:

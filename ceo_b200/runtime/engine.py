@@ -39,9 +39,32 @@ class TrainEngine:
         # while activations and gradients still grow quickly (first steps of a run)
         self.fp8 = self.model.enable_fp8(margin=2, dgrad=g8, wgrad=g8) \
             if cfg.training.fp8_training else None
+        # ZeRO stage (runtime.zero_stage): with the peer-memory communicator and AdamW / Lion
+        # the flat buffers use the row-sharded segment layout and stage 1, 2 or 3 as configured
+        # (parallel/fsdp.py); every other combination shards the optimizer state over
+        # contiguous slices with library collectives (stage 1 semantics).
+        fused = (self.world > 1 and getattr(comm, "fused", False)
+                 and cfg.training.optimizer in ("adamw", "lion") and self.device.type == "cuda"
+                 and self.world in (2, 4, 8))
+        stage = int(cfg.runtime.zero_stage)
+        self.zero_stage = 0 if self.world == 1 else (max(1, min(3, stage)) if fused else 1)
         self.flat = FlatParams(self.model, self.world, self.rank,
-                               alloc=getattr(comm, "alloc", None))
+                               alloc=getattr(comm, "alloc", None),
+                               layout="segment" if fused else "contiguous")
         self.optimizer = build_optimizer(self.flat, cfg.training, comm)
+        self.reducer = None
+        self.gathers = []
+        if fused and self.zero_stage >= 2:
+            from ..parallel.fsdp import BucketReducer
+            self.reducer = BucketReducer(comm, self.flat,
+                                         [f"blocks.{i}." for i in range(len(self.model.blocks))])
+            self.model.block_input_hook = self.reducer.block_hook
+        if fused and self.zero_stage >= 3:
+            if self.fp8 is not None:
+                raise ValueError("runtime.zero_stage 3 and training.fp8_training cannot be "
+                                 "combined: the fused weight gather is a bf16 GEMM")
+            from ..parallel.fsdp import attach_weight_gathers
+            self.gathers = attach_weight_gathers(self.model, comm, self.flat)
         t = cfg.training
         self.scheduler = LRScheduler(t.learning_rate, t.min_learning_rate, t.warmup_steps,
                                      t.total_steps, t.lr_schedule)
@@ -81,13 +104,22 @@ class TrainEngine:
                 tok, tgt = batches[i]
             with trace_range("forward"):
                 loss = self.model(tok, tgt, self.label_smoothing)
+            if self.reducer is not None and i == n - 1:
+                # last micro-batch: each block's gradients leave for their owners as soon as
+                # the block's backward is done
+                self.reducer.armed = True
             with trace_range("backward"):
                 loss.backward()
             total += loss.detach().float()
             self.tokens_seen += tok.numel() * self.world
         # mean over micro-batches and data-parallel ranks (the collectives sum)
         with trace_range("optimizer"):
+            if self.reducer is not None:
+                self.reducer.finish()
+                self.optimizer.grads_reduced = True
             gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.world))
+            for g in self.gathers:
+                g.pending = True
         if self.fp8 is not None:
             self.fp8.step()
         self.scheduler.step()
@@ -98,6 +130,14 @@ class TrainEngine:
             mean = mean / self.world
         return mean, gnorm
 
+    def materialize_params(self):
+        """ZeRO stage 3: completes every rank's local copy of the parameters that the last
+        optimizer step left as row shards (a collective: every rank must call it).  Needed
+        before reading parameters outside a training step (checkpoints, evaluation)."""
+        for g in self.gathers:
+            g.materialize()
+
     @torch.no_grad()
     def eval_loss(self, tok, tgt):
+        self.materialize_params()
         return self.model(self._to_device(tok), self._to_device(tgt))

@@ -97,13 +97,20 @@ class Heartbeat:
 
 
 WAIT_CODES = {1: "gemm: TMA producer waiting for a free stage", 2: "gemm: MMA waiting for data",
-              3: "gemm: MMA waiting for a free accumulator", 4: "gemm: epilogue waiting for MMA"}
+              3: "gemm: MMA waiting for a free accumulator", 4: "gemm: epilogue waiting for MMA",
+              5: "all-gather gemm: TMA producer waiting for a peer's row block to be copied in",
+              6: "gemm reduce-scatter: reduction waiting for a peer's partial tiles",
+              7: "all-gather gemm: copy CTA waiting for a bulk copy from a peer",
+              0x4546: "efla: a tile or pipeline wait ran out"}
 
 
 def describe_status(code: int) -> str:
+    """What a non-zero device status word means (the code the first bounded wait that ran out
+    wrote: csrc/gemm_tcgen05.cu ST_*, csrc/efla.cu EFLA_WAIT_STATUS, csrc/comm.cu
+    100 + 10 * barrier slot + missing rank)."""
     if code in WAIT_CODES:
         return WAIT_CODES[code]
-    if code >= 100:
+    if 100 <= code < 200:
         slot, peer = (code - 100) // 10, (code - 100) % 10
         return f"peer barrier {slot}: no signal from rank {peer}"
     return f"status {code}"

@@ -23,6 +23,7 @@ from ..utils.config import Config
 from ..utils.telemetry import HealthStatus, Telemetry
 from .checkpoint import CheckpointManager
 from .engine import TrainEngine
+from .fault import Heartbeat, KernelWatch, StepGuard
 
 
 def _git_revision() -> str:
@@ -57,6 +58,11 @@ class Trainer:
         self.ckpt = CheckpointManager(checkpoint_dir or ck.dir, ck.keep_last_n, ck.save_optimizer,
                                       ck.async_save, self.rank, self.world)
         self.data_path = data_path or cfg.data.path
+        # Failure detection: the device status word (a bounded wait in a kernel ran out) is
+        # read every metrics interval and before every checkpoint; with more than one rank a
+        # store heartbeat is consulted before each step, so a dead peer is noticed on the host
+        # before the next kernel that would wait for it is launched.
+        self.guard = self._make_guard()
         self.loader = None
         self.epoch = 0
         self.last_loss = float("nan")
@@ -64,6 +70,20 @@ class Trainer:
         dp = max(1, self.world)
         self.micro_batch = t.micro_batch_size
         self.n_micro = max(1, t.global_batch_size // (t.micro_batch_size * dp))
+
+    def _make_guard(self) -> StepGuard:
+        kw = KernelWatch() if self.device.type == "cuda" else None
+        hb = None
+        if self.world > 1:
+            try:
+                import torch.distributed as dist
+                from torch.distributed.distributed_c10d import _get_default_store
+                if dist.is_initialized():
+                    hb = Heartbeat(_get_default_store(), self.rank, self.world, interval=2.0,
+                                   timeout=120.0).start()
+            except Exception as e:  # noqa: BLE001  (no store: status-word checks only)
+                self.telemetry.log("warn", "trainer", f"heartbeat unavailable: {e}")
+        return StepGuard(hb, kw, check_every=max(1, self.cfg.telemetry.metrics_interval))
 
     # ------------------------------------------------------------------------- data
     def _open_data(self):
@@ -116,7 +136,9 @@ class Trainer:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             t0 = time.time()
+            self.guard.before_step()
             loss, gnorm = eng.train_step(batches, lr)
+            self.guard.after_step()  # status word every metrics interval (one host read)
             step = eng.step_count
             log_now = step % max(1, cfg.telemetry.metrics_interval) == 0 or step == total
             if log_now:
@@ -144,6 +166,8 @@ class Trainer:
             if cfg.checkpoint.save_interval > 0 and step % cfg.checkpoint.save_interval == 0:
                 self.save_checkpoint()
         self.ckpt.wait()
+        if self.guard.hb is not None:
+            self.guard.hb.stop()
         return {"step": eng.step_count, "loss": self.last_loss, "tokens_seen": eng.tokens_seen}
 
     def smoke_test(self, iterations: int = 3) -> list[float]:
@@ -161,6 +185,9 @@ class Trainer:
     # ------------------------------------------------------------------ checkpointing
     def save_checkpoint(self) -> str:
         eng = self.engine
+        if self.guard.kw is not None:
+            self.guard.kw.check()  # never checkpoint state a timed-out kernel may have left
+        eng.materialize_params()  # ZeRO stage 3: complete the local parameter copy first
         md = {"step": eng.step_count, "epoch": self.epoch, "tokens_seen": eng.tokens_seen,
               "loss": self.last_loss if math.isfinite(self.last_loss) else 0.0,
               "learning_rate": eng.scheduler.get_lr(), "git_revision": _git_revision(),
@@ -176,7 +203,8 @@ class Trainer:
         opt["step_count"] = torch.tensor([eng.optimizer.step_count], dtype=torch.int64)
         rng = torch.get_rng_state().numpy().tobytes()
         extra = {"scheduler": eng.scheduler.state_dict(),
-                 "loader": self.loader.state_dict() if self.loader is not None else None}
+                 "loader": self.loader.state_dict() if self.loader is not None else None,
+                 "flat_layout": eng.flat.layout_info()}
         if eng.fp8 is not None:
             extra["fp8"] = eng.fp8.state_dict()
         path = self.ckpt.save(eng.step_count, eng.model.state_dict_reference(), md, opt, rng,
@@ -196,16 +224,20 @@ class Trainer:
             raise errors.CheckpointCorrupted(str(e)) from e
         eng.model.load_reference_state(tensors)
         eng.flat.refresh_master()
-        opt = self.ckpt.load_optimizer(path, eng.flat.shard)
+        opt = self.ckpt.load_optimizer(path, eng.flat)
         if opt is not None:
             eng.flat.master.copy_(opt["master"].to(eng.flat.master))
+            # Muon matrices are owned whole, round-robin over the ranks of THIS run
+            owned = {s.name for i, s in enumerate(eng.optimizer._matrix_segs)
+                     if i % self.world == self.rank}
             for k, v in opt.items():
                 if k in ("master", "step_count"):
                     continue
                 if k.startswith("muon."):
                     _, rest = k.split(".", 1)
                     name, key = rest.rsplit(".", 1)
-                    eng.optimizer._muon_state.setdefault(name, {})[key] = v.to(eng.flat.device)
+                    if name in owned:
+                        eng.optimizer._muon_state.setdefault(name, {})[key] = v.to(eng.flat.device)
                 elif k.startswith("side."):
                     _, rest = k.split(".", 1)
                     name, key = rest.rsplit(".", 1)

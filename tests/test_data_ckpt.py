@@ -156,15 +156,106 @@ def test_tensor_file_and_checkpoint_manager(tmp_path):
         CheckpointManager.convert(m.path_for(20), tmp_path / "x", "onnx")
 
 
-def test_optimizer_resharding_on_load(tmp_path):
-    full = torch.arange(16, dtype=torch.float32)
-    for r in range(4):
+class _TinyModel(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        g = torch.Generator().manual_seed(0)
+        self.a = torch.nn.Parameter(torch.randn(16, 24, generator=g))
+        self.b = torch.nn.Parameter(torch.randn(8, 40, generator=g))
+        self.n = torch.nn.Parameter(torch.randn(24, generator=g))
+        self.s = torch.nn.Parameter(torch.ones(1))
+
+
+def _flat(world, rank, layout):
+    from ceo_b200.optim.flat import FlatParams
+    return FlatParams(_TinyModel(), world, rank, layout=layout)
+
+
+def test_segment_layout_covers_every_parameter_once():
+    from ceo_b200.optim.flat import FlatParams
+    for world in (1, 2, 4, 8):
+        owner = None
+        for rank in range(world):
+            f = FlatParams(_TinyModel(), world, rank, layout="segment")
+            if owner is None:
+                owner = torch.full((f.total,), -1, dtype=torch.int64)
+            off = 0
+            for rg in f.ranges:
+                a = rg.goff + rank * rg.len
+                assert rg.len % 4 == 0 and rg.goff % 4 == 0 and rg.loff == off
+                assert (owner[a:a + rg.len] == -1).all()
+                owner[a:a + rg.len] = rank
+                off += rg.len
+            assert off == f.shard
+            # the master shard is the owned slices of the parameters, in shard-local order
+            assert torch.equal(f.master, f.owned(f.params).float())
+        for seg in f.segments:
+            assert (owner[seg.offset:seg.offset + seg.numel] >= 0).all(), seg.name
+        # a matrix whose rows divide evenly is split by rows
+        rg = f.ranges[f.range_of("a")]
+        assert rg.names == ("a",) and rg.len == 16 * 24 // world
+    with pytest.raises(ValueError):
+        FlatParams(_TinyModel(), 3, 0, layout="segment")
+
+
+@pytest.mark.parametrize("save_layout,load_layout", [("contiguous", "contiguous"),
+                                                      ("segment", "contiguous"),
+                                                      ("contiguous", "segment"),
+                                                      ("segment", "segment")])
+def test_optimizer_resharding_on_load(tmp_path, save_layout, load_layout):
+    """Save at world 4, load at world 2: flat-shard tensors are rebuilt through the ownership
+    maps, replicated entries come back unchanged, muon entries are the union of all files."""
+    flats = [_flat(4, r, save_layout) for r in range(4)]
+    total = flats[0].total
+    truth = torch.arange(total, dtype=torch.float32) + 1.0
+    for r in reversed(range(4)):  # rank 0 last: it waits for the other ranks' markers
+        f = flats[r]
+        opt = {"master": f.owned(truth), "exp_avg": f.owned(truth * 2),
+               "step_count": torch.tensor([5], dtype=torch.int64),
+               "side.s.m": torch.tensor([0.25]),
+               f"muon.mat{r}.momentum": torch.full((3,), float(r))}
         m = CheckpointManager(tmp_path / "ck", rank=r, world=4)
-        m.save(5, {"w": torch.zeros(1)} if r == 0 else {}, {}, {"master": full[r * 4:(r + 1) * 4]})
+        m.save(5, {"w": torch.zeros(1)} if r == 0 else {}, {}, opt,
+               extra={"flat_layout": f.layout_info()}, shard_timeout=5.0)
+    assert CheckpointManager.validate(tmp_path / "ck" / "step_00000005") == []
     for r in range(2):
+        f2 = _flat(2, r, load_layout)
         m2 = CheckpointManager(tmp_path / "ck", rank=r, world=2)
-        got = m2.load_optimizer(m2.path_for(5), 8)["master"]
-        assert torch.equal(got, full[r * 8:(r + 1) * 8])
+        got = m2.load_optimizer(m2.path_for(5), f2)
+        assert got["master"].shape == (f2.shard,)
+        # every element a parameter occupies comes back where the new map puts it
+        want = f2.owned(torch.cat([truth, torch.zeros(max(0, f2.total - total))])[:f2.total])
+        covered = f2.owned(_covered_mask(f2))
+        assert torch.equal(got["master"][covered], want[covered])
+        assert torch.equal(got["exp_avg"][covered], 2 * want[covered])
+        assert got["step_count"].tolist() == [5] and got["side.s.m"].tolist() == [0.25]
+        assert {k for k in got if k.startswith("muon.")} == \
+            {f"muon.mat{i}.momentum" for i in range(4)}
+
+
+def _covered_mask(f):
+    m = torch.zeros(f.total, dtype=torch.bool)
+    for seg in f.segments:
+        m[seg.offset:seg.offset + seg.numel] = True
+    return m
+
+
+def test_missing_optimizer_shard_is_reported(tmp_path):
+    from ceo_b200.utils import errors
+    for r in reversed(range(2)):
+        m = CheckpointManager(tmp_path / "ck", rank=r, world=2)
+        m.save(3, {"w": torch.zeros(1)} if r == 0 else {}, {}, {"master": torch.zeros(4)},
+               shard_timeout=5.0)
+    path = m.path_for(3)
+    (tmp_path / "ck" / "step_00000003" / "optimizer.rank1.bin").unlink()
+    assert any("optimizer.rank1.bin" in p for p in CheckpointManager.validate(path))
+    with pytest.raises(errors.CheckpointCorrupted):
+        CheckpointManager(tmp_path / "ck", rank=1, world=2).load_optimizer(path)
+    # rank 0 never commits a checkpoint whose other shards did not arrive
+    m0 = CheckpointManager(tmp_path / "ck2", rank=0, world=2)
+    with pytest.raises(TimeoutError):
+        m0.save(4, {"w": torch.zeros(1)}, {}, {"master": torch.zeros(4)}, shard_timeout=0.3)
+    assert m0.latest() is None
 
 
 def test_telemetry_files_and_prometheus(tmp_path):

@@ -33,31 +33,42 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+def _nranks():
+    """All visible GPUs, rounded down to 2, 4 or 8."""
+    n = _ngpu()
+    return 8 if n >= 8 else (4 if n >= 4 else 2)
+
+
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_zero_step_matches_nccl():
-    n = 4 if _ngpu() >= 4 else 2
-    out = _run("fused_vs_nccl", n)
+    out = _run("fused_vs_nccl", _nranks())
     assert "OK fused_vs_nccl" in out
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_ag_gemm_and_gemm_rs():
-    n = 4 if _ngpu() >= 4 else 2
-    out = _run("tp_fused", n)
+    out = _run("tp_fused", _nranks())
     assert "OK tp_fused" in out
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_context_parallel_efla_matches_single_gpu():
-    n = 4 if _ngpu() >= 4 else 2
-    out = _run("cp", n)
+    out = _run("cp", _nranks())
     assert "OK cp" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_zero_stages_match_library_composition():
+    out = _run("zero_stages", _nranks())
+    assert "OK zero_stages" in out
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("what", ["tp_model", "cp_model"])
 def test_parallel_model_matches_single_gpu(what):
-    out = _run(what, 2)
+    # tensor parallel over at most 4 ranks (the model has 4 heads), context parallel over all
+    n = min(4, _nranks()) if what == "tp_model" else _nranks()
+    out = _run(what, n)
     assert f"OK {what}" in out
 
 

@@ -221,3 +221,31 @@ def test_bounds_checked_build_is_clean_and_its_recorder_works():
     assert n == 5 and site == 199 and 100 <= idx < 105 and extent == 100
     assert out["after_reset"] == [0, 0, 0, 0]
     assert out["sum"] == 100.0 + 5.0             # the five redirected reads saw element 0
+
+
+@pytest.mark.parametrize("kind", ["adamw", "lion", "lion_muon"])
+def test_non_finite_gradient_skips_the_step(kind):
+    """One inf in the gradients: parameters, master weights and moments stay bit-identical,
+    the gradients are dropped, and the next (finite) step works."""
+    model = _model()
+    flat = FlatParams(model)
+    opt = ShardedOptimizer(flat, kind, weight_decay=0.1, max_grad_norm=1.0)
+    flat.grads.copy_(torch.randn(flat.total, device=DEV) * 0.01)
+    opt.step(1e-2)  # a normal step first, so that the moments are not all zero
+    snap = {k: v.clone() for k, v in flat.optimizer_state().items()}
+    muon = {n: {k: v.clone() for k, v in st.items()} for n, st in opt._muon_state.items()}
+    params = flat.params.clone()
+    flat.grads.copy_(torch.randn(flat.total, device=DEV) * 0.01)
+    flat.grads[17] = float("inf")
+    gn = opt.step(1e-2)
+    assert not torch.isfinite(gn).item()
+    assert torch.equal(flat.params, params)
+    for k, v in flat.optimizer_state().items():
+        assert torch.equal(v, snap[k]), k
+    for n, st in opt._muon_state.items():
+        for k, v in st.items():
+            assert torch.equal(v, muon[n][k]), (n, k)
+    assert float(flat.grads.abs().max()) == 0.0
+    flat.grads.copy_(torch.randn(flat.total, device=DEV) * 0.01)
+    opt.step(1e-2)
+    assert not torch.equal(flat.params, params) and torch.isfinite(flat.master).all()

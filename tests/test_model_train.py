@@ -119,6 +119,32 @@ def test_flat_adamw_matches_torch_adamw():
     assert float(flat.grads.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("kind", ["adamw", "lion", "lion_muon"])
+def test_non_finite_gradient_skips_the_step_cpu(kind):
+    torch.manual_seed(0)
+    lin = torch.nn.Sequential(torch.nn.Linear(8, 16, bias=False), torch.nn.Linear(16, 4, bias=False))
+    flat = FlatParams(lin)
+    opt = ShardedOptimizer(flat, kind, weight_decay=0.1, max_grad_norm=1.0)
+    flat.grads.copy_(torch.randn(flat.total) * 0.01)
+    opt.step(1e-2)
+    snap = {k: v.clone() for k, v in flat.optimizer_state().items()}
+    muon = {n: {k: v.clone() for k, v in st.items()} for n, st in opt._muon_state.items()}
+    params = flat.params.clone()
+    flat.grads.copy_(torch.randn(flat.total) * 0.01)
+    flat.grads[3] = float("nan")
+    gn = opt.step(1e-2)
+    assert not math.isfinite(float(gn))
+    assert torch.equal(flat.params, params) and float(flat.grads.abs().max()) == 0.0
+    for k, v in flat.optimizer_state().items():
+        assert torch.equal(v, snap[k]), k
+    for n, st in opt._muon_state.items():
+        for k, v in st.items():
+            assert torch.equal(v, muon[n][k]), (n, k)
+    flat.grads.copy_(torch.randn(flat.total) * 0.01)
+    opt.step(1e-2)
+    assert not torch.equal(flat.params, params) and torch.isfinite(flat.master).all()
+
+
 def test_muon_orthogonalises_and_lion_sign():
     torch.manual_seed(1)
     g = torch.randn(12, 20)
