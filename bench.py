@@ -18,7 +18,13 @@ memory (copied host->device inside the step) and the loss read back to the host 
 step.  Every micro-batch streams far more than L2 (126 MB) through the device, so no
 explicit L2 flush is needed between timed iterations.
 
-``--impl reference`` reports why the reference cannot be run.
+``--impl reference`` times the reference's own CUDA kernels (``baseline/ref_step_bench.py``:
+a kernel-sum floor of its step; the reference itself cannot run a training step) and prints
+the same JSON line with ``"impl": "reference"``, or its ``unavailable`` line when the
+reference's kernel library has not been built.
+
+Every step reads fresh synthetic batches (the token stream never repeats within a run), so
+``final_loss`` is a training loss, not the memorisation of one batch.
 """
 from __future__ import annotations
 
@@ -33,11 +39,6 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-
-REFERENCE_UNAVAILABLE = (
-    "reference is a Zig project with no setup.py/pyproject.toml: `pip install --no-index "
-    "--target baseline/_ref <reference tree>` answers 'not installable', Zig is not in the "
-    "image, and its model forward rejects non-CPU devices (src/model/model.zig:378-380)")
 
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -120,10 +121,25 @@ def main(argv=None):
     ap.add_argument("--tp", type=int, default=0,
                     help="tensor-parallel size (0: 1 for the default config, else the config's)")
     ap.add_argument("--cp", type=int, default=0, help="context-parallel size (0: the config's)")
+    ap.add_argument("--zero-stage", type=int, default=-1,
+                    help="ZeRO stage of the data-parallel replicas (1: one fused reduce-scatter + "
+                         "update + all-gather kernel after backward; 2: bucket reduce-scatter "
+                         "overlapped with backward; 3: + weight all-gather inside the consuming "
+                         "GEMMs; -1: the config's runtime.zero_stage)")
     a = ap.parse_args(argv)
 
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        # the reference's own kernels only: nothing of this framework's ops, models or engine
+        from baseline import ref_step_bench
+        try:
+            rec = ref_step_bench.run(a.config, a.gpus, a.steps, a.warmup)
+        except Exception as e:  # noqa: BLE001
+            rec = ref_step_bench.unavailable(f"reference kernels failed: {type(e).__name__}: {e}"
+                                             .replace("\n", " ")[:300])
+            if int(os.environ.get("RANK", "0")) != 0:
+                rec = {}
+        if rec:
+            print(json.dumps(rec))
         return 0
 
     import torch
@@ -166,6 +182,10 @@ def main(argv=None):
     mbs = a.micro_batch or cfg.training.micro_batch_size
     cfg.training.micro_batch_size = mbs
     cfg.training.fp8_training = bool(a.fp8 or a.fp8_dgrad or a.fp8_all)
+    if a.zero_stage >= 0:
+        cfg.runtime.zero_stage = a.zero_stage
+    if cfg.training.fp8_training and cfg.runtime.zero_stage >= 3:
+        cfg.runtime.zero_stage = 2  # the fused weight gather is a bf16 GEMM
     if world % (tp * cp) or gbs % (mbs * dp):
         raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x dp {dp}")
     n_micro = gbs // (mbs * dp)
@@ -192,17 +212,26 @@ def main(argv=None):
         data_rank = rank
     data = SyntheticTokens(cfg.model.vocab_size, cfg.data.synthetic.kind or "zipf",
                            cfg.data.synthetic.s, cfg.data.synthetic.seed, data_rank)
-    host = [data.batch(mbs, seq, pin=True) for _ in range(n_micro)]
-    on_dev = [(t.to(dev), g.to(dev)) for t, g in host]
     lr = cfg.training.learning_rate
+
+    def fresh(n_steps, on_device):
+        """n_steps x n_micro new micro-batches from the token stream (drawn before the timed
+        region; pinned host memory, or already on the device)."""
+        out = []
+        for _ in range(n_steps):
+            mb = [data.batch(mbs, seq, pin=True) for _ in range(n_micro)]
+            out.append([(t.to(dev), g.to(dev)) for t, g in mb] if on_device else mb)
+        return out
 
     def sync():
         if comm is not None:
             comm.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(a.warmup):
-        eng.train_step(on_dev, lr)
+    for b in fresh(a.warmup, True):
+        eng.train_step(b, lr)
+    dev_batches = fresh(a.steps, True)
+    host_batches = fresh(0 if a.skip_e2e else a.steps, False)
     sync()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -212,8 +241,8 @@ def main(argv=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
     e0.record()
-    for _ in range(a.steps):
-        loss, gnorm = eng.train_step(on_dev, lr)
+    for b in dev_batches:
+        loss, gnorm = eng.train_step(b, lr)
     e1.record()
     sync()
     launches = _lib.launch_count - l0
@@ -226,8 +255,8 @@ def main(argv=None):
         e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sync()
         e2.record()
-        for _ in range(a.steps):
-            loss, gnorm = eng.train_step(host, lr)
+        for b in host_batches:
+            loss, gnorm = eng.train_step(b, lr)
             last_loss = loss.item()  # device -> host read of the step's result
         e3.record()
         sync()
@@ -235,10 +264,17 @@ def main(argv=None):
         ms2 = comm.max_over_ranks(ms2) if comm is not None else ms2
         e2e = {"value": tokens_per_step * a.steps / (ms2 * 1e-3), "unit": "tokens/s",
                "ms_per_step": ms2 / a.steps,
-               "h2d_bytes_per_step": sum(t.numel() * 8 + g.numel() * 8 for t, g in host) * world,
+               "h2d_bytes_per_step": sum(t.numel() * t.element_size() + g.numel() * g.element_size()
+                                         for t, g in host_batches[0]) * world,
                "d2h_bytes_per_step": 4 * world}
     clocks = sampler.stop() if rank == 0 else None
     status = _lib.read_status(dev)
+    # what is partitioned over the data-parallel replicas: 0 nothing (one GPU), 1 optimizer
+    # state, 2 + gradients (reduced bucket by bucket during backward), 3 + parameters (FSDP)
+    zero_stage = getattr(eng, "zero_stage", 1 if dp > 1 else 0)
+    shard = {0: f"dp{dp}", 1: f"zero1-dp{dp}", 2: f"zero2-dp{dp}", 3: f"fsdp{dp}"}[zero_stage]
+    parallelism = shard if tp * cp == 1 else f"tp{tp}xcp{cp}x{shard}"
+    peak_mem = torch.cuda.max_memory_allocated(dev)
     if rank == 0:
         value = tokens_per_step * a.steps / (ms * 1e-3)
         flops = eng.model.flops_per_token(seq) * value
@@ -254,14 +290,15 @@ def main(argv=None):
             "config": {"model": cfg.model.name, "global_batch": gbs, "seq_len": seq,
                        "tokens_per_step": tokens_per_step, "micro_batch": mbs,
                        "grad_accum_steps": n_micro,
-                       "parallelism": (f"fsdp{world}" if tp * cp == 1 else
-                                       f"tp{tp}xcp{cp}xfsdp{dp}"),
+                       "parallelism": parallelism,
+                       "zero_stage": zero_stage,
                        "optimizer": cfg.training.optimizer,
                        "collectives": type(comm).__name__ if comm else "none",
                        "l2": "inputs larger than L2 (each micro-batch streams >1 GB)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "model_tflops_per_gpu": flops / world / 1e12, "final_loss": last_loss,
             "wait_status": status, "impl": "ours",
+            "torch_peak_alloc_gb": round(peak_mem / 2**30, 2),
         }
         print(json.dumps(out))
     if comm is not None:

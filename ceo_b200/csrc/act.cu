@@ -57,6 +57,40 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __r
   }
 }
 
+// ---------------------------------------------------------------------------- dropout
+// y = x * keep / (1 - p) with keep decided by a stateless hash of (element index, seed), so
+// the backward pass re-creates the mask from the seed instead of storing it: apply the same
+// call to dy.  Counterpart of the reference's CPU Dropout layer (src/nn/layers.zig:461-503),
+// which draws from a host RNG and keeps a mask tensor.
+__device__ __forceinline__ unsigned dropout_hash(unsigned long long idx, unsigned seed) {
+  unsigned x = static_cast<unsigned>(idx) ^ seed ^ (static_cast<unsigned>(idx >> 32) * 0x9E3779B9u);
+  x ^= x >> 16; x *= 0x7feb352du;
+  x ^= x >> 15; x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+__global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n,
+                               float p, float scale, unsigned seed) {
+  const long long n8 = n >> 3;
+  const unsigned thresh = static_cast<unsigned>(p * 16777216.f);  // keep iff top 24 bits >= p
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      f[j] = (dropout_hash(static_cast<unsigned long long>(i) * 8 + j, seed) >> 8) >= thresh
+                 ? f[j] * scale : 0.f;
+    reinterpret_cast<uint4*>(y)[i] = pack8(f);
+  }
+  // tail (n not a multiple of 8)
+  for (long long i = (n8 << 3) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool keep = (dropout_hash(static_cast<unsigned long long>(i), seed) >> 8) >= thresh;
+    y[i] = __float2bfloat16(keep ? __bfloat162float(x[i]) * scale : 0.f);
+  }
+}
+
 // mode 0: tanh GELU, 1: erf GELU, 2: SiLU, 3: ReLU
 __device__ __forceinline__ float act_f(float x, int mode) {
   if (mode == 0) {
@@ -160,6 +194,16 @@ extern "C" int ceo_act_bwd(const void* dy, const void* x, void* dx, long long n,
       mode);
   return static_cast<int>(cudaGetLastError());
 }
+extern "C" int ceo_dropout(const void* x, void* y, long long n, float p, unsigned int seed,
+                           cudaStream_t stream) {
+  if (n <= 0 || !(p >= 0.f) || p >= 1.f ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15))
+    return -5;
+  dropout_kernel<<<grid_for(n, 256 * 8 * 2, 148 * 8), 256, 0, stream>>>(
+      static_cast<const bf16*>(x), static_cast<bf16*>(y), n, p, 1.f / (1.f - p), seed);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int ceo_softmax_fwd(const float* x, float* y, int rows, int n, cudaStream_t stream) {
   if (rows <= 0 || n <= 0) return -5;
   softmax_fwd_kernel<<<rows < 65535 ? rows : 65535, 256, 0, stream>>>(x, y, rows, n);

@@ -106,6 +106,10 @@ int ceo_act_fwd(const void* x, void* y, long long n, int mode, cudaStream_t stre
 int ceo_act_bwd(const void* dy, const void* x, void* dx, long long n, int mode,
                 cudaStream_t stream);
 int ceo_softmax_fwd(const float* x, float* y, int rows, int n, cudaStream_t stream);
+/* Inverted dropout on bf16: y = keep ? x / (1 - p) : 0, keep from a stateless hash of
+ * (element index, seed); the backward pass is the same call on dy with the same seed. */
+int ceo_dropout(const void* x, void* y, long long n, float p, unsigned int seed,
+                cudaStream_t stream);
 
 /* ---- causal depthwise short convolution: x,y (B,T,D) bf16, weight (D,Wn) bf16 ------- */
 int ceo_shortconv_fwd(const void* x, const void* weight, void* y, int B, int T, int D, int Wn,

@@ -203,6 +203,7 @@ class Prefetcher:
 
     def __init__(self, loader: DataLoader, depth: int = 2):
         self.loader = loader
+        self._consumed = loader.state_dict()
         self.q: queue.Queue = queue.Queue(maxsize=max(1, depth))
         self._stop = False
         self.t = threading.Thread(target=self._run, daemon=True)
@@ -212,7 +213,9 @@ class Prefetcher:
         try:
             while not self._stop:
                 b = self.loader.next()
-                self.q.put(b)
+                # the loader's cursor right after this batch travels with it, so a checkpoint
+                # records what has been CONSUMED, not how far the thread has read ahead
+                self.q.put((b, self.loader.state_dict()))
                 if b is None:
                     return
         except BaseException as e:  # noqa: BLE001
@@ -222,7 +225,12 @@ class Prefetcher:
         item = self.q.get()
         if isinstance(item, BaseException):
             raise item
-        return item
+        b, self._consumed = item
+        return b
+
+    def state_dict(self):
+        """The loader state after the last batch ``next`` handed out."""
+        return getattr(self, "_consumed", None) or self.loader.state_dict()
 
     def close(self):
         self._stop = True

@@ -157,17 +157,24 @@ class Block(nn.Module):
         self.prism = PrismLayer(cfg, device, dtype, gen, std) if cfg.prism.enabled else None
         self.ln2 = Norm(cfg.hidden_dim, cfg.norm_type, device, dtype)
         self.mlp = MLP(cfg, device, dtype, gen, std)
+        self.dropout = float(cfg.dropout)  # on both branch outputs, training mode only
 
     def forward(self, h, state=None, resets=None):
+        drop = self.dropout if self.training else 0.0
         n1, h = self.ln1(h, skip=True)
         o, s_final = self.efla(n1, h, state, resets)
         if self.prism is not None:
             a = _lin(self.efla, "o", o, self.efla.w_o)
-            h = h + self.prism(n1, a)
+            h = h + K.dropout(self.prism(n1, a), drop)
+        elif drop > 0.0:
+            h = h + K.dropout(_lin(self.efla, "o", o, self.efla.w_o), drop)
         else:
-            h = _lin(self.efla, "o", o, self.efla.w_o, h)
+            h = _lin(self.efla, "o", o, self.efla.w_o, h)  # residual add in the GEMM epilogue
         n2, h = self.ln2(h, skip=True)
-        h = self.mlp(n2, h)
+        if drop > 0.0:
+            h = h + K.dropout(self.mlp(n2, None), drop)
+        else:
+            h = self.mlp(n2, h)
         return h, s_final
 
     def decode_step(self, h, state):
@@ -263,7 +270,11 @@ class EflaLM(nn.Module):
         for blk, st in zip(self.blocks, states):
             h = blk.decode_step(h, st)
         hn = self.final_norm(h)
-        return hn.float() @ self.head_weight().float().t()
+        w = self.head_weight()
+        if hn.is_cuda:
+            from ..ops.matmul import gemm
+            return gemm(hn, w, out_dtype=torch.float32)   # (B, V) logits on the tcgen05 GEMM
+        return hn.float() @ w.float().t()
 
     # ------------------------------------------------------------ checkpoint name mapping
     def count_parameters(self) -> int:

@@ -214,15 +214,74 @@ def activation(x, kind: str = "gelu"):
     return _ActFn.apply(x, ACT_MODES[kind])
 
 
-def softmax(x: torch.Tensor) -> torch.Tensor:
-    """Softmax over the last dimension (fp32)."""
+def softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """Softmax over dimension ``dim`` (fp32), as the reference's ``Softmax(dim)`` layer
+    (src/nn/layers.zig:386-458).  The kernel reduces rows; another dimension is moved last."""
     if not x.is_cuda:
-        return torch.softmax(x.float(), dim=-1)
+        return torch.softmax(x.float(), dim=dim)
+    dim = dim % x.dim()
+    if dim != x.dim() - 1:
+        return softmax(x.movedim(dim, -1), -1).movedim(-1, dim)
     x2 = x.float().reshape(-1, x.shape[-1]).contiguous()
     y = torch.empty_like(x2)
     _lib.check(_lib.lib().ceo_softmax_fwd(x2.data_ptr(), y.data_ptr(), x2.shape[0], x2.shape[1],
                                           _lib.stream()), "ceo_softmax_fwd")
     return y.view(x.shape)
+
+
+# ---------------------------------------------------------------------------- dropout
+def dropout_keep_mask(numel: int, p: float, seed: int, device="cpu") -> torch.Tensor:
+    """The keep mask of ``ceo_dropout`` (the same integer hash in PyTorch): element i is kept
+    iff the top 24 bits of hash(i, seed) are >= p * 2^24."""
+    M = 0xFFFFFFFF
+    idx = torch.arange(numel, dtype=torch.int64, device=device)
+    x = ((idx & M) ^ (seed & M) ^ (((idx >> 32) * 0x9E3779B9) & M)) & M
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & M
+    x = x ^ (x >> 15)
+    x = (x * 0x846CA68B) & M
+    x = x ^ (x >> 16)
+    return (x >> 8) >= int(p * 16777216.0)
+
+
+class _DropoutFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, seed):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _lib.check(_lib.lib().ceo_dropout(xc.data_ptr(), y.data_ptr(), xc.numel(), float(p),
+                                          int(seed) & 0xFFFFFFFF, _lib.stream()), "ceo_dropout")
+        ctx.p, ctx.seed = p, seed
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dyc = dy.contiguous()
+        dx = torch.empty_like(dyc)
+        _lib.check(_lib.lib().ceo_dropout(dyc.data_ptr(), dx.data_ptr(), dyc.numel(),
+                                          float(ctx.p), int(ctx.seed) & 0xFFFFFFFF, _lib.stream()),
+                   "ceo_dropout")
+        return dx, None, None
+
+
+_dropout_calls = [0]
+
+
+def dropout(x: torch.Tensor, p: float, training: bool = True, seed: int | None = None):
+    """Inverted dropout (reference: ``Dropout`` in src/nn/layers.zig:461-503; ``model.dropout``,
+    src/util/config.zig:92,118).  The mask is a stateless hash of (element index, seed): nothing
+    is stored for the backward pass.  ``seed`` defaults to the torch seed plus a call counter."""
+    if not training or p <= 0.0:
+        return x
+    if not 0.0 <= p < 1.0:
+        raise ValueError(f"dropout probability {p} is not in [0, 1)")
+    if seed is None:
+        _dropout_calls[0] += 1
+        seed = (torch.initial_seed() * 0x9E3779B1 + _dropout_calls[0] * 0x85EBCA6B) & 0xFFFFFFFF
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        keep = dropout_keep_mask(x.numel(), p, seed, x.device).view(x.shape)
+        return torch.where(keep, x / (1.0 - p), torch.zeros_like(x))
+    return _DropoutFn.apply(x, p, seed)
 
 
 # -------------------------------------------------------------------------- embedding

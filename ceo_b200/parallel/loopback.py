@@ -35,7 +35,8 @@ class LoopbackPeers:
 
     def __init__(self, world: int = 2, device=None):
         self.world = world
-        self.dev = torch.device(device or ("cuda", torch.cuda.current_device()))
+        self.dev = torch.device(device) if device is not None else \
+            torch.device("cuda", torch.cuda.current_device())
         # per pretend rank: 8 flag slots x 8 words, then 8 floats of norm slots, 64 of staging
         self.ctrl = [torch.zeros(1024, dtype=torch.int32, device=self.dev) for _ in range(world)]
         self.epoch = 2

@@ -81,7 +81,9 @@ class TrainEngine:
 
     def train_step(self, batches, lr: float | None = None):
         """``batches``: a list (one entry per micro-batch) of (tokens, targets) integer tensors
-        of shape (mb, T), on the host (pinned) or already on the device.
+        of shape (mb, T), on the host (pinned) or already on the device; an optional third
+        entry ``resets`` (mb, T/64, bool) marks the chunks that start a new document of a
+        packed batch (``data.dataset.packed_batch``).
         Returns (mean loss, gradient norm) as device scalars."""
         n = len(batches)
         if lr is None:
@@ -94,16 +96,17 @@ class TrainEngine:
         for i in range(n):
             if self._copy_stream is not None:
                 torch.cuda.current_stream().wait_stream(self._copy_stream)
-                tok, tgt = nxt
-                tok.record_stream(torch.cuda.current_stream())
-                tgt.record_stream(torch.cuda.current_stream())
+                tok, tgt, *rest = nxt
+                for x in nxt:
+                    x.record_stream(torch.cuda.current_stream())
                 if i + 1 < n:
                     with torch.cuda.stream(self._copy_stream):
                         nxt = tuple(self._to_device(x) for x in batches[i + 1])
             else:
-                tok, tgt = batches[i]
+                tok, tgt, *rest = batches[i]
+            resets = rest[0] if rest else None
             with trace_range("forward"):
-                loss = self.model(tok, tgt, self.label_smoothing)
+                loss = self.model(tok, tgt, self.label_smoothing, resets=resets)
             if self.reducer is not None and i == n - 1:
                 # last micro-batch: each block's gradients leave for their owners as soon as
                 # the block's backward is done

@@ -16,7 +16,8 @@ import time
 
 import torch
 
-from ..data.dataset import BinaryDataset, DataLoader, Prefetcher
+from ..data.dataset import (BinaryDataset, DataLoader, Prefetcher, pack_sequences,
+                            packed_batch)
 from ..data.synthetic import SyntheticTokens
 from ..utils import errors
 from ..utils.config import Config
@@ -64,12 +65,21 @@ class Trainer:
         # before the next kernel that would wait for it is launched.
         self.guard = self._make_guard()
         self.loader = None
+        self._prefetch = None
+        self._packing = False
         self.epoch = 0
         self.last_loss = float("nan")
         t = cfg.training
         dp = max(1, self.world)
         self.micro_batch = t.micro_batch_size
         self.n_micro = max(1, t.global_batch_size // (t.micro_batch_size * dp))
+        # training.gradient_accumulation_steps (src/util/config.zig:407) must agree with
+        # global / (micro x data-parallel ranks), which is what the step runs
+        gas = int(getattr(t, "gradient_accumulation_steps", 0) or 0)
+        if gas not in (0, self.n_micro):
+            self.telemetry.log("warn", "config", f"gradient_accumulation_steps = {gas} does not "
+                               f"match global_batch_size / (micro_batch_size x {dp} ranks) = "
+                               f"{self.n_micro}; running {self.n_micro} micro-batches per step")
 
     def _make_guard(self) -> StepGuard:
         kw = KernelWatch() if self.device.type == "cuda" else None
@@ -101,6 +111,59 @@ class Trainer:
             raise errors.DataExhausted(
                 f"{self.data_path}: not enough tokens for one batch of {self.micro_batch} x "
                 f"{d.seq_len + 1}")
+        # data.pack_sequences (src/util/config.zig:567): windows are cut at the end-of-document
+        # token and the documents packed on 64-token boundaries, with the recurrent state
+        # reset at every document start; needs a sequence length that is a multiple of 64
+        self._packing = bool(d.pack_sequences) and d.eos_token_id >= 0 and d.seq_len % 64 == 0
+        self._packs = []
+
+    def _loader_state(self):
+        if self.loader is None:
+            return None
+        return self._prefetch.state_dict() if self._prefetch is not None else \
+            self.loader.state_dict()
+
+    def _close_data(self):
+        if self._prefetch is not None:
+            self._prefetch.close()
+            self._prefetch = None
+
+    def _next_window_batch(self):
+        """The next (inputs, targets) window batch, read ``data.prefetch_factor`` batches ahead
+        on a background thread (src/util/config.zig:565); rolls over to the next epoch."""
+        while True:
+            if self.cfg.data.prefetch_factor > 0:
+                if self._prefetch is None:
+                    self._prefetch = Prefetcher(self.loader, self.cfg.data.prefetch_factor)
+                b = self._prefetch.next()
+            else:
+                b = self.loader.next()
+            if b is not None:
+                return b
+            self._close_data()
+            self.loader.reset()
+            self.epoch += 1
+
+    def _next_packed(self):
+        """One packed micro-batch (tokens, targets, resets) of ``micro_batch`` rows."""
+        d = self.cfg.data
+        while len(self._packs) < self.micro_batch:
+            b = self._next_window_batch()
+            full = torch.cat([b.input, b.target[:, -1:]], dim=1).numpy()
+            docs = []
+            for row in full:
+                cuts = (row == d.eos_token_id).nonzero()[0] + 1
+                lo = 0
+                for c in list(cuts) + [len(row)]:
+                    if c > lo:
+                        docs.append(row[lo:c])
+                    lo = c
+            self._packs += pack_sequences(docs, d.seq_len + 1, align=64)
+        take, self._packs = self._packs[:self.micro_batch], self._packs[self.micro_batch:]
+        tok, tgt, resets = packed_batch(take, 64)
+        if self.device.type == "cuda":
+            tok, tgt, resets = tok.pin_memory(), tgt.pin_memory(), resets.pin_memory()
+        return tok, tgt, resets
 
     def _next_micro_batches(self):
         out = []
@@ -110,12 +173,11 @@ class Trainer:
                                              pin=self.device.type == "cuda"))
             return out
         while len(out) < self.n_micro:
-            b = self.loader.next()
-            if b is None:
-                self.loader.reset()
-                self.epoch += 1
-                continue
-            out.append((b.input, b.target))
+            if self._packing:
+                out.append(self._next_packed())
+            else:
+                b = self._next_window_batch()
+                out.append((b.input, b.target))
         return out
 
     # ------------------------------------------------------------------------- loop
@@ -166,6 +228,7 @@ class Trainer:
             if cfg.checkpoint.save_interval > 0 and step % cfg.checkpoint.save_interval == 0:
                 self.save_checkpoint()
         self.ckpt.wait()
+        self._close_data()
         if self.guard.hb is not None:
             self.guard.hb.stop()
         return {"step": eng.step_count, "loss": self.last_loss, "tokens_seen": eng.tokens_seen}
@@ -203,7 +266,7 @@ class Trainer:
         opt["step_count"] = torch.tensor([eng.optimizer.step_count], dtype=torch.int64)
         rng = torch.get_rng_state().numpy().tobytes()
         extra = {"scheduler": eng.scheduler.state_dict(),
-                 "loader": self.loader.state_dict() if self.loader is not None else None,
+                 "loader": self._loader_state(),
                  "flat_layout": eng.flat.layout_info()}
         if eng.fp8 is not None:
             extra["fp8"] = eng.fp8.state_dict()

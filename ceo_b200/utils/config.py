@@ -260,6 +260,9 @@ class DataConfig:  # config.zig:541-587
     prefetch_factor: int = 2
     num_workers: int = 4
     pack_sequences: bool = True
+    # extension: the end-of-document token that pack_sequences cuts the stream at (the
+    # tokenizer's <eos> is 259); -1 = the stream has no document marks, nothing to pack
+    eos_token_id: int = -1
     synthetic: SyntheticConfig = field(default_factory=SyntheticConfig)
 
 

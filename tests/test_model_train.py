@@ -316,3 +316,141 @@ def test_cloud_launcher_commands():
     assert mt.command_for("smoke_test")[-1] == "smoke-test" and mt.GPU_TRAIN == "B200:8"
     with pytest.raises(ValueError):
         mt.command_for("fly")
+
+
+class _FakeVolume:
+    """In-memory stand-in with Modal's volume calls (batch_upload / read_file / listdir)."""
+
+    def __init__(self):
+        self.files = {}
+
+    class _Batch:
+        def __init__(self, vol):
+            self.vol = vol
+
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+        def put_file(self, src, dst):
+            self.vol.files[dst] = open(src, "rb").read()
+
+        def put_directory(self, src, dst):
+            for base, _, names in os.walk(src):
+                for n in names:
+                    full = os.path.join(base, n)
+                    self.vol.files[dst + "/" + os.path.relpath(full, src)] = open(full, "rb").read()
+
+    def batch_upload(self, force=False):
+        return self._Batch(self)
+
+    def read_file(self, path):
+        data = self.files[path]
+        return (data[i:i + 5] for i in range(0, len(data), 5))
+
+    def listdir(self, root, recursive=True):
+        class E:
+            def __init__(self, path, kind):
+                self.path, self.type = path, kind
+        dirs = {os.path.dirname(p) for p in self.files if p.startswith(root + "/")}
+        return [E(d, "DIRECTORY") for d in sorted(dirs)] + \
+            [E(p, "FILE") for p in sorted(self.files) if p.startswith(root + "/")]
+
+
+def test_cloud_volume_transfers(tmp_path):
+    sys.path.insert(0, ROOT)
+    from cloud import modal_train as mt
+    src = tmp_path / "ck" / "step_00000004"
+    (src / "sub").mkdir(parents=True)
+    (src / "metadata.json").write_text("{}")
+    (src / "sub" / "tensors.bin").write_bytes(bytes(range(40)))
+    vol = _FakeVolume()
+    assert mt.transfer("upload-checkpoint", local_path=str(src), remote_path="/runs/a/",
+                       volume=vol) == "runs/a"
+    assert set(vol.files) == {"runs/a/metadata.json", "runs/a/sub/tensors.bin"}
+    got = mt.transfer("download-checkpoint", local_path=str(tmp_path / "out"), checkpoint="runs/a",
+                      volume=vol)
+    assert got == ["metadata.json", "sub/tensors.bin"]
+    assert (tmp_path / "out" / "sub" / "tensors.bin").read_bytes() == bytes(range(40))
+    one = tmp_path / "d.bin"
+    one.write_bytes(b"tokens!")
+    mt.transfer("upload-data", local_path=str(one), remote_path="sets/d.bin", volume=vol)
+    assert mt.transfer("download-data-file", local_path=str(tmp_path / "back.bin"),
+                       remote_path="sets/d.bin", volume=vol) == 7
+    with pytest.raises(FileNotFoundError):
+        mt.transfer("download-checkpoint", local_path=str(tmp_path / "x"), checkpoint="nope",
+                    volume=vol)
+    with pytest.raises(ValueError):
+        mt.transfer("upload-data", local_path=str(one), remote_path="/", volume=vol)
+    with pytest.raises(ValueError):
+        mt.transfer("upload-data", volume=vol)
+
+
+def test_dropout_and_softmax_dim():
+    from ceo_b200.ops import nn as K
+    x = torch.randn(64, 50)
+    assert K.dropout(x, 0.3, training=False) is x and K.dropout(x, 0.0) is x
+    y = K.dropout(x, 0.25, seed=7)
+    keep = K.dropout_keep_mask(x.numel(), 0.25, 7).view(x.shape)
+    assert torch.equal(y, torch.where(keep, x / 0.75, torch.zeros_like(x)))
+    assert abs(keep.float().mean().item() - 0.75) < 0.03
+    assert not torch.equal(keep, K.dropout_keep_mask(x.numel(), 0.25, 8).view(x.shape))
+    with pytest.raises(ValueError):
+        K.dropout(x, 1.0)
+    z = torch.randn(3, 5, 7)
+    for dim in (0, 1, 2, -2):
+        s = K.softmax(z, dim)
+        assert torch.allclose(s, torch.softmax(z, dim), atol=1e-6)
+        assert torch.allclose(s.sum(dim), torch.ones_like(s.sum(dim)), atol=1e-5)
+
+
+def test_model_dropout_only_in_training_mode():
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    cfg.model.dropout = 0.5
+    model = EflaLM(cfg.model, "cpu", seed=0)
+    tok = torch.randint(0, cfg.model.vocab_size, (2, 32))
+    model.eval()
+    a, b = model(tok, tok), model(tok, tok)
+    assert torch.equal(a, b)
+    model.train()
+    c, d = model(tok, tok), model(tok, tok)
+    assert not torch.equal(c, d) and not torch.equal(a, c)
+    c.backward()
+    assert all(p.grad is not None for p in model.parameters() if p.requires_grad)
+
+
+def test_trainer_packs_documents_and_prefetches(tmp_path):
+    """data.pack_sequences with an end-of-document id: windows are cut into documents, packed
+    on 64-token boundaries with state resets, read ahead by the prefetch thread."""
+    from ceo_b200.data import dataset as D
+    from ceo_b200.runtime.trainer import Trainer
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    cfg.data.seq_len, cfg.data.eos_token_id, cfg.data.pack_sequences = 128, 5, True
+    cfg.data.prefetch_factor = 2
+    cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 4
+    cfg.training.total_steps = 3
+    cfg.checkpoint.save_interval = 0
+    rng = np.random.default_rng(0)
+    toks = rng.integers(6, cfg.model.vocab_size, size=6000).astype(np.uint32)
+    toks[rng.choice(6000, 90, replace=False)] = 5          # document ends
+    D.write_dataset(tmp_path / "d.bin", toks)
+    tr = Trainer(cfg, "cpu", data_path=str(tmp_path / "d.bin"), checkpoint_dir=str(tmp_path / "ck"))
+    tr._open_data()
+    assert tr._packing
+    tok, tgt, resets = tr._next_packed()
+    assert tok.shape == (2, 128) and tgt.shape == (2, 128) and resets.shape == (2, 2)
+    assert resets[:, 0].all() and (tgt == -100).any()
+    # an end-of-document token is never asked to predict the next document's first token
+    ends = (tok == 5)
+    assert (tgt[ends] == -100).all()
+    res = tr.run()
+    assert res["step"] == 3 and math.isfinite(res["loss"])
+    assert tr._prefetch is None  # closed at the end of the run
+    # without an end-of-document id the same config trains on plain windows
+    cfg.data.eos_token_id = -1
+    tr2 = Trainer(cfg, "cpu", data_path=str(tmp_path / "d.bin"), checkpoint_dir=str(tmp_path / "c2"))
+    tr2._open_data()
+    assert not tr2._packing and len(tr2._next_micro_batches()[0]) == 2
+    tr2._close_data()
