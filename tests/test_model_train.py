@@ -428,7 +428,8 @@ def test_trainer_packs_documents_and_prefetches(tmp_path):
     from ceo_b200.runtime.trainer import Trainer
     cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
     cfg.data.seq_len, cfg.data.eos_token_id, cfg.data.pack_sequences = 128, 5, True
-    cfg.data.prefetch_factor = 2
+    cfg.data.prefetch_factor, cfg.data.synthetic.kind = 2, ""
+    cfg.training.gradient_accumulation_steps = 2
     cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 4
     cfg.training.total_steps = 3
     cfg.checkpoint.save_interval = 0
