@@ -69,6 +69,21 @@ def _comm():
     return Comm()
 
 
+def _fit_mesh(rt, world: int):
+    """Largest (tp, cp, pp) not above the configured sizes whose product divides ``world``."""
+    tp, cp, pp = rt.tensor_parallel_size, rt.context_parallel_size, rt.pipeline_parallel_size
+    while world % (tp * cp * pp):
+        if pp > 1:
+            pp = max(1, pp // 2)
+        elif cp > 1:
+            cp = max(1, cp // 2)
+        elif tp > 1:
+            tp = max(1, tp // 2)
+        else:
+            break
+    return tp, cp, pp
+
+
 def run_train(args: ArgParser) -> int:
     o = _options(args, {"--config": ("str", None), "--resume": ("str", None),
                         "--data": ("str", None), "--checkpoint-dir": ("str", None),
@@ -78,11 +93,23 @@ def run_train(args: ArgParser) -> int:
     from .runtime.trainer import Trainer
     from .utils.telemetry import Telemetry
     cfg = Config.parse_from_file(o["config"])
-    comm = _comm()
-    if comm is not None:
-        cfg.runtime.world_size = comm.world
-        cfg.runtime.tensor_parallel_size = 1
-    tel = Telemetry(cfg.telemetry, rank=comm.rank if comm else 0)
+    rt = cfg.runtime
+    from .parallel.comm import init_distributed
+    rank, world, _ = init_distributed()
+    # the mesh of the config (tensor x context x pipeline, data parallel over the rest) must
+    # fit the ranks that were launched; a config written for more GPUs is cut down axis by axis
+    mp = rt.tensor_parallel_size * rt.context_parallel_size * rt.pipeline_parallel_size
+    if world % max(1, mp):
+        fitted = _fit_mesh(rt, world)
+        print(f"warning: tp x cp x pp = {mp} does not divide {world} rank(s); using "
+              f"tp={fitted[0]} cp={fitted[1]} pp={fitted[2]}", file=sys.stderr)
+        rt.tensor_parallel_size, rt.context_parallel_size, rt.pipeline_parallel_size = fitted
+        mp = fitted[0] * fitted[1] * fitted[2]
+    rt.world_size = world
+    # the model-parallel engines build their own groups; plain data parallelism gets the
+    # peer-memory communicator (library collectives when that is unavailable)
+    comm = _comm() if mp == 1 else None
+    tel = Telemetry(cfg.telemetry, rank=rank)
     for w in cfg.model.validate():
         tel.log("warn", "config", w)
     cfg.training.validate()

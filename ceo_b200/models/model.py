@@ -283,36 +283,9 @@ class EflaLM(nn.Module):
     def state_dict_reference(self) -> "OrderedDict[str, torch.Tensor]":
         """Tensors under the reference's names and (in, out) orientation."""
         out = OrderedDict()
-        hd = self.cfg.num_heads * self.cfg.head_dim
         out["embed_tokens.weight"] = self.embed_tokens.detach()
         for i, b in enumerate(self.blocks):
-            p = f"blocks.{i}."
-            out[p + "ln1.weight"] = b.ln1.weight.detach()
-            if b.ln1.bias is not None:
-                out[p + "ln1.bias"] = b.ln1.bias.detach()
-            names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
-            parts = b.efla.w_qkv.detach()[:len(names) * hd].split(hd, dim=0)
-            for nme, w in zip(names, parts):
-                out[p + "efla." + nme] = w.t().contiguous()
-            out[p + "efla.w_o"] = b.efla.w_o.detach().t().contiguous()
-            if b.efla.per_token_beta:
-                nb = len(names) * hd
-                out[p + "efla.w_beta"] = b.efla.w_qkv.detach()[nb:nb + b.efla.H].t().contiguous()
-            else:
-                out[p + "efla.beta_param"] = b.efla.beta_param.detach()
-            if b.prism is not None:
-                for nme, t in b.prism.reference_tensors().items():
-                    out[p + "prism." + nme] = t
-            out[p + "ln2.weight"] = b.ln2.weight.detach()
-            if b.ln2.bias is not None:
-                out[p + "ln2.bias"] = b.ln2.bias.detach()
-            if b.mlp.act == "swiglu":
-                g, u = b.mlp.w_up.detach().split(b.mlp.F, dim=0)
-                out[p + "mlp_gate.weight"] = g.t().contiguous()
-                out[p + "mlp_up.weight"] = u.t().contiguous()
-            else:
-                out[p + "mlp_up.weight"] = b.mlp.w_up.detach().t().contiguous()
-            out[p + "mlp_down.weight"] = b.mlp.w_down.detach().t().contiguous()
+            block_reference_tensors(b, f"blocks.{i}.", self.cfg, out)
         out["final_norm.weight"] = self.final_norm.weight.detach()
         if self.final_norm.bias is not None:
             out["final_norm.bias"] = self.final_norm.bias.detach()
@@ -323,41 +296,14 @@ class EflaLM(nn.Module):
     @torch.no_grad()
     def load_reference_state(self, tensors: dict) -> None:
         """Inverse of ``state_dict_reference`` (raises KeyError on a missing tensor)."""
-        def put(dst, src):
-            dst.copy_(src.to(dst.device, dst.dtype))
-        hd = self.cfg.num_heads * self.cfg.head_dim
-        put(self.embed_tokens, tensors["embed_tokens.weight"])
+        _put(self.embed_tokens, tensors["embed_tokens.weight"])
         for i, b in enumerate(self.blocks):
-            p = f"blocks.{i}."
-            put(b.ln1.weight, tensors[p + "ln1.weight"])
-            if b.ln1.bias is not None:
-                put(b.ln1.bias, tensors[p + "ln1.bias"])
-            names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
-            for j, nme in enumerate(names):
-                put(b.efla.w_qkv[j * hd:(j + 1) * hd], tensors[p + "efla." + nme].t())
-            put(b.efla.w_o, tensors[p + "efla.w_o"].t())
-            if b.efla.per_token_beta:
-                nb = len(names) * hd
-                put(b.efla.w_qkv[nb:nb + b.efla.H], tensors[p + "efla.w_beta"].t())
-            else:
-                put(b.efla.beta_param, tensors[p + "efla.beta_param"].reshape(1))
-            if b.prism is not None:
-                b.prism.load_reference_tensors({k[len(p + "prism."):]: v for k, v in tensors.items()
-                                                if k.startswith(p + "prism.")})
-            put(b.ln2.weight, tensors[p + "ln2.weight"])
-            if b.ln2.bias is not None:
-                put(b.ln2.bias, tensors[p + "ln2.bias"])
-            if b.mlp.act == "swiglu":
-                put(b.mlp.w_up[:b.mlp.F], tensors[p + "mlp_gate.weight"].t())
-                put(b.mlp.w_up[b.mlp.F:], tensors[p + "mlp_up.weight"].t())
-            else:
-                put(b.mlp.w_up, tensors[p + "mlp_up.weight"].t())
-            put(b.mlp.w_down, tensors[p + "mlp_down.weight"].t())
-        put(self.final_norm.weight, tensors["final_norm.weight"])
+            load_block_reference(b, f"blocks.{i}.", self.cfg, tensors)
+        _put(self.final_norm.weight, tensors["final_norm.weight"])
         if self.final_norm.bias is not None:
-            put(self.final_norm.bias, tensors["final_norm.bias"])
+            _put(self.final_norm.bias, tensors["final_norm.bias"])
         if self.lm_head is not None:
-            put(self.lm_head, tensors["lm_head.weight"].t())
+            _put(self.lm_head, tensors["lm_head.weight"].t())
 
     def flops_per_token(self, seq_len: int | None = None) -> float:
         """Model FLOPs per token for one forward+backward (6 x matmul parameters + EFLA)."""
@@ -369,3 +315,85 @@ class EflaLM(nn.Module):
             mat += self.embed_tokens.numel()
         efla = c.num_layers * c.num_heads * (4 * c.head_dim * c.head_dim + 8 * 64 * c.head_dim)
         return 6.0 * mat + 3.0 * efla
+
+
+def model_flops_per_token(c: ModelConfig) -> float:
+    """Model FLOPs per token of one forward + backward, from the configuration alone
+    (6 x the multiply-accumulates of the projections, MLP and LM head, plus EFLA)."""
+    e = c.efla
+    hd = c.num_heads * c.head_dim
+    P = 3 if e.use_query else 2
+    up = (2 if c.activation == "swiglu" else 1) * c.intermediate_dim
+    per_block = (P * hd + (c.num_heads if e.per_token_beta else 0)) * c.hidden_dim \
+        + c.hidden_dim * hd + up * c.hidden_dim + c.hidden_dim * c.intermediate_dim
+    mat = c.num_layers * per_block + c.vocab_size * c.hidden_dim
+    efla = c.num_layers * c.num_heads * (4 * c.head_dim * c.head_dim + 8 * 64 * c.head_dim)
+    return 6.0 * mat + 3.0 * efla
+
+
+# ---- one block's tensors under the reference's names (shared with the pipeline stages) ----
+def _put(dst, src):
+    dst.copy_(src.to(dst.device, dst.dtype))
+
+
+def block_reference_tensors(b: Block, p: str, cfg: ModelConfig, out: dict) -> dict:
+    """Adds block ``b``'s tensors to ``out`` under prefix ``p`` (``blocks.{i}.``), reference
+    names and (in, out) orientation (src/model/model.zig:494-521)."""
+    hd = cfg.num_heads * cfg.head_dim
+    out[p + "ln1.weight"] = b.ln1.weight.detach()
+    if b.ln1.bias is not None:
+        out[p + "ln1.bias"] = b.ln1.bias.detach()
+    names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
+    parts = b.efla.w_qkv.detach()[:len(names) * hd].split(hd, dim=0)
+    for nme, w in zip(names, parts):
+        out[p + "efla." + nme] = w.t().contiguous()
+    out[p + "efla.w_o"] = b.efla.w_o.detach().t().contiguous()
+    if b.efla.per_token_beta:
+        nb = len(names) * hd
+        out[p + "efla.w_beta"] = b.efla.w_qkv.detach()[nb:nb + b.efla.H].t().contiguous()
+    else:
+        out[p + "efla.beta_param"] = b.efla.beta_param.detach()
+    if b.prism is not None:
+        for nme, t in b.prism.reference_tensors().items():
+            out[p + "prism." + nme] = t
+    out[p + "ln2.weight"] = b.ln2.weight.detach()
+    if b.ln2.bias is not None:
+        out[p + "ln2.bias"] = b.ln2.bias.detach()
+    if b.mlp.act == "swiglu":
+        g, u = b.mlp.w_up.detach().split(b.mlp.F, dim=0)
+        out[p + "mlp_gate.weight"] = g.t().contiguous()
+        out[p + "mlp_up.weight"] = u.t().contiguous()
+    else:
+        out[p + "mlp_up.weight"] = b.mlp.w_up.detach().t().contiguous()
+    out[p + "mlp_down.weight"] = b.mlp.w_down.detach().t().contiguous()
+    return out
+
+
+@torch.no_grad()
+def load_block_reference(b: Block, p: str, cfg: ModelConfig, tensors: dict) -> None:
+    """Inverse of ``block_reference_tensors``."""
+    hd = cfg.num_heads * cfg.head_dim
+    _put(b.ln1.weight, tensors[p + "ln1.weight"])
+    if b.ln1.bias is not None:
+        _put(b.ln1.bias, tensors[p + "ln1.bias"])
+    names = ["w_q", "w_k", "w_v"] if b.efla.P == 3 else ["w_k", "w_v"]
+    for j, nme in enumerate(names):
+        _put(b.efla.w_qkv[j * hd:(j + 1) * hd], tensors[p + "efla." + nme].t())
+    _put(b.efla.w_o, tensors[p + "efla.w_o"].t())
+    if b.efla.per_token_beta:
+        nb = len(names) * hd
+        _put(b.efla.w_qkv[nb:nb + b.efla.H], tensors[p + "efla.w_beta"].t())
+    else:
+        _put(b.efla.beta_param, tensors[p + "efla.beta_param"].reshape(1))
+    if b.prism is not None:
+        b.prism.load_reference_tensors({k[len(p + "prism."):]: v for k, v in tensors.items()
+                                        if k.startswith(p + "prism.")})
+    _put(b.ln2.weight, tensors[p + "ln2.weight"])
+    if b.ln2.bias is not None:
+        _put(b.ln2.bias, tensors[p + "ln2.bias"])
+    if b.mlp.act == "swiglu":
+        _put(b.mlp.w_up[:b.mlp.F], tensors[p + "mlp_gate.weight"].t())
+        _put(b.mlp.w_up[b.mlp.F:], tensors[p + "mlp_up.weight"].t())
+    else:
+        _put(b.mlp.w_up, tensors[p + "mlp_up.weight"].t())
+    _put(b.mlp.w_down, tensors[p + "mlp_down.weight"].t())

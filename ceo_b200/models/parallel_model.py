@@ -171,6 +171,95 @@ class ParallelEflaLM(nn.Module):
         w = self.embed_tokens if self.lm_head is None else self.lm_head
         return K.linear_cross_entropy(hn, w, tgt, label_smoothing)
 
+    # ------------------------------------------------------------ checkpoint name mapping
+    def state_dict_shards(self):
+        """This rank's tensors under the reference's names and (in, out) orientation
+        (src/model/model.zig:494-521), as ``name -> (tensor, shard_dim)``: ``shard_dim`` is the
+        dimension of the FULL tensor this rank holds a ``1 / tp`` slice of (its tp rank-th
+        slice), or None for a tensor every rank holds whole."""
+        out = {}
+        out["embed_tokens.weight"] = (self.embed_tokens.detach(), None)
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            hd = b.H_loc * b.d
+            out[p + "ln1.weight"] = (b.ln1.weight.detach(), None)
+            if b.ln1.bias is not None:
+                out[p + "ln1.bias"] = (b.ln1.bias.detach(), None)
+            names = ["w_q", "w_k", "w_v"] if b.P == 3 else ["w_k", "w_v"]
+            for j, nme in enumerate(names):
+                out[p + "efla." + nme] = (b.w_qkv.detach()[j * hd:(j + 1) * hd].t().contiguous(), 1)
+            out[p + "efla.w_o"] = (b.w_o.detach().t().contiguous(), 0)
+            if b.per_token_beta:
+                nb = len(names) * hd
+                out[p + "efla.w_beta"] = (b.w_qkv.detach()[nb:nb + b.H_loc].t().contiguous(), 1)
+            else:
+                out[p + "efla.beta_param"] = (b.beta_param.detach(), None)
+            out[p + "ln2.weight"] = (b.ln2.weight.detach(), None)
+            if b.ln2.bias is not None:
+                out[p + "ln2.bias"] = (b.ln2.bias.detach(), None)
+            if b.act == "swiglu":
+                g, u = b.w_up.detach().split(b.F_loc, dim=0)
+                out[p + "mlp_gate.weight"] = (g.t().contiguous(), 1)
+                out[p + "mlp_up.weight"] = (u.t().contiguous(), 1)
+            else:
+                out[p + "mlp_up.weight"] = (b.w_up.detach().t().contiguous(), 1)
+            out[p + "mlp_down.weight"] = (b.w_down.detach().t().contiguous(), 0)
+        out["final_norm.weight"] = (self.final_norm.weight.detach(), None)
+        if self.final_norm.bias is not None:
+            out["final_norm.bias"] = (self.final_norm.bias.detach(), None)
+        if self.lm_head is not None:
+            out["lm_head.weight"] = (self.lm_head.detach().t().contiguous(), None)
+        return out
+
+    @torch.no_grad()
+    def load_reference_state(self, tensors: dict) -> None:
+        """Loads FULL tensors (reference names and orientation, e.g. a checkpoint written at
+        any tensor-parallel size) and keeps this rank's slices."""
+        r, w = self.tp_rank, self.tp_world
+
+        def put(dst, src):
+            dst.copy_(src.to(dst.device, dst.dtype))
+
+        def cut(t, dim):
+            return t.chunk(w, dim=dim)[r]
+        put(self.embed_tokens, tensors["embed_tokens.weight"])
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            hd = b.H_loc * b.d
+            put(b.ln1.weight, tensors[p + "ln1.weight"])
+            if b.ln1.bias is not None:
+                put(b.ln1.bias, tensors[p + "ln1.bias"])
+            names = ["w_q", "w_k", "w_v"] if b.P == 3 else ["w_k", "w_v"]
+            for j, nme in enumerate(names):
+                put(b.w_qkv[j * hd:(j + 1) * hd], cut(tensors[p + "efla." + nme], 1).t())
+            put(b.w_o, cut(tensors[p + "efla.w_o"], 0).t())
+            if b.per_token_beta:
+                nb = len(names) * hd
+                put(b.w_qkv[nb:nb + b.H_loc], cut(tensors[p + "efla.w_beta"], 1).t())
+            else:
+                put(b.beta_param, tensors[p + "efla.beta_param"].reshape(1))
+            put(b.ln2.weight, tensors[p + "ln2.weight"])
+            if b.ln2.bias is not None:
+                put(b.ln2.bias, tensors[p + "ln2.bias"])
+            if b.act == "swiglu":
+                put(b.w_up[:b.F_loc], cut(tensors[p + "mlp_gate.weight"], 1).t())
+                put(b.w_up[b.F_loc:], cut(tensors[p + "mlp_up.weight"], 1).t())
+            else:
+                put(b.w_up, cut(tensors[p + "mlp_up.weight"], 1).t())
+            put(b.w_down, cut(tensors[p + "mlp_down.weight"], 0).t())
+        put(self.final_norm.weight, tensors["final_norm.weight"])
+        if self.final_norm.bias is not None:
+            put(self.final_norm.bias, tensors["final_norm.bias"])
+        if self.lm_head is not None:
+            put(self.lm_head, tensors["lm_head.weight"].t())
+
+    def count_parameters(self) -> int:
+        """Parameters of the whole model (sharded tensors counted at full size)."""
+        n = 0
+        for p in self.parameters():
+            n += p.numel() if getattr(p, "replicated", False) else p.numel() * self.tp_world
+        return n
+
     def grad_scale_divisor(self) -> int:
         """Each rank of a tp / cp group back-propagates the mean loss of ITS tokens; the
         gradient of the group's mean loss is the sum of those divided by the group size."""

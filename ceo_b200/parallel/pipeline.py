@@ -33,6 +33,46 @@ def stage_bounds(num_layers: int, stages: int, stage: int) -> tuple[int, int]:
 class PipelineStage(nn.Module):
     """The slice of the model one pipeline rank runs."""
 
+    def flops_per_token(self, seq_len=None) -> float:
+        """Of the WHOLE model (all stages), for throughput accounting."""
+        from ..models.model import model_flops_per_token
+        return model_flops_per_token(self.cfg)
+
+    def count_parameters(self) -> int:
+        """Parameters this stage holds."""
+        return sum(p.numel() for p in self.parameters())
+
+    def state_dict_shards(self):
+        """name -> (tensor, None): this stage's tensors under the reference's names."""
+        from ..models.model import block_reference_tensors
+        out = {}
+        if self.first:
+            out["embed_tokens.weight"] = self.embed_tokens.detach()
+        for j, b in enumerate(self.blocks):
+            block_reference_tensors(b, f"blocks.{self.lo + j}.", self.cfg, out)
+        if self.last:
+            out["final_norm.weight"] = self.final_norm.weight.detach()
+            if self.final_norm.bias is not None:
+                out["final_norm.bias"] = self.final_norm.bias.detach()
+            if self.lm_head is not None:
+                out["lm_head.weight"] = self.lm_head.detach().t().contiguous()
+        return {k: (v, None) for k, v in out.items()}
+
+    @torch.no_grad()
+    def load_reference_state(self, tensors: dict) -> None:
+        """Keeps this stage's part of a FULL set of tensors (reference names)."""
+        from ..models.model import _put, load_block_reference
+        if self.embed_tokens is not None:
+            _put(self.embed_tokens, tensors["embed_tokens.weight"])
+        for j, b in enumerate(self.blocks):
+            load_block_reference(b, f"blocks.{self.lo + j}.", self.cfg, tensors)
+        if self.last:
+            _put(self.final_norm.weight, tensors["final_norm.weight"])
+            if self.final_norm.bias is not None:
+                _put(self.final_norm.bias, tensors["final_norm.bias"])
+            if self.lm_head is not None:
+                _put(self.lm_head, tensors["lm_head.weight"].t())
+
     def __init__(self, cfg: ModelConfig, device, stage: int, stages: int, seed: int = 0,
                  dtype=None):
         super().__init__()
@@ -92,10 +132,13 @@ class PipelineRunner:
         _p2p(ops)
         return got
 
-    def run(self, batches, label_smoothing: float = 0.0) -> torch.Tensor:
+    def run(self, batches, label_smoothing: float = 0.0, scale_loss: bool = True) -> torch.Tensor:
         """``batches``: list of (tokens, targets), the same on every stage.  Gradients
-        accumulate in the parameters (mean over the micro-batches).  Returns the mean loss
-        (valid on every rank: the last stage broadcasts it)."""
+        accumulate in the parameters: their mean over the micro-batches, or, with
+        ``scale_loss=False``, their SUM (every loss back-propagated with gradient 1, which is
+        what the fp32 ``main_grad`` accumulation of the GEMM epilogues assumes; the caller
+        then folds 1/n into the optimizer's gradient scale).  Returns the mean loss (valid on
+        every rank: the last stage broadcasts it)."""
         n = len(batches)
         st = self.stage
         dev = batches[0][0].device
@@ -121,7 +164,7 @@ class PipelineRunner:
         def backward(g):
             x, out = pending.pop(0)
             if st.last:
-                (out / n).backward()
+                (out / n if scale_loss else out).backward()
             else:
                 torch.autograd.backward(out, grad_tensors=g)
             return None if st.first else x.grad

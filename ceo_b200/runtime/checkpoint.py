@@ -61,9 +61,17 @@ class CheckpointManager:
     # --------------------------------------------------------------------------- save
     def save(self, step: int, tensors: dict, metadata: dict, optimizer_state: dict | None = None,
              rng_state: bytes | None = None, config_yaml: str | None = None,
-             extra: dict | None = None, shard_timeout: float = 600.0) -> str:
+             extra: dict | None = None, shard_timeout: float = 600.0,
+             tensor_shards: dict | None = None, shard_rank: int = 0, shard_world: int = 1) -> str:
         """``tensors``: name -> tensor (reference names/orientation), written by rank 0.
         ``optimizer_state``: name -> tensor, this rank's slice, written by every rank.
+        ``tensor_shards`` (tensor / pipeline parallelism): name -> (tensor, shard_dim or None),
+        what model shard ``shard_rank`` of ``shard_world`` holds (shards ordered pipeline stage
+        first, tensor-parallel rank second; a slice along ``shard_dim`` or a whole tensor).
+        Each shard holder writes ``tensors.rank{shard_rank}.bin`` and rank 0 writes
+        ``tensors.index.json``, from which ``load_tensors`` rebuilds the full tensors, so every
+        reader sees one model whatever layout wrote it.  Pass it on the ranks that hold
+        data-parallel replica 0 only.
         Every rank drops a ``rank{r}.done`` marker once its files are complete; rank 0 commits
         ``metadata.json`` (and prunes older checkpoints) only after all markers are there, so a
         directory that ``latest()`` returns always holds every shard."""
@@ -71,6 +79,11 @@ class CheckpointManager:
         path = self.path_for(step)
         host_tensors = {k: v.detach().to("cpu", copy=True) for k, v in tensors.items()} \
             if self.rank == 0 else {}
+        host_shards = None
+        if tensor_shards is not None:
+            # a slice is stored as "name@dim" (this file's slice of the full tensor along dim)
+            host_shards = {(k if v[1] is None else f"{k}@{int(v[1])}"):
+                           v[0].detach().to("cpu", copy=True) for k, v in tensor_shards.items()}
         host_opt = None
         if optimizer_state is not None and self.save_optimizer:
             host_opt = {k: v.detach().to("cpu", copy=True) for k, v in optimizer_state.items()}
@@ -82,10 +95,18 @@ class CheckpointManager:
                     name = "optimizer.bin" if self.world == 1 else f"optimizer.rank{self.rank}.bin"
                     formats.write_tensor_file(os.path.join(path, name), host_opt,
                                               formats.MAGIC_OPTIMIZER)
+                if host_shards is not None:
+                    formats.write_tensor_file(os.path.join(path, f"tensors.rank{shard_rank}.bin"),
+                                              host_shards)
+                    if self.rank == 0:
+                        with open(os.path.join(path, "tensors.index.json"), "w") as f:
+                            json.dump({"files": [f"tensors.rank{r}.bin"
+                                                 for r in range(shard_world)]}, f, indent=1)
                 with open(os.path.join(path, f"rank{self.rank}.done"), "w") as f:
                     f.write(str(int(step)))
                 if self.rank == 0:
-                    formats.write_tensor_file(os.path.join(path, "tensors.bin"), host_tensors)
+                    if host_shards is None:
+                        formats.write_tensor_file(os.path.join(path, "tensors.bin"), host_tensors)
                     if rng_state is not None:
                         with open(os.path.join(path, "rng.bin"), "wb") as f:
                             f.write(rng_state)
@@ -151,7 +172,25 @@ class CheckpointManager:
 
     @staticmethod
     def load_tensors(path, verify: bool = True) -> dict:
-        return formats.read_tensor_file(os.path.join(path, "tensors.bin"), verify=verify)
+        """The model's full tensors under the reference's names: ``tensors.bin``, or, for a
+        checkpoint written under tensor parallelism, the per-rank files merged through
+        ``tensors.index.json`` (sharded tensors concatenated along their shard dimension)."""
+        single = os.path.join(path, "tensors.bin")
+        if os.path.exists(single):
+            return formats.read_tensor_file(single, verify=verify)
+        with open(os.path.join(path, "tensors.index.json")) as f:
+            idx = json.load(f)
+        whole, slices = {}, {}
+        for n in idx["files"]:  # file order = (pipeline stage, tensor-parallel rank)
+            for key, t in formats.read_tensor_file(os.path.join(path, n), verify=verify).items():
+                if "@" in key:
+                    name, dim = key.rsplit("@", 1)
+                    slices.setdefault(name, (int(dim), []))[1].append(t)
+                else:
+                    whole.setdefault(key, t)
+        for name, (dim, parts) in slices.items():
+            whole[name] = torch.cat(parts, dim=dim)
+        return whole
 
     def load_optimizer(self, path, flat=None) -> dict | None:
         """This rank's optimizer state.  Saved with the same world size and ownership layout:
@@ -216,7 +255,8 @@ class CheckpointManager:
         """Returns a list of problems (empty = valid): files present, index parses, sizes
         consistent, every checksum matches."""
         problems = []
-        for need in ("metadata.json", "tensors.bin"):
+        sharded = os.path.exists(os.path.join(path, "tensors.index.json"))
+        for need in ("metadata.json", "tensors.index.json" if sharded else "tensors.bin"):
             if not os.path.exists(os.path.join(path, need)):
                 problems.append(f"missing {need}")
         if problems:
@@ -232,18 +272,16 @@ class CheckpointManager:
         except Exception as e:  # noqa: BLE001
             problems.append(f"metadata.json: {e}")
         try:
-            formats.read_tensor_file(os.path.join(path, "tensors.bin"), verify=True)
+            CheckpointManager.load_tensors(path, verify=True)
         except Exception as e:  # noqa: BLE001
-            problems.append(f"tensors.bin: {e}")
+            problems.append(f"{'tensors.rank*.bin' if sharded else 'tensors.bin'}: {e}")
         return problems
 
     @staticmethod
     def convert(input_path, output_path, fmt: str) -> None:
         """``efla_native`` (re-write), ``pytorch`` (torch.save of the dict) or ``safetensors``."""
-        src = input_path
-        if os.path.isdir(src):
-            src = os.path.join(src, "tensors.bin")
-        tensors = formats.read_tensor_file(src)
+        tensors = CheckpointManager.load_tensors(input_path) if os.path.isdir(input_path) \
+            else formats.read_tensor_file(input_path)
         if fmt == "efla_native":
             formats.write_tensor_file(output_path, tensors)
         elif fmt == "pytorch":

@@ -106,6 +106,10 @@ class ParallelEngine:
         self.step_count = 0
         self.tokens_seen = 0
         self.cp_rank = self.pc.sp_rank
+        self.zero_stage = 1 if rep_world > 1 else 0
+
+    def materialize_params(self):
+        pass
 
     def local_span(self, tokens: torch.Tensor) -> torch.Tensor:
         """This rank's contiguous span of the sequence dimension under context parallelism."""
@@ -121,7 +125,7 @@ class ParallelEngine:
         if lr is None:
             lr = self.scheduler.get_lr()
         total = torch.zeros((), dtype=torch.float32, device=self.device)
-        for tok, tgt in batches:
+        for tok, tgt, *_ in batches:
             tok = self.local_span(tok.to(self.device, non_blocking=True))
             tgt = self.local_span(tgt.to(self.device, non_blocking=True))
             loss = self.model(tok, tgt, self.cfg.training.label_smoothing)
@@ -146,3 +150,92 @@ class ParallelEngine:
         for c in (self.tp_comm, self.cp_comm, self.rep_comm):
             if c is not None and hasattr(c, "close"):
                 c.close()
+
+
+class PipelineEngine:
+    """Training engine for pipeline-parallel runs (``runtime.pipeline_parallel_size`` > 1):
+    the blocks are cut into contiguous stages (``parallel.pipeline``), micro-batches flow
+    through them on the 1F1B schedule with point-to-point exchanges of the library, and the
+    ranks that hold the same stage (the data-parallel group) share a sharded optimizer.
+    Rank order pp -> dp as in the reference's ``ParallelConfig.globalRank``
+    (src/tensor/sharding.zig:401-412).  Tensor and context parallelism inside a stage are not
+    combined with it."""
+
+    def __init__(self, cfg: Config, device):
+        from ..parallel.pipeline import PipelineRunner, PipelineStage
+        self.cfg = cfg
+        self.device = torch.device(device)
+        rt = cfg.runtime
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        pp = rt.pipeline_parallel_size
+        if rt.tensor_parallel_size * rt.context_parallel_size != 1:
+            raise ValueError("pipeline parallelism is not combined with tensor / context "
+                             "parallelism: set tensor_parallel_size = context_parallel_size = 1")
+        if world % pp:
+            raise ValueError(f"world {world} is not a multiple of the pipeline size {pp}")
+        dp = world // pp
+        self.pc = ParallelConfig.from_global_rank(rank, pp, dp, 1, 1, rt.zero_stage)
+        pcs = [ParallelConfig.from_global_rank(r, pp, dp, 1, 1) for r in range(world)]
+        pp_sets = sorted({tuple(p.group_ranks("pp")) for p in pcs})
+        dp_sets = sorted({tuple(p.group_ranks("dp")) for p in pcs})
+        self.pp_group = _group_for(None, pp_sets) if world > 1 else None
+        self.dp_group = _group_for(None, dp_sets) if world > 1 else None
+        self.pp_size, self.dp_size, self.tp_size, self.cp_size = pp, dp, 1, 1
+        self.rank, self.world = rank, world
+        self.fp8 = None
+        self.zero_stage = 1 if dp > 1 else 0
+        dtype = torch.bfloat16 if self.device.type == "cuda" else None
+        self.model = PipelineStage(cfg.model, self.device, self.pc.pp_rank, pp, seed=rt.seed,
+                                   dtype=dtype)
+        self.runner = PipelineRunner(self.model, self.pp_group)
+        self.dp_comm = Comm(self.dp_group) if dp > 1 else None
+        self.flat = FlatParams(self.model, dp, self.pc.dp_rank)
+        self.optimizer = build_optimizer(self.flat, cfg.training, self.dp_comm)
+        if pp > 1:
+            self.optimizer.extra_norm_group = self.pp_group  # the norm spans all stages
+            self.optimizer.use_fused_step = False
+        t = cfg.training
+        self.scheduler = LRScheduler(t.learning_rate, t.min_learning_rate, t.warmup_steps,
+                                     t.total_steps, t.lr_schedule)
+        self.step_count = 0
+        self.tokens_seen = 0
+
+    def train_step(self, batches, lr: float | None = None):
+        """``batches``: this data-parallel replica's micro-batches (the same list on every
+        stage of the replica)."""
+        n = len(batches)
+        if lr is None:
+            lr = self.scheduler.get_lr()
+        dev_batches = [tuple(x.to(self.device, non_blocking=True) for x in b[:2]) for b in batches]
+        loss = self.runner.run(dev_batches, self.cfg.training.label_smoothing, scale_loss=False)
+        self.runner.sync_tied_grads()
+        for tok, _ in dev_batches:
+            self.tokens_seen += tok.numel() * self.dp_size
+        gnorm = self.optimizer.step(lr, grad_scale=1.0 / (n * self.dp_size))
+        self.scheduler.step()
+        self.step_count += 1
+        if self.dp_comm is not None:
+            self.dp_comm.all_reduce(loss)
+            loss = loss / self.dp_size
+        return loss, gnorm
+
+    def materialize_params(self):
+        pass
+
+    def close(self):
+        pass
+
+
+def build_engine(cfg: Config, device, comm=None):
+    """The engine the ``runtime`` section asks for: pipeline stages when
+    ``pipeline_parallel_size`` > 1, the tensor / context parallel engine when
+    ``tensor_parallel_size x context_parallel_size`` > 1, else the data-parallel
+    ``TrainEngine`` (ZeRO stage from ``zero_stage``) on ``comm``."""
+    rt = cfg.runtime
+    if rt.pipeline_parallel_size > 1:
+        return PipelineEngine(cfg, device)
+    if rt.tensor_parallel_size * rt.context_parallel_size > 1:
+        return ParallelEngine(cfg, device)
+    from .engine import TrainEngine
+    return TrainEngine(cfg, device, comm)

@@ -46,9 +46,25 @@ class Trainer:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
         self.comm = comm
-        self.rank = comm.rank if comm is not None else 0
-        self.world = comm.world if comm is not None else 1
-        self.engine = TrainEngine(cfg, self.device, comm)
+        import torch.distributed as dist
+        if comm is not None:
+            self.rank, self.world = comm.rank, comm.world
+        elif dist.is_available() and dist.is_initialized():
+            self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        else:
+            self.rank, self.world = 0, 1
+        # runtime.{tensor,context,pipeline}_parallel_size pick the engine
+        # (src/util/config.zig:487-489,509-510; rank order src/tensor/sharding.zig:357-421)
+        from .parallel_engine import build_engine
+        self.engine = build_engine(cfg, self.device, comm)
+        rt = cfg.runtime
+        self.model_parallel = rt.tensor_parallel_size * rt.context_parallel_size * \
+            rt.pipeline_parallel_size
+        if self.model_parallel > 1:
+            pc = self.engine.pc
+            self.dp_rank, self.dp_world = pc.dp_rank, pc.dp_world_size
+        else:
+            self.dp_rank, self.dp_world = self.rank, self.world
         self.telemetry = telemetry or Telemetry(rank=self.rank, log_file=None,
                                                 log_level=cfg.telemetry.log_level)
         if self.engine.fp8 is not None:
@@ -70,7 +86,7 @@ class Trainer:
         self.epoch = 0
         self.last_loss = float("nan")
         t = cfg.training
-        dp = max(1, self.world)
+        dp = max(1, self.dp_world)
         self.micro_batch = t.micro_batch_size
         self.n_micro = max(1, t.global_batch_size // (t.micro_batch_size * dp))
         # training.gradient_accumulation_steps (src/util/config.zig:407) must agree with
@@ -100,13 +116,13 @@ class Trainer:
         d = self.cfg.data
         if d.synthetic.kind:
             self._synth = SyntheticTokens(self.cfg.model.vocab_size, d.synthetic.kind,
-                                          d.synthetic.s, d.synthetic.seed, self.rank)
+                                          d.synthetic.s, d.synthetic.seed, self.dp_rank)
             return
         self._synth = None
         ds = BinaryDataset.open(self.data_path)
         self.loader = DataLoader(ds, d.seq_len, self.micro_batch, shuffle=True, drop_last=True,
-                                 seed=self.cfg.runtime.seed, dp_rank=self.rank, dp_world=self.world,
-                                 pin=self.device.type == "cuda")
+                                 seed=self.cfg.runtime.seed, dp_rank=self.dp_rank,
+                                 dp_world=self.dp_world, pin=self.device.type == "cuda")
         if len(self.loader) == 0:
             raise errors.DataExhausted(
                 f"{self.data_path}: not enough tokens for one batch of {self.micro_batch} x "
@@ -186,7 +202,7 @@ class Trainer:
         self._open_data()
         total = cfg.training.total_steps if max_steps is None else \
             min(cfg.training.total_steps, eng.step_count + max_steps)
-        tokens_per_step = self.micro_batch * self.n_micro * cfg.data.seq_len * self.world
+        tokens_per_step = self.micro_batch * self.n_micro * cfg.data.seq_len * self.dp_world
         flops_tok = eng.model.flops_per_token(cfg.data.seq_len)
         tel.log("info", "trainer", f"training {cfg.model.name}: {eng.model.count_parameters()} "
                 f"parameters, {tokens_per_step} tokens/step, {self.world} rank(s)")
@@ -210,6 +226,11 @@ class Trainer:
                     secs = e0.elapsed_time(e1) * 1e-3
                     if self.comm is not None:
                         secs = self.comm.max_over_ranks(secs)
+                    elif self.world > 1:
+                        import torch.distributed as dist
+                        tmax = torch.tensor([secs], dtype=torch.float64, device=self.device)
+                        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                        secs = float(tmax)
                 else:
                     secs = time.time() - t0
                 lv, gv = float(loss), float(gnorm)
@@ -265,13 +286,26 @@ class Trainer:
                 opt[f"side.{name}.{k}"] = v
         opt["step_count"] = torch.tensor([eng.optimizer.step_count], dtype=torch.int64)
         rng = torch.get_rng_state().numpy().tobytes()
+        rt = self.cfg.runtime
         extra = {"scheduler": eng.scheduler.state_dict(),
                  "loader": self._loader_state(),
-                 "flat_layout": eng.flat.layout_info()}
+                 "flat_layout": eng.flat.layout_info(),
+                 "mesh": {"pp": rt.pipeline_parallel_size, "tp": rt.tensor_parallel_size,
+                          "cp": rt.context_parallel_size, "world": self.world}}
         if eng.fp8 is not None:
             extra["fp8"] = eng.fp8.state_dict()
-        path = self.ckpt.save(eng.step_count, eng.model.state_dict_reference(), md, opt, rng,
-                              self.cfg.to_yaml(), extra)
+        if self.model_parallel > 1:
+            # every model shard of data-parallel replica 0 writes its slice; readers merge them
+            pc = eng.pc
+            writer = pc.dp_rank == 0 and pc.sp_rank == 0
+            shards = eng.model.state_dict_shards() if writer else None
+            path = self.ckpt.save(eng.step_count, {}, md, opt, rng, self.cfg.to_yaml(), extra,
+                                  tensor_shards=shards,
+                                  shard_rank=pc.pp_rank * pc.tp_world_size + pc.tp_rank,
+                                  shard_world=pc.pp_world_size * pc.tp_world_size)
+        else:
+            path = self.ckpt.save(eng.step_count, eng.model.state_dict_reference(), md, opt, rng,
+                                  self.cfg.to_yaml(), extra)
         self.telemetry.log("info", "checkpoint", f"saved {path}")
         return path
 
@@ -287,7 +321,21 @@ class Trainer:
             raise errors.CheckpointCorrupted(str(e)) from e
         eng.model.load_reference_state(tensors)
         eng.flat.refresh_master()
-        opt = self.ckpt.load_optimizer(path, eng.flat)
+        mesh_now = {"pp": self.cfg.runtime.pipeline_parallel_size,
+                    "tp": self.cfg.runtime.tensor_parallel_size,
+                    "cp": self.cfg.runtime.context_parallel_size, "world": self.world}
+        saved_mesh = (md.get("extra") or {}).get("mesh") or \
+            {"pp": 1, "tp": 1, "cp": 1, "world": int(md.get("world_size", 1))}
+        if self.model_parallel > 1 or any(saved_mesh[k] != 1 for k in ("pp", "tp", "cp")):
+            # optimizer shards follow the model-parallel layout: they carry over only when the
+            # mesh is unchanged; otherwise the moments restart (master weights come from the
+            # loaded parameters)
+            opt = self.ckpt.load_optimizer(path, eng.flat) if saved_mesh == mesh_now else None
+            if saved_mesh != mesh_now:
+                self.telemetry.log("warn", "checkpoint", f"mesh changed {saved_mesh} -> {mesh_now}: "
+                                   "optimizer moments restart from zero")
+        else:
+            opt = self.ckpt.load_optimizer(path, eng.flat)
         if opt is not None:
             eng.flat.master.copy_(opt["master"].to(eng.flat.master))
             # Muon matrices are owned whole, round-robin over the ranks of THIS run

@@ -101,6 +101,32 @@ def main():
         if stage.embed_tokens is not None:
             assert torch.allclose(stage.embed_tokens.grad, full.embed_tokens.grad, atol=2e-5,
                                   rtol=1e-4)
+    elif what == "pipeline_trainer":
+        # `train` with runtime.pipeline_parallel_size = 2: the Trainer builds the pipeline
+        # engine, trains, and writes a checkpoint whose stages' tensors merge into one model
+        from ceo_b200.runtime.checkpoint import CheckpointManager
+        from ceo_b200.runtime.parallel_engine import PipelineEngine
+        from ceo_b200.runtime.trainer import Trainer
+        cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+        cfg.model.num_layers = 3
+        cfg.runtime.world_size, cfg.runtime.pipeline_parallel_size = world, 2
+        cfg.training.total_steps, cfg.training.global_batch_size = 4, 8
+        cfg.training.micro_batch_size, cfg.checkpoint.save_interval = 4, 2
+        cfg.checkpoint.async_save = False
+        tr = Trainer(cfg, "cpu", checkpoint_dir=os.path.join(out, "ck"))
+        assert isinstance(tr.engine, PipelineEngine) and tr.dp_world == world // 2
+        res = tr.run()
+        assert res["step"] == 4 and res["loss"] == res["loss"]
+        dist.barrier()
+        path = tr.ckpt.path_for(4)
+        assert CheckpointManager.validate(path) == [], CheckpointManager.validate(path)
+        merged = CheckpointManager.load_tensors(path)
+        mine = {k: v[0] for k, v in tr.engine.model.state_dict_shards().items()}
+        for k, v in mine.items():
+            assert torch.equal(merged[k], v), k
+        assert {f"blocks.{i}.mlp_down.weight" for i in range(3)} <= set(merged)
+        if rank == 0:
+            torch.save({"loss": res["loss"]}, os.path.join(out, "pp_done.pt"))
     comm.barrier()
     dist.destroy_process_group()
 

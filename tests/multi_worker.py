@@ -208,6 +208,59 @@ def main():
         par.close()
         if rank == 0:
             print(f"OK {what}", lp, ls)
+    elif what == "train_tp":
+        # the Trainer (what `efla-train train` builds) on a tensor-parallel mesh from the
+        # config: trains, saves a sharded checkpoint, and the merged tensors load into a
+        # single-GPU model that gives the same loss
+        import tempfile
+
+        import torch.distributed as dist
+
+        from ceo_b200.models.model import EflaLM
+        from ceo_b200.runtime.checkpoint import CheckpointManager
+        from ceo_b200.runtime.parallel_engine import ParallelEngine
+        from ceo_b200.runtime.trainer import Trainer
+        cfg = small_cfg(world)
+        cfg.model.num_heads, cfg.model.head_dim = 4, 128
+        cfg.data.seq_len = 256
+        cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 4
+        cfg.training.total_steps, cfg.checkpoint.save_interval = 2, 2
+        cfg.checkpoint.async_save = False
+        cfg.telemetry.metrics_interval = 1
+        cfg.runtime.tensor_parallel_size = world
+        box = [tempfile.mkdtemp() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tr = Trainer(cfg, checkpoint_dir=box[0])
+        assert isinstance(tr.engine, ParallelEngine) and tr.dp_world == 1
+        res = tr.run()
+        assert res["step"] == 2 and res["loss"] == res["loss"]
+        dist.barrier()
+        path = tr.ckpt.path_for(2)
+        assert CheckpointManager.validate(path) == [], CheckpointManager.validate(path)
+        merged = CheckpointManager.load_tensors(path)
+        data = SyntheticTokens(cfg.model.vocab_size, "zipf", 1.1, 7, 0)
+        tok, tgt = (t.cuda() for t in data.batch(2, 256))
+        with torch.no_grad():
+            lp = float(tr.engine.model(tok, tgt))
+        lp_all = Comm().all_gather_cat(torch.tensor([lp], device="cuda"))
+        single = EflaLM(cfg.model, "cuda", seed=99)
+        single.load_reference_state(merged)
+        with torch.no_grad():
+            ls = float(single(tok, tgt))
+        # each tensor-parallel rank scores its own row shard: their mean is the batch loss
+        assert abs(float(lp_all.mean()) - ls) < 2e-2 * abs(ls), (lp_all, ls)
+        tr2 = Trainer(cfg, checkpoint_dir=box[0])
+        md = tr2.resume()
+        assert md["step"] == 2 and tr2.engine.optimizer.step_count == 2
+        for a, b in zip(tr.engine.model.parameters(), tr2.engine.model.parameters()):
+            assert torch.equal(a, b)
+        assert torch.equal(tr.engine.flat.buffer("exp_avg"), tr2.engine.flat.buffer("exp_avg"))
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        tr.engine.close()
+        tr2.engine.close()
+        if rank == 0:
+            print("OK train_tp", lp_all.tolist(), ls)
     elif what == "pipeline":
         # two pipeline stages over NCCL point-to-point against the whole model on one GPU
         from ceo_b200.models.model import EflaLM

@@ -126,3 +126,57 @@ def test_run_with_recovery_resumes_after_injected_failure(tmp_path):
     tr2 = fault.run_with_recovery(lambda a: Trainer(cfg, "cpu", checkpoint_dir=str(tmp_path / "ck")),
                                   total_steps=8)
     assert tr2.engine.step_count == 8
+
+
+def test_train_command_builds_pipeline_engine_and_merged_checkpoint(tmp_path):
+    """runtime.pipeline_parallel_size = 2 on two gloo ranks: Trainer -> PipelineEngine, a
+    checkpoint written stage by stage that reads back as ONE model - also by a single-process
+    run of the same config without pipeline stages."""
+    _spawn("pipeline_trainer", 2, tmp_path)
+    assert (tmp_path / "pp_done.pt").exists()
+    from ceo_b200.runtime.trainer import Trainer
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    cfg.model.num_layers = 3
+    cfg.training.total_steps, cfg.training.global_batch_size = 6, 8
+    cfg.training.micro_batch_size = 4
+    cfg.checkpoint.save_interval = 0
+    tr = Trainer(cfg, "cpu", checkpoint_dir=str(tmp_path / "ck"))
+    md = tr.resume()   # pipeline size 2 -> 1: parameters load, the moments restart
+    assert md["step"] == 4 and tr.engine.step_count == 4
+    res = tr.run()
+    assert res["step"] == 6 and res["loss"] == res["loss"]
+
+
+def test_tensor_parallel_checkpoint_shards_merge_and_reload(tmp_path):
+    """Tensor-parallel ranks write their slices; the merged view equals the single-GPU model
+    drawn from the same seed, and loads at another tensor-parallel size."""
+    from types import SimpleNamespace
+
+    from ceo_b200.models.model import EflaLM
+    from ceo_b200.models.parallel_model import ParallelEflaLM
+    from ceo_b200.runtime.checkpoint import CheckpointManager
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "smoke_cpu.yaml"))
+    m = cfg.model
+    full = EflaLM(m, "cpu", dtype=torch.bfloat16, seed=3).state_dict_reference()
+    for r in reversed(range(2)):
+        pm = ParallelEflaLM(m, "cpu", tp=SimpleNamespace(rank=r, world=2), seed=3)
+        CheckpointManager(tmp_path / "ck", rank=r, world=2).save(
+            7, {}, {}, None, tensor_shards=pm.state_dict_shards(), shard_rank=r, shard_world=2,
+            shard_timeout=5.0)
+    path = str(tmp_path / "ck" / "step_00000007")
+    assert CheckpointManager.validate(path) == []
+    merged = CheckpointManager.load_tensors(path)
+    assert set(merged) == set(full)
+    for k, v in full.items():
+        assert torch.equal(merged[k], v), k
+    # ... into 4 tensor-parallel ranks, and into the unsharded model
+    for r in range(4):
+        fresh = ParallelEflaLM(m, "cpu", tp=SimpleNamespace(rank=r, world=4), seed=3)
+        other = ParallelEflaLM(m, "cpu", tp=SimpleNamespace(rank=r, world=4), seed=99)
+        other.load_reference_state(merged)
+        for (n, a), (_, b) in zip(fresh.named_parameters(), other.named_parameters()):
+            assert torch.equal(a, b), (r, n)
+    single = EflaLM(m, "cpu", dtype=torch.bfloat16, seed=99)
+    single.load_reference_state(merged)
+    assert all(torch.equal(v, full[k]) for k, v in single.state_dict_reference().items())
+    CheckpointManager.convert(path, tmp_path / "m.safetensors", "safetensors")

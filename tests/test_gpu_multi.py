@@ -76,3 +76,9 @@ def test_parallel_model_matches_single_gpu(what):
 def test_pipeline_stages_match_whole_model():
     out = _run("pipeline", 2)
     assert "OK pipeline" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_trainer_on_tensor_parallel_mesh_and_sharded_checkpoint():
+    out = _run("train_tp", 2)
+    assert "OK train_tp" in out
