@@ -160,6 +160,22 @@ int ceo_muon_apply(float* master, const void* y_bf16, void* shadow_bf16, long lo
                    float weight_decay, float scale, const float* gscale_ptr,
                    cudaStream_t stream);
 
+/* ---- PRISM refinement (one iteration in the head_dim-wide proxy space) -------------------
+ * gate: bd = sigmoid(bt) * gelu_tanh(p * rp), all (n) bf16, n a multiple of 8; the backward
+ * returns d(rp), d(p), d(bt) from d(bd).  update: r_out = r_in - c, out_out = out_in +
+ * scale * c in one pass (outputs may alias their inputs).  state: the recurrent state
+ * S_t = alpha S_{t-1} (I - b k^T) + sum_l bd^l k^l^T with b = sigmoid(bt1) * k^1 over T tokens;
+ * bd, k: (L, B, T, hd) bf16 (L <= 4), bt1: (B, T, hd) beta logits of iteration 1, s_in (may
+ * be null = zero) / s_out: (B, hd, hd) fp32, hd in {32, 64, 128}. */
+int ceo_prism_gate_fwd(const void* rp, const void* p, const void* bt, void* bd, long long n,
+                       cudaStream_t stream);
+int ceo_prism_gate_bwd(const void* dbd, const void* rp, const void* p, const void* bt, void* drp,
+                       void* dp, void* dbt, long long n, cudaStream_t stream);
+int ceo_prism_update(const void* c, const void* r_in, const void* out_in, void* r_out,
+                     void* out_out, long long n, float scale, cudaStream_t stream);
+int ceo_prism_state(const void* bd, const void* k, const void* bt1, const float* s_in,
+                    float* s_out, int B, int T, int hd, int L, float alpha, cudaStream_t stream);
+
 /* Bounds-checked debug build only (-DCEO_BOUNDS_CHECK; -1 otherwise): out[4] = {violations,
  * site, index, extent} of the first out-of-range index recorded since the last reset. */
 int ceo_bounds_status(long long* out, int reset);

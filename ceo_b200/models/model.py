@@ -49,6 +49,11 @@ def _lin(mod, name, x, w, residual=None):
     return fp8_linear(x, w, st[name], residual)
 
 
+class _StateList(list):
+    """The per-block EFLA states; a list that can also carry the PRISM decode caches."""
+    prism = None
+
+
 class Norm(nn.Module):
     def __init__(self, dim, kind, device, dtype):
         super().__init__()
@@ -177,10 +182,16 @@ class Block(nn.Module):
             h = self.mlp(n2, h)
         return h, s_final
 
-    def decode_step(self, h, state):
+    def decode_step(self, h, state, prism_cache=None):
         n1 = self.ln1(h)
         o = self.efla.decode_step(n1, state)
-        h = linear(o, self.efla.w_o, h)
+        if self.prism is not None:
+            if prism_cache is None:
+                raise ValueError("a block with PRISM needs its decode cache "
+                                 "(EflaLM.new_prism_caches)")
+            h = h + self.prism.decode_step(n1, linear(o, self.efla.w_o), prism_cache)
+        else:
+            h = linear(o, self.efla.w_o, h)
         return self.mlp(self.ln2(h), h)
 
 
@@ -260,15 +271,35 @@ class EflaLM(nn.Module):
     def new_states(self, batch, device=None):
         device = device or self.embed_tokens.device
         c = self.cfg
-        return [torch.zeros(batch, c.num_heads, c.head_dim, c.head_dim, dtype=torch.float32,
-                            device=device) for _ in self.blocks]
+        return _StateList(torch.zeros(batch, c.num_heads, c.head_dim, c.head_dim,
+                                      dtype=torch.float32, device=device) for _ in self.blocks)
+
+    def new_prism_caches(self, batch, device=None):
+        """Per-block PRISM decode caches (ShortConv window + recurrent state); None for blocks
+        without the PRISM branch."""
+        device = device or self.embed_tokens.device
+        return [blk.prism.new_cache(batch, device) if blk.prism is not None else None
+                for blk in self.blocks]
 
     @torch.no_grad()
-    def decode_step(self, token, states):
-        """token: (B,) ids; states: list of (B,H,d,d) fp32 updated in place -> logits (B,V)."""
+    def decode_step(self, token, states, prism_caches=None):
+        """token: (B,) ids; states: list of (B,H,d,d) fp32 updated in place -> logits (B,V).
+        With the PRISM branch enabled the caches live next to the states: they are attached to
+        the ``states`` list on first use (``states.prism``) unless passed explicitly."""
+        if prism_caches is None and any(b.prism is not None for b in self.blocks):
+            prism_caches = getattr(states, "prism", None)
+            if prism_caches is None:
+                prism_caches = self.new_prism_caches(token.shape[0], token.device)
+                try:
+                    states.prism = prism_caches
+                except AttributeError:  # a plain list cannot carry the caches
+                    raise ValueError("pass prism_caches=model.new_prism_caches(batch) to "
+                                     "decode_step, or create the states with new_states()")
+        if prism_caches is None:
+            prism_caches = [None] * len(self.blocks)
         h = K.embedding(token, self.embed_tokens)
-        for blk, st in zip(self.blocks, states):
-            h = blk.decode_step(h, st)
+        for blk, st, pc in zip(self.blocks, states, prism_caches):
+            h = blk.decode_step(h, st, pc)
         hn = self.final_norm(h)
         w = self.head_weight()
         if hn.is_cuda:

@@ -455,3 +455,49 @@ def test_trainer_packs_documents_and_prefetches(tmp_path):
     tr2._open_data()
     assert not tr2._packing and len(tr2._next_micro_batches()[0]) == 2
     tr2._close_data()
+
+
+def test_prism_gate_state_and_recurrent_decode():
+    """PRISM: the fused gate equals its formula, the layer's recurrent state equals the
+    token-serial recurrence, and token-by-token decoding reproduces the parallel forward."""
+    from ceo_b200.ops import prism as P
+    torch.manual_seed(0)
+    rp, p, bt = (torch.randn(3, 5, 16, requires_grad=True) for _ in range(3))
+    bd = P.gate(rp, p, bt)
+    want = torch.sigmoid(bt) * torch.nn.functional.gelu(p * rp, approximate="tanh")
+    assert torch.allclose(bd, want, atol=1e-6)
+    c, r, out = torch.randn(4, 8), torch.randn(4, 8), torch.randn(4, 8)
+    r2, o2 = P.update(c, r, out, 0.5)
+    assert torch.allclose(r2, r - c) and torch.allclose(o2, out + 0.5 * c)
+    # state: one call over T tokens == T calls over one token each
+    L, B, T, hd = 2, 2, 6, 8
+    bds, ks, bt1 = torch.randn(L, B, T, hd), torch.randn(L, B, T, hd) * 0.3, torch.randn(B, T, hd)
+    s_all = P.state(bds, ks, bt1, None, 0.9)
+    s = None
+    for t in range(T):
+        s = P.state(bds[:, :, t:t + 1], ks[:, :, t:t + 1], bt1[:, t:t + 1], s, 0.9)
+    assert torch.allclose(s, s_all, atol=1e-5)
+    # model with the PRISM branch: decode == forward
+    cfg = smoke_cfg()
+    cfg.model.prism.enabled = True
+    cfg.model.prism.num_iterations, cfg.model.prism.shortconv_window = 2, 4
+    model = EflaLM(cfg.model, "cpu", dtype=torch.float32, seed=0).eval()
+    tok = torch.randint(0, cfg.model.vocab_size, (2, 12))
+    with torch.no_grad():
+        logits = model(tok)
+        states = model.new_states(2)
+        step_logits = torch.stack([model.decode_step(tok[:, t], states) for t in range(12)], dim=1)
+    assert torch.allclose(step_logits, logits, atol=2e-4, rtol=1e-3)
+    pl = model.blocks[0].prism
+    x = torch.randn(2, 12, cfg.model.hidden_dim)
+    a = torch.randn(2, 12, cfg.model.hidden_dim)
+    with torch.no_grad():
+        out, st = pl(x, a, return_state=True)
+        cache = pl.new_cache(2, dtype=torch.float32)
+        for t in range(12):
+            o_t = pl.decode_step(x[:, t], a[:, t], cache)
+            assert torch.allclose(o_t, out[:, t], atol=1e-5)
+    assert st.shape == (2, cfg.model.head_dim, cfg.model.head_dim)
+    assert torch.allclose(cache["state"], st, atol=1e-5)
+    with pytest.raises(ValueError):
+        model.decode_step(tok[:, 0], [s for s in model.new_states(2)])
