@@ -6,7 +6,8 @@ The sources are compiled as shipped with the reference's flags (``-arch=sm_100 -
 dead kernel that uses an undeclared identifier and does not compile, so those lines are left
 out of the copy that is built.  Nothing of the reference is committed: the copies and the
 library live under the git-ignored ``baseline/_ref``.
-Usage: ``python baseline/build_ref_kernels.py [/path/to/reference]``.
+Usage: ``python baseline/build_ref_kernels.py /path/to/reference`` (or the path in the
+environment variable ``CEO_REFERENCE_DIR``).
 """
 import os
 import shutil
@@ -17,7 +18,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
 
-def main(ref="/root/reference"):
+def main(ref=None):
+    ref = ref or os.environ.get("CEO_REFERENCE_DIR")
+    if not ref:
+        print("usage: build_ref_kernels.py <reference tree>  (or set CEO_REFERENCE_DIR)")
+        return 2
     src = os.path.join(ref, "kernels", "cuda")
     if not os.path.isdir(src):
         print(f"reference kernels not found at {src}")

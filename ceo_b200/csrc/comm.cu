@@ -460,3 +460,42 @@ extern "C" int ceo_cp_exchange(const float* src, void* const* gather, void* cons
                                                status);
   return static_cast<int>(cudaGetLastError());
 }
+
+
+// ---------------------------------------------------------------------------------------
+// out[b] = P[b] s[b] + R[b]  (or P[b]^T s[b] + R[b]) for `nb` independent d x d fp32 matrices:
+// one step of folding a rank's affine state map onto the incoming state in context
+// parallelism.  fp32 on purpose (the maps compose over up to 8 ranks); the matrices are tiny
+// (d <= 128), so a 16 x 16 shared-memory tiling per CTA is enough.
+namespace ceo {
+__global__ void __launch_bounds__(256)
+fold_affine_kernel(const float* __restrict__ P, const float* __restrict__ s,
+                   const float* __restrict__ R, float* __restrict__ out, int d, int transpose) {
+  __shared__ float ps[16][17], ss[16][17];
+  const int tiles = d / 16;
+  const int b = blockIdx.x / (tiles * tiles), t = blockIdx.x % (tiles * tiles);
+  const int ti = t / tiles, tj = t % tiles, ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const long long base = static_cast<long long>(b) * d * d;
+  const int row = ti * 16 + ty, col = tj * 16 + tx;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < d; k0 += 16) {
+    // ps[ty][tx] = Pm[row][k0 + tx] with Pm = P or P^T
+    ps[ty][tx] = transpose ? P[base + static_cast<long long>(k0 + tx) * d + ti * 16 + ty]
+                           : P[base + static_cast<long long>(row) * d + k0 + tx];
+    ss[ty][tx] = s[base + static_cast<long long>(k0 + ty) * d + col];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc += ps[ty][k] * ss[k][tx];
+    __syncthreads();
+  }
+  out[base + static_cast<long long>(row) * d + col] = acc + R[base + static_cast<long long>(row) * d + col];
+}
+}  // namespace ceo
+
+extern "C" int ceo_fold_affine(const float* P, const float* s, const float* R, float* out, int nb,
+                               int d, int transpose, cudaStream_t stream) {
+  if (nb <= 0 || d <= 0 || (d & 15)) return -5;
+  const int tiles = d / 16;
+  fold_affine_kernel<<<nb * tiles * tiles, 256, 0, stream>>>(P, s, R, out, d, transpose);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -101,6 +101,18 @@ enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4,
 // order; with grp_m = row blocks per rank the kernel works through one rank's rows at a time
 // (local rows first for an all-gathered A, the other ranks' rows first for a reduce-scatter).
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int r, int& m_blk, int& n_blk) {
+  if (p.rs_on) {
+    // reduce-scatter: stripe by stripe (the lb-th row block of EVERY owner, the other ranks'
+    // first), so that all partials of a stripe arrive everywhere within one stripe's time and
+    // the reducer CTAs work through the stripes while later ones are still being computed
+    const int bpr = p.rs_rows_per_rank / BM;
+    const int per_stripe = p.world * p.num_n;
+    const int lb = r / per_stripe, rem = r - lb * per_stripe;
+    const int oi = rem / p.num_n;
+    n_blk = rem - oi * p.num_n;
+    m_blk = ((p.rank + 1 + oi) % p.world) * bpr + lb;
+    return;
+  }
   const int per_group = p.grp_m * p.num_n;
   const int g = r / per_group, rem = r - g * per_group;
   const int left = p.num_m - g * p.grp_m;           // the last group may be narrower
@@ -155,7 +167,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int total_tiles = tiles_per_batch * p.batch;
   constexpr int BKE = FP8 ? 2 * BK : BK;  // elements of K per stage
   const int num_kb = (p.K + BKE - 1) / BKE;
-  // the first ag_ctas CTAs only copy (all-gather); the others walk the output tiles
+  // the first ag_ctas CTAs are helpers: they copy (all-gather) or reduce (reduce-scatter);
+  // the others walk the output tiles
   const bool copy_cta = static_cast<int>(blockIdx.x) < p.ag_ctas;
   const int tile_step = static_cast<int>(gridDim.x) - p.ag_ctas;
   // split-K: a work unit is (k-slice, tile); slices of one tile accumulate into C with atomics
@@ -230,7 +243,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         // let any copy still in flight land before the CTA's shared memory goes away
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
       }
-      if (copy_cta) {
+      if (copy_cta && p.ag_operand) {
         // ---------------------------------------------------- all-gather copy CTA
         // Pulls row blocks of the peers' shards through a ring of shared-memory buffers with
         // bulk async copies (peer -> smem -> local gathered buffer), nearest peer first, and
@@ -657,16 +670,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                               1u);
       }
     }
-    if (p.rs_on && ok && !copy_cta) {
+    if (p.rs_on && ok && copy_cta) {
       // ---------------------------------------------------- reduce this rank's own rows
-      // Work item = one (row block, 256-column block) of the rows this rank owns; a block is
-      // complete when every source rank's counter for it has reached the target.
+      // (reducer CTAs only.)  Work item = one (row block, 256-column block) of the rows this
+      // rank owns, in stripe order; a row block is complete when every source rank's counter
+      // for it has reached the target.
       const int bpr = p.rs_rows_per_rank / BM;
       const int items = bpr * p.num_n;
       const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
       const unsigned* cnt = p.rs_count[p.rank];
-      for (int item = first_tile; item < items && ok; item += tile_step) {
-        const int lb = item % bpr, nb = item / bpr;
+      for (int item = static_cast<int>(blockIdx.x); item < items && ok; item += p.ag_ctas) {
+        const int lb = item / p.num_n, nb = item - lb * p.num_n;
         for (int src = 0; src < p.world; ++src) {
           if (!flag_wait_ge<true>(cnt + src * bpr + lb, p.rs_target)) {
             if (lane == 0) atomicCAS(p.status, 0, ST_RS_WAIT);
@@ -859,6 +873,7 @@ struct FusedDesc {
   void* rs_out = nullptr;
   const void* rs_residual = nullptr;
   long long rs_ldo = 0;
+  int rs_ctas = 0;                 // RS: CTAs that only reduce (0: 16)
 };
 
 static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -982,10 +997,10 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
     p.rs_residual = fz.rs_residual;
     p.rs_ldo = fz.rs_ldo;
     p.ldc = N;  // staging rows are dense
-    // other ranks' rows first, this rank's own rows last
-    // plain m-fastest order interleaves the owners, which spreads the peer stores evenly over
-    // the kernel instead of saturating NVLink during the first (world-1)/world of it
-    p.m_rot = ((fz.rank + 1) % fz.world) * (p.rs_rows_per_rank / BM);
+    // tile order: see tile_coords (stripes); a few CTAs do nothing but reduce
+    p.ag_ctas = fz.rs_ctas > 0 ? fz.rs_ctas : 16;
+    if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
+    if (p.ag_ctas < 1) p.ag_ctas = 1;
     p.grp_m = p.num_m;
   }
   long long total = static_cast<long long>(p.num_m) * p.num_n * batch;
@@ -1090,14 +1105,20 @@ extern "C" int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* 
 // GEMM fused with the reduce-scatter of its output over M: every rank computes the partial
 // product of its K-slice; out (M/world x N bf16, this rank's rows) = sum over ranks (+residual).
 // `stage`: table of per-rank staging buffers [world][M/world][N] bf16; `counters`: table of
-// per-rank unsigned[world][M/world/128]; target = 4 * ceil(N/256) * (number of calls so far).
+// per-rank unsigned[world][M/world/128], never reset: `target` is the value every counter of
+// this rank reaches when all partial tiles of THIS call have arrived (it grows by
+// 4 * ceil(N/256) per call as long as M stays the same).  rs_ctas CTAs (0 = 16) only reduce:
+// tiles are computed stripe by stripe so the reduction of a stripe overlaps the next ones.
+// Successive calls must alternate between two staging buffers (a rank can be one call ahead
+// of a peer that is still reducing), which replaces a barrier between calls.
 extern "C" int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
                                 long long ldb, int a_mn_major, int b_mn_major, float alpha,
                                 void* const* stage, void* const* counters, unsigned int target,
                                 void* out, const void* residual, long long ldo, int rank,
-                                int world, int* status, cudaStream_t stream) {
+                                int world, int rs_ctas, int* status, cudaStream_t stream) {
   FusedDesc fz;
   fz.kind = 3;
+  fz.rs_ctas = rs_ctas;
   fz.rank = rank;
   fz.world = world;
   fz.peers = stage;

@@ -267,18 +267,24 @@ int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void
 /* GEMM fused with the reduce-scatter of its output over M (epilogue stores partial tiles
  * into the owner's staging area over NVLink and bumps its counters; each rank then reduces
  * its own rows, adding an optional bf16 residual).  stage[r]: [world][M/world][N] bf16;
- * counters[r]: unsigned[world][M/world/128], zeroed once; target = 4*ceil(N/256)*calls.
- * Call ceo_symm_barrier first so no rank is still reducing the previous call. */
+ * counters[r]: unsigned[world][M/world/128], zeroed once and never reset: target is the value
+ * they reach when this call's tiles have all arrived (+ 4*ceil(N/256) per call with the same
+ * M).  rs_ctas CTAs (0 = 16) only reduce, stripe by stripe, while the others compute.
+ * Successive calls alternate between two staging buffers instead of a barrier between them. */
 int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
                      long long ldb, int a_mn_major, int b_mn_major, float alpha,
                      void* const* stage, void* const* counters, unsigned int target, void* out,
-                     const void* residual, long long ldo, int rank, int world, int* status,
-                     cudaStream_t stream);
+                     const void* residual, long long ldo, int rank, int world, int rs_ctas,
+                     int* status, cudaStream_t stream);
 /* Context-parallel exchange: store `n` floats into slot `rank` of every rank's gather buffer
  * (n floats per slot) and barrier, in one launch.  done_counter: local unsigned, zero. */
 int ceo_cp_exchange(const float* src, void* const* gather, void* const* flags, long long n,
                     int rank, int world, unsigned int epoch, unsigned int* done_counter,
                     int* status, cudaStream_t stream);
+/* out[b] = P[b] s[b] + R[b] (transpose: P[b]^T) for nb d x d fp32 matrices, d a multiple of 16:
+ * one step of composing a rank's affine state map in context parallelism. */
+int ceo_fold_affine(const float* P, const float* s, const float* R, float* out, int nb, int d,
+                    int transpose, cudaStream_t stream);
 /* One cooperative launch per rank: reduce-scatter of the fp32 gradients (peer loads) ->
  * global-norm clip -> AdamW (kind 0) or Lion (kind 1; v unused) on the rank's fp32 master
  * shard -> bf16 parameters stored into every rank's buffer -> this rank's gradient buffer

@@ -47,28 +47,50 @@ class CPContext:
         self.comm, self.rank, self.world = comm, comm.rank, comm.world
         self.d, self.max_bh = d, max_bh
         self.slot_floats = 2 * max_bh * d * d
-        self.gather = SymmetricBuffer(self.world * self.slot_floats * 4, comm.group)
+        # two gather areas used alternately: the kernel's own barrier says every rank has
+        # STORED its block of this call, which (stream order) it only does after it has consumed
+        # the call before - so when a rank writes an area again, two calls later, nobody reads
+        # it any more.  No barrier before the exchange, no copy of the result.
+        self.half_bytes = self.world * self.slot_floats * 4
+        self.gather = SymmetricBuffer(2 * self.half_bytes, comm.group)
+        self.calls = 0
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.done = torch.zeros(1, dtype=torch.int32, device=self.dev)
 
     def exchange(self, block: torch.Tensor) -> torch.Tensor:
         """block: fp32 tensor (same numel on every rank).  Returns (world, *block.shape): slot s
-        = rank s's block."""
+        = rank s's block - a view of the gather area, valid until the exchange after the next
+        one (consume it, or copy what must live longer)."""
         n = block.numel()
         assert n % 4 == 0 and n <= self.slot_floats and block.dtype == torch.float32
         block = block.contiguous()
-        # slots are n floats apart for this call; nobody may still be reading the previous one
-        self.comm.device_barrier()
+        self.calls += 1
+        off = (self.calls & 1) * self.half_bytes
         L = _lib.lib()
-        _lib.check(L.ceo_cp_exchange(block.data_ptr(), self.gather.table(),
+        _lib.check(L.ceo_cp_exchange(block.data_ptr(), self.gather.table(off),
                                      self.comm.ctrl.table(), n, self.rank, self.world,
                                      self.comm._next_epoch(), self.done.data_ptr(),
                                      _lib.status_word(self.dev).data_ptr(), _lib.stream()),
                    "ceo_cp_exchange")
-        return self.gather.view(torch.float32, self.world * n).view(self.world, *block.shape).clone()
+        return self.gather.view(torch.float32, self.world * n, off).view(self.world, *block.shape)
 
     def close(self):
         self.gather.close()
+
+
+def fold_affine(P, s, R, transpose: bool = False):
+    """``P s + R`` (or ``P^T s + R``) for batches of d x d fp32 matrices: one step of
+    composing a rank's affine state map onto a state.  Runs on the library's own fp32 kernel
+    (``ceo_fold_affine``); the first step of a fold (s = 0) just returns R."""
+    if not P.is_cuda:
+        return torch.matmul(P.transpose(-1, -2) if transpose else P, s) + R
+    d = P.shape[-1]
+    nb = P.numel() // (d * d)
+    P, s, R = P.contiguous(), s.contiguous(), R.contiguous()
+    out = torch.empty_like(s)
+    _lib.check(_lib.lib().ceo_fold_affine(P.data_ptr(), s.data_ptr(), R.data_ptr(), out.data_ptr(),
+                                          nb, d, int(transpose), _lib.stream()), "ceo_fold_affine")
+    return out
 
 
 class _CPDeltaRule(torch.autograd.Function):
@@ -96,7 +118,7 @@ class _CPDeltaRule(torch.autograd.Function):
         allmaps = cp.exchange(torch.stack([P, R]))          # (G, 2, B, H, d, d)
         s_in = torch.zeros_like(R)
         for j in range(cp.rank):                            # fold the maps of earlier ranks
-            s_in = torch.matmul(allmaps[j, 0], s_in) + allmaps[j, 1]
+            s_in = fold_affine(allmaps[j, 0], s_in, allmaps[j, 1])
         s_out = torch.empty_like(R)
         _stage(1, dict(base, s0=s_in, s_final=s_out), strides, B, T, H, d)
         _stage(2, base, strides, B, T, H, d)
@@ -127,7 +149,7 @@ class _CPDeltaRule(torch.autograd.Function):
         allq = cp.exchange(Q)                                              # (G, B, H, d, d)
         ds_out = torch.zeros_like(Q)
         for j in range(cp.world - 1, cp.rank, -1):                          # fold from the end
-            ds_out = torch.matmul(Pall[j].transpose(-1, -2), ds_out) + allq[j]
+            ds_out = fold_affine(Pall[j], ds_out, allq[j], transpose=True)
         ds0 = torch.empty_like(Q)
         _stage(4, dict(base, ds_final=ds_out, ds0=ds0), strides, B, T, H, d)
         _stage(5, base, strides, B, T, H, d)

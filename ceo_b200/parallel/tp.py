@@ -36,8 +36,17 @@ class TPContext:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
         nb = max_rows * max_cols * 2
-        self.gather = SymmetricBuffer(nb, self.group)        # AG destination (rows x K)
-        self.stage = SymmetricBuffer(nb, self.group)         # RS staging [world][rows/world][N]
+        # AG destination (rows x K), twice: calls alternate between the halves, so a rank that
+        # is already filling in its shard for the next call cannot disturb a peer that is still
+        # pulling the previous one (no barrier after the kernel)
+        self.gather = SymmetricBuffer(2 * nb, self.group)
+        self.gather_half = nb
+        # RS staging [world][rows/world][N], twice: successive calls alternate between the two
+        # halves (a rank may be one call ahead of a peer that still reduces the previous one)
+        self.stage = SymmetricBuffer(2 * nb, self.group)
+        self.stage_half = nb
+        self.rs_calls = 0
+        self.rs_rows = None
         nblk = (max_rows + 127) // 128
         self.counters = SymmetricBuffer(self.world * nblk * 4, self.group)
         self.ag_flags = torch.zeros(nblk, dtype=torch.int32, device=dev)
@@ -56,12 +65,15 @@ class TPContext:
         rows, K = x_shard.shape
         M = rows * self.world
         N = w.shape[1] if w_mn else w.shape[0]
-        assert M * K * 2 <= self.gather.nbytes and rows % 128 == 0
-        full = self.gather.view(torch.bfloat16, M * K).view(M, K)
-        full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
-        self.barrier()  # every rank's shard is in place
-        out = torch.empty(M, N, dtype=out_dtype, device=self.dev)
+        assert M * K * 2 <= self.gather_half and rows % 128 == 0
         self.ag_calls += 1
+        half = (self.ag_calls & 1) * self.gather_half
+        full = self.gather.view(torch.bfloat16, M * K, half).view(M, K)
+        full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
+        # every rank's shard is in place - and every rank has finished the call before last,
+        # which used this half of the buffer
+        self.barrier()
+        out = torch.empty(M, N, dtype=out_dtype, device=self.dev)
         # enough copy CTAs to keep NVLink busy when the transfer, not the math, is the bound:
         # one copy CTA sustains roughly 40 GB/s (six 32 KB bulk copies in flight)
         comm_s = (self.world - 1) / self.world * M * K * 2 / 770e9
@@ -69,7 +81,7 @@ class TPContext:
         ratio = comm_s / max(math_s, 1e-9)
         copy_ctas = self.copy_ctas if ratio < 0.3 else (16 if ratio < 0.6 else 24)
         L = _lib.lib()
-        _lib.check(L.ceo_ag_gemm_bf16(self.gather.table(), 1, w.data_ptr(), out.data_ptr(), M, N, K,
+        _lib.check(L.ceo_ag_gemm_bf16(self.gather.table(half), 1, w.data_ptr(), out.data_ptr(), M, N, K,
                                       w.stride(0), out.stride(0), int(w_mn),
                                       int(out_dtype == torch.float32), 0, 1.0, None, 0,
                                       self.ag_flags.data_ptr(), self.ag_calls, self.rank,
@@ -77,7 +89,6 @@ class TPContext:
                                       _lib.status_word(self.dev).data_ptr(), _lib.stream()),
                    "ceo_ag_gemm_bf16")
         saved = full.clone() if keep_gathered else None
-        self.barrier()  # nobody overwrites its shard while a peer is still pulling it
         return (out, saved) if keep_gathered else out
 
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False,
@@ -87,20 +98,31 @@ class TPContext:
         M, K = a.shape
         N = w.shape[1] if w_mn else w.shape[0]
         rows = M // self.world
-        assert M % self.world == 0 and rows % 128 == 0 and M * N * 2 <= self.stage.nbytes
+        assert M % self.world == 0 and rows % 128 == 0 and M * N * 2 <= self.stage_half
         assert M // 128 <= self.nblk
         out = torch.empty(rows, N, dtype=torch.bfloat16, device=self.dev)
-        # This rank's previous reduction has consumed every increment sent to it, so its
-        # counters can be cleared; the barrier then tells the peers they may send again.
-        self.counters.view(torch.int32, self.world * self.nblk).zero_()
-        self.barrier()
-        self.rs_target = 4 * ((N + 255) // 256)
+        if self.rs_rows != rows:
+            # another row count re-maps the counters: start over behind a barrier (every rank
+            # has then consumed what was sent to it)
+            self.barrier()
+            self.counters.view(torch.int32, self.world * self.nblk).zero_()
+            self.barrier()
+            self.rs_target, self.rs_rows = 0, rows
+        # counters only grow: no reset and no barrier between calls of the same shape
+        self.rs_target += 4 * ((N + 255) // 256)
+        self.rs_calls += 1
+        # more reducer CTAs when the transfer, not the math, bounds the kernel
+        comm_s = (self.world - 1) / self.world * M * N * 2 / 770e9
+        math_s = 2.0 * M * N * K / 1.4e15
+        ratio = comm_s / max(math_s, 1e-9)
+        rs_ctas = 8 if ratio < 0.3 else (16 if ratio < 1.0 else 24)
         L = _lib.lib()
         _lib.check(L.ceo_gemm_rs_bf16(a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
-                                      w.stride(0), 0, int(w_mn), 1.0, self.stage.table(),
+                                      w.stride(0), 0, int(w_mn), 1.0,
+                                      self.stage.table((self.rs_calls & 1) * self.stage_half),
                                       self.counters.table(), self.rs_target, out.data_ptr(),
                                       _lib.ptr(residual),
-                                      out.stride(0), self.rank, self.world,
+                                      out.stride(0), self.rank, self.world, rs_ctas,
                                       _lib.status_word(self.dev).data_ptr(), _lib.stream()),
                    "ceo_gemm_rs_bf16")
         return out

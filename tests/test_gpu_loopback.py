@@ -260,7 +260,7 @@ def test_gemm_reduce_scatter_loopback():
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
     _lib.check(L.ceo_gemm_rs_bf16(a.data_ptr(), w.data_ptr(), M, N, K, K, K, 0, 0, 1.0,
                                   table(stage), table(cnt), target, out.data_ptr(), res.data_ptr(),
-                                  N, 0, 2, st.data_ptr(), _lib.stream()), "ceo_gemm_rs_bf16")
+                                  N, 0, 2, 4, st.data_ptr(), _lib.stream()), "ceo_gemm_rs_bf16")
     torch.cuda.synchronize()
     assert _lib.read_status() == 0
     full = a.float() @ w.float().t()
@@ -269,3 +269,21 @@ def test_gemm_reduce_scatter_loopback():
     # the partial tiles for the peer's rows went to the peer's staging area, slot of rank 0
     assert _rel(stage[1][0], full[rows:]) < 6e-3
     assert int(cnt[1][0].min()) == target
+
+
+def test_fold_affine_matches_fp32_matmul():
+    from ceo_b200.parallel.cp import fold_affine
+    torch.manual_seed(3)
+    for d in (64, 128):
+        P = torch.randn(3, 2, d, d, device=DEV)
+        s = torch.randn(3, 2, d, d, device=DEV)
+        R = torch.randn(3, 2, d, d, device=DEV)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            want = torch.matmul(P, s) + R
+            want_t = torch.matmul(P.transpose(-1, -2), s) + R
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+        assert _rel(fold_affine(P, s, R), want) < 1e-5
+        assert _rel(fold_affine(P, s, R, transpose=True), want_t) < 1e-5

@@ -74,7 +74,7 @@ def test_model_with_prism_trains_and_decodes():
 
 
 def test_dropout_kernel_matches_hash_mask_and_backward():
-    x = torch.randn(1000, 77, device=DEV).bfloat16().requires_grad_()   # odd size: tail path
+    x = torch.randn(1001, 77, device=DEV).bfloat16().requires_grad_()   # odd size: tail path
     y = K.dropout(x, 0.2, seed=123)
     keep = K.dropout_keep_mask(x.numel(), 0.2, 123, DEV).view(x.shape)
     want = torch.where(keep, x.float() / 0.8, torch.zeros_like(x, dtype=torch.float32))
