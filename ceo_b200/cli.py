@@ -54,13 +54,48 @@ def _options(args: ArgParser, spec: dict) -> dict:
     return out
 
 
-def _comm():
+def _runtime(cfg=None, log=None):
+    """Joins the launched job and looks at the machine (the reference's
+    ``DistributedRuntime.init`` + ``Topology.detect``, src/runtime/main.zig:192-240, 322-391):
+    device bound, process group up, every rank on Blackwell, peer access between all local
+    GPUs checked before any peer-mapped buffer is opened."""
+    from .runtime.device import DistributedRuntime, Topology, device_count
+    rt = DistributedRuntime.init(None)
+    peer_ok = False
+    if device_count():
+        d = rt.device
+        if log:
+            free, total = rt.get_memory_info()
+            log("info", "runtime", f"rank {rt.rank}/{rt.world_size} on cuda:{rt.local_rank} "
+                f"{d.name} sm_{d.major}{d.minor} {d.sm_count} SMs, {free / 2**30:.1f} of "
+                f"{total / 2**30:.1f} GiB free")
+        if not rt.all_blackwell() and log:
+            log("warn", "runtime", "not every rank runs on a Blackwell (sm_100) GPU: the kernel "
+                "library is built for sm_100a only")
+        if rt.world_size > 1:
+            try:
+                rt.enable_peer_access()
+                peer_ok = True
+            except Exception as e:  # noqa: BLE001
+                if log:
+                    log("warn", "runtime", f"{e}: falling back to library collectives")
+        if log and rt.rank == 0:
+            try:
+                topo = Topology.detect()
+                log("info", "runtime", f"topology: {len(topo.numa_nodes)} NUMA node(s), " +
+                    ", ".join(f"gpu{a.gpu_id}->numa{a.numa_node}" for a in topo.gpu_affinity))
+            except Exception as e:  # noqa: BLE001  (topology is informational)
+                log("debug", "runtime", f"topology not available: {e}")
+    return rt, peer_ok
+
+
+def _comm(peer_ok: bool = True):
     from .parallel.comm import Comm, init_distributed
     rank, world, local = init_distributed()
     if world == 1:
         return None
     import torch
-    if torch.cuda.is_available():
+    if torch.cuda.is_available() and peer_ok:
         try:
             from .parallel.fused import FusedComm
             return FusedComm()
@@ -108,8 +143,9 @@ def run_train(args: ArgParser) -> int:
     rt.world_size = world
     # the model-parallel engines build their own groups; plain data parallelism gets the
     # peer-memory communicator (library collectives when that is unavailable)
-    comm = _comm() if mp == 1 else None
     tel = Telemetry(cfg.telemetry, rank=rank)
+    _, peer_ok = _runtime(cfg, tel.log)
+    comm = _comm(peer_ok) if mp == 1 else None
     for w in cfg.model.validate():
         tel.log("warn", "config", w)
     cfg.training.validate()

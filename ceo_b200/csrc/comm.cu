@@ -117,13 +117,18 @@ __device__ __forceinline__ float reduce_ranges(const PeerPtrs& grads, const ZRan
     float* gl = reinterpret_cast<float*>(grads.p[rank]) + base;
     const long long n4 = rg.len >> 2;
     for (long long i = tid; i < n4; i += nth) {
+      // all ranks' loads are issued before any is consumed (one load in flight per thread
+      // leaves the links idle); the sum runs in rank order, so it is the same on every run
+      float4 g[MAXR];
+#pragma unroll
+      for (int r = 0; r < MAXR; ++r)
+        if (r < world)  // L2-only load: peer data must never be served from a stale L1 line
+          g[r] = __ldcg(reinterpret_cast<const float4*>(
+                            reinterpret_cast<const float*>(grads.p[r]) + base) + i);
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < world; ++r) {
-        // L2-only load: peer data must never be served from a stale L1 line
-        const float4 g = __ldcg(reinterpret_cast<const float4*>(
-                                    reinterpret_cast<const float*>(grads.p[r]) + base) + i);
-        s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-      }
+#pragma unroll
+      for (int r = 0; r < MAXR; ++r)
+        if (r < world) { s.x += g[r].x; s.y += g[r].y; s.z += g[r].z; s.w += g[r].w; }
       reinterpret_cast<float4*>(gl)[i] = s;
       ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
     }

@@ -121,6 +121,87 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int r, int& m_b
   n_blk = (rem / gsz + p.n_rot) % p.num_n;
 }
 
+// Reducer CTAs of the GEMM -> reduce-scatter kernel.  Work item = one (row block, 256-column
+// block) of the rows this rank owns, in stripe order (the order the partial tiles are produced
+// in everywhere); an item is ready when every source rank's counter for its row block has
+// reached the target.  A warp takes 8 rows of an item at a time and keeps RU rows x W sources
+// of 16-byte loads in flight per lane (W x RU = 16): with few CTAs reducing, memory-level
+// parallelism per CTA is what bounds the reduction.
+template <int W, int RU>
+__device__ __forceinline__ void rs_reduce(const GemmParams& p, int warp, int lane) {
+  const int bpr = p.rs_rows_per_rank / BM;
+  const int items = bpr * p.num_n;
+  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
+  const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(p.rs_residual);
+  __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.rs_out);
+  const unsigned* cnt = p.rs_count[p.rank];
+  constexpr int GROUP = 8, GPI = BM / GROUP, WARPS = GEMM_THREADS / 32;
+  const int my_items = static_cast<int>(blockIdx.x) < items
+                           ? (items - static_cast<int>(blockIdx.x) + p.ag_ctas - 1) / p.ag_ctas
+                           : 0;
+  int ready_item = -1;
+  const int c = lane * 8;  // a warp covers one 256-column row segment per row
+  for (int u = warp; u < my_items * GPI; u += WARPS) {
+    const int item = static_cast<int>(blockIdx.x) + (u / GPI) * p.ag_ctas, grp = u % GPI;
+    const int lb = item / p.num_n, nb = item - lb * p.num_n;
+    if (item != ready_item) {
+      for (int src = 0; src < p.world; ++src)
+        if (!flag_wait_ge<true>(cnt + src * bpr + lb, p.rs_target)) {
+          if (lane == 0) atomicCAS(p.status, 0, ST_RS_WAIT);
+          return;
+        }
+      ready_item = item;
+    }
+    if (c >= min(BN, p.N - nb * BN)) continue;
+#pragma unroll 1
+    for (int rr = 0; rr < GROUP; rr += RU) {
+      const int row0 = lb * BM + grp * GROUP + rr;  // rows within this rank's slice
+      uint4 part[RU][W];
+      uint4 resv[RU];
+#pragma unroll
+      for (int q = 0; q < RU; ++q) {
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < p.world)
+            part[q][src] = __ldcg(reinterpret_cast<const uint4*>(
+                stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row0 + q) * p.ldc +
+                nb * BN + c));
+        if (resid)
+          resv[q] = *reinterpret_cast<const uint4*>(resid + (row0 + q) * p.rs_ldo + nb * BN + c);
+      }
+#pragma unroll
+      for (int q = 0; q < RU; ++q) {
+        float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < p.world) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[q][src]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 x = __bfloat1622float2(h[j]);
+              acc8[2 * j] += x.x;
+              acc8[2 * j + 1] += x.y;
+            }
+          }
+        if (resid) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&resv[q]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 x = __bfloat1622float2(h[j]);
+            acc8[2 * j] += x.x;
+            acc8[2 * j + 1] += x.y;
+          }
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
+        *reinterpret_cast<uint4*>(outp + (row0 + q) * p.rs_ldo + nb * BN + c) = o;
+      }
+    }
+  }
+}
+
 // FP8 = 1: both operands are K-major 8-bit floats; a stage row is still 128 bytes, i.e. 128
 // elements of K, and one MMA covers 32 of them.
 template <int A_MN, int B_MN, int FP8 = 0>
@@ -176,7 +257,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
   const int first_tile = copy_cta ? total_units : static_cast<int>(blockIdx.x) - p.ag_ctas;
 
-  if (warp == 0) {
+  if (p.rs_on && copy_cta) {
+    // ------------------------------------------------ reduce-scatter: reducer CTA
+    // All six warps reduce this rank's own rows from the staged partial tiles, item by item in
+    // stripe order, while the other CTAs compute.
+    if (p.world <= 2) rs_reduce<2, 8>(p, warp, lane);
+    else if (p.world <= 4) rs_reduce<4, 4>(p, warp, lane);
+    else rs_reduce<8, 2>(p, warp, lane);
+  } else if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       int s = 0;
@@ -670,79 +758,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                               1u);
       }
     }
-    if (p.rs_on && ok && copy_cta) {
-      // ---------------------------------------------------- reduce this rank's own rows
-      // (reducer CTAs only.)  Work item = one (row block, 256-column block) of the rows this
-      // rank owns, in stripe order; a row block is complete when every source rank's counter
-      // for it has reached the target.
-      const int bpr = p.rs_rows_per_rank / BM;
-      const int items = bpr * p.num_n;
-      const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
-      const unsigned* cnt = p.rs_count[p.rank];
-      for (int item = static_cast<int>(blockIdx.x); item < items && ok; item += p.ag_ctas) {
-        const int lb = item / p.num_n, nb = item - lb * p.num_n;
-        for (int src = 0; src < p.world; ++src) {
-          if (!flag_wait_ge<true>(cnt + src * bpr + lb, p.rs_target)) {
-            if (lane == 0) atomicCAS(p.status, 0, ST_RS_WAIT);
-            ok = false;
-            break;
-          }
-        }
-        if (!ok) break;
-        const int ncols = min(BN, p.N - nb * BN);
-        const int c = lane * 8;  // a warp covers one 256-column row segment per row
-        constexpr int RU = 4;    // rows in flight per warp: all their loads are issued first
-        for (int rr = 0; rr < 32 && c < ncols; rr += RU) {
-          const int row0 = lb * BM + quad * 32 + rr;  // rows within this rank's slice
-          uint4 part[RU][8];
-          uint4 resv[RU];
-#pragma unroll
-          for (int u = 0; u < RU; ++u) {
-#pragma unroll
-            for (int src = 0; src < 8; ++src)
-              if (src < p.world)
-                part[u][src] = __ldcg(reinterpret_cast<const uint4*>(
-                    stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row0 + u) * p.ldc +
-                    nb * BN + c));
-            if (p.rs_residual)
-              resv[u] = *reinterpret_cast<const uint4*>(
-                  reinterpret_cast<const __nv_bfloat16*>(p.rs_residual) + (row0 + u) * p.rs_ldo +
-                  nb * BN + c);
-          }
-#pragma unroll
-          for (int u = 0; u < RU; ++u) {
-            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int src = 0; src < 8; ++src)
-              if (src < p.world) {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[u][src]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 x = __bfloat1622float2(h[j]);
-                  acc8[2 * j] += x.x;
-                  acc8[2 * j + 1] += x.y;
-                }
-              }
-            if (p.rs_residual) {
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&resv[u]);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 x = __bfloat1622float2(h[j]);
-                acc8[2 * j] += x.x;
-                acc8[2 * j + 1] += x.y;
-              }
-            }
-            uint4 o;
-            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_out) +
-                                      (row0 + u) * p.rs_ldo + nb * BN + c) = o;
-          }
-        }
-      }
-    }
   }
 
   tc_fence_before();
@@ -873,7 +888,7 @@ struct FusedDesc {
   void* rs_out = nullptr;
   const void* rs_residual = nullptr;
   long long rs_ldo = 0;
-  int rs_ctas = 0;                 // RS: CTAs that only reduce (0: 16)
+  int rs_ctas = 0;                 // RS: CTAs that only reduce (0: 32)
 };
 
 static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -998,8 +1013,8 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
     p.rs_ldo = fz.rs_ldo;
     p.ldc = N;  // staging rows are dense
     // tile order: see tile_coords (stripes); a few CTAs do nothing but reduce
-    p.ag_ctas = fz.rs_ctas > 0 ? fz.rs_ctas : 16;
-    if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
+    p.ag_ctas = fz.rs_ctas > 0 ? fz.rs_ctas : 32;
+    if (p.ag_ctas > cap / 3) p.ag_ctas = cap / 3;
     if (p.ag_ctas < 1) p.ag_ctas = 1;
     p.grp_m = p.num_m;
   }
@@ -1107,7 +1122,7 @@ extern "C" int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* 
 // `stage`: table of per-rank staging buffers [world][M/world][N] bf16; `counters`: table of
 // per-rank unsigned[world][M/world/128], never reset: `target` is the value every counter of
 // this rank reaches when all partial tiles of THIS call have arrived (it grows by
-// 4 * ceil(N/256) per call as long as M stays the same).  rs_ctas CTAs (0 = 16) only reduce:
+// 4 * ceil(N/256) per call as long as M stays the same).  rs_ctas CTAs (0 = 32) only reduce:
 // tiles are computed stripe by stripe so the reduction of a stripe overlaps the next ones.
 // Successive calls must alternate between two staging buffers (a rank can be one call ahead
 // of a peer that is still reducing), which replaces a barrier between calls.

@@ -269,7 +269,7 @@ int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void
  * its own rows, adding an optional bf16 residual).  stage[r]: [world][M/world][N] bf16;
  * counters[r]: unsigned[world][M/world/128], zeroed once and never reset: target is the value
  * they reach when this call's tiles have all arrived (+ 4*ceil(N/256) per call with the same
- * M).  rs_ctas CTAs (0 = 16) only reduce, stripe by stripe, while the others compute.
+ * M).  rs_ctas CTAs (0 = 32) only reduce, stripe by stripe, while the others compute.
  * Successive calls alternate between two staging buffers instead of a barrier between them. */
 int ceo_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
                      long long ldb, int a_mn_major, int b_mn_major, float alpha,

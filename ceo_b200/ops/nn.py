@@ -288,7 +288,7 @@ def dropout(x: torch.Tensor, p: float, training: bool = True, seed: int | None =
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, table):
-        flat = ids.reshape(-1).to(torch.int64)
+        flat = ids.reshape(-1).to(torch.int64).contiguous()
         V, D = table.shape
         out = torch.empty(flat.numel(), D, dtype=table.dtype, device=table.device)
         _lib.check(_lib.lib().ceo_embedding_fwd(flat.data_ptr(), table.data_ptr(), out.data_ptr(),
@@ -326,6 +326,20 @@ def embedding(ids, table):
 
 
 # ------------------------------------------------------------- LM head + cross-entropy
+_pools = {}
+
+
+def _workspace(device, nbytes: int):
+    """The device's workspace pool (``utils.layout.MemoryPool``), grown when a call needs more."""
+    from ..utils.layout import MemoryPool
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    pool = _pools.get(key)
+    if pool is None or pool.buf.numel() < nbytes:
+        pool = MemoryPool(nbytes, device)
+        _pools[key] = pool
+    return pool
+
+
 class _LinearCrossEntropyFn(torch.autograd.Function):
     """mean CE of ``x @ W^T`` against targets, row-chunked: logits exist only for one chunk
     at a time (fp32, from the GEMM epilogue); the CE kernel writes d(logits) in bf16 and the
@@ -335,7 +349,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
     def forward(ctx, x, weight, targets, label_smoothing, ignore_index, chunk_rows):
         D = x.shape[-1]
         x2 = x.reshape(-1, D)
-        t = targets.reshape(-1).to(torch.int64)
+        t = targets.reshape(-1).to(torch.int64).contiguous()
         rows, V = x2.shape[0], weight.shape[0]
         n_valid = (t != ignore_index).sum().clamp(min=1).to(torch.float32)
         inv = (1.0 / n_valid).reshape(1)
@@ -348,8 +362,12 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
             dw = torch.zeros(V, D, dtype=torch.float32, device=x.device)
         L = _lib.lib()
         cr = min(chunk_rows, rows)
-        logits = torch.empty(cr, V, dtype=torch.float32, device=x.device)
-        dlog = torch.empty(cr, V, dtype=torch.bfloat16, device=x.device) if need_grad else None
+        # logits and d(logits) of a chunk live in a step-scoped workspace pool (one buffer per
+        # device, re-used by every call: both are dead when this function returns)
+        pool = _workspace(x.device, cr * V * 6 + 1024)
+        pool.reset()
+        logits = pool.allocate((cr, V), torch.float32)
+        dlog = pool.allocate((cr, V), torch.bfloat16) if need_grad else None
         for r0 in range(0, rows, cr):
             r1 = min(rows, r0 + cr)
             n = r1 - r0
@@ -399,7 +417,7 @@ def cross_entropy_rows(logits, targets, label_smoothing: float = 0.0, ignore_ind
     l2 = logits.reshape(-1, logits.shape[-1])
     if l2.dtype not in (torch.float32, torch.bfloat16) or not l2.is_contiguous():
         l2 = l2.float().contiguous()
-    t = targets.reshape(-1).to(torch.int64)
+    t = targets.reshape(-1).to(torch.int64).contiguous()
     out = torch.empty(l2.shape[0], dtype=torch.float32, device=logits.device)
     _lib.check(_lib.lib().ceo_cross_entropy(l2.data_ptr(), int(l2.dtype == torch.float32),
                                             t.data_ptr(), out.data_ptr(), None, l2.shape[0],

@@ -115,7 +115,7 @@ class TPContext:
         comm_s = (self.world - 1) / self.world * M * N * 2 / 770e9
         math_s = 2.0 * M * N * K / 1.4e15
         ratio = comm_s / max(math_s, 1e-9)
-        rs_ctas = 8 if ratio < 0.3 else (16 if ratio < 1.0 else 24)
+        rs_ctas = 24 if ratio < 0.3 else (32 if ratio < 1.0 else 40)
         L = _lib.lib()
         _lib.check(L.ceo_gemm_rs_bf16(a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
                                       w.stride(0), 0, int(w_mn), 1.0,

@@ -88,3 +88,22 @@ def test_softmax_over_any_dimension():
     z = torch.randn(6, 33, 20, device=DEV)
     for dim in (0, 1, 2):
         assert torch.allclose(K.softmax(z, dim), torch.softmax(z, dim), atol=1e-5)
+
+
+def test_embedding_and_decode_accept_strided_ids():
+    """A column of a (B, T) id tensor is a strided view: the kernels must not read it as if it
+    were dense (decode_step receives exactly such views)."""
+    table = torch.randn(500, 128, device=DEV).bfloat16()
+    ids = torch.randint(0, 500, (4, 32), device=DEV)
+    assert torch.equal(K.embedding(ids[:, 7], table), table[ids[:, 7]])
+    cfg = Config.parse_from_file(os.path.join(ROOT, "configs", "efla_340m.yaml"))
+    m = cfg.model
+    m.num_layers, m.vocab_size, m.hidden_dim, m.num_heads, m.intermediate_dim = 2, 1024, 256, 4, 512
+    model = EflaLM(m, DEV, seed=0).eval()
+    tok = torch.randint(0, m.vocab_size, (3, 64), device=DEV)
+    with torch.no_grad():
+        logits = model(tok)
+        states = model.new_states(3)
+        step = torch.stack([model.decode_step(tok[:, t], states) for t in range(64)], dim=1)
+    for b in range(3):
+        assert _rel(step[b], logits[b]) < 3e-2, b
