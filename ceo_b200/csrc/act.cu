@@ -12,6 +12,78 @@ namespace ceo {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// 8 (gate, up) pairs of a row for output columns [8c, 8c+8): from the two halves of the row
+// ([gate | up]) or, interleaved, from 16 consecutive values (gate_0, up_0, gate_1, ...).
+__device__ __forceinline__ void load_gate_up(const uint4* row, int c, int fv, int il, float* g,
+                                             float* u) {
+  if (!il) {
+    unpack8(row[c], g);
+    unpack8(row[fv + c], u);
+    return;
+  }
+  float a[8], b[8];
+  unpack8(row[2 * c], a);
+  unpack8(row[2 * c + 1], b);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    g[j] = a[2 * j]; u[j] = a[2 * j + 1];
+    g[4 + j] = b[2 * j]; u[4 + j] = b[2 * j + 1];
+  }
+}
+
+// gate_up: (rows, 2F) with gate in [:, :F] and up in [:, F:] (il = 0) or with gate and up in
+// alternating columns (il = 1, the layout the fused GEMM epilogue uses).  out: (rows, F)
+__global__ void swiglu_fwd_il_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out,
+                                     long long rows, int F, int il) {
+  const int fv = F >> 3;
+  const long long total = rows * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i - r * fv);
+    float g[8], u[8], o[8];
+    load_gate_up(reinterpret_cast<const uint4*>(gu + r * 2 * F), CEO_IDX(c, fv, 204), fv, il, g, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j];
+    reinterpret_cast<uint4*>(out)[CEO_IDX(r * fv + c, rows * fv, 205)] = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_il_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu,
+                                     bf16* __restrict__ dgu, long long rows, int F, int il) {
+  const int fv = F >> 3;
+  const long long total = rows * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i - r * fv);
+    float g[8], u[8], d[8], dg[8], du[8];
+    load_gate_up(reinterpret_cast<const uint4*>(gu + r * 2 * F), c, fv, il, g, u);
+    unpack8(reinterpret_cast<const uint4*>(dout + r * F)[c], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = sigmoidf_(g[j]);
+      const float silu = g[j] * s;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * (s + silu * (1.f - s));
+    }
+    uint4* orow = reinterpret_cast<uint4*>(dgu + r * 2 * F);
+    if (!il) {
+      orow[c] = pack8(dg);
+      orow[fv + c] = pack8(du);
+    } else {
+      float a[8], b[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a[2 * j] = dg[j]; a[2 * j + 1] = du[j];
+        b[2 * j] = dg[4 + j]; b[2 * j + 1] = du[4 + j];
+      }
+      orow[2 * c] = pack8(a);
+      orow[2 * c + 1] = pack8(b);
+    }
+  }
+}
+
 // gate_up: (rows, 2F) with gate in [:, :F] and up in [:, F:].  out: (rows, F)
 __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out,
                                   long long rows, int F) {
@@ -178,6 +250,21 @@ extern "C" int ceo_swiglu_bwd(const void* dout, const void* gate_up, void* dgate
   swiglu_bwd_kernel<<<grid_for(rows * (F >> 3), 256, 148 * 16), 256, 0, stream>>>(
       static_cast<const bf16*>(dout), static_cast<const bf16*>(gate_up),
       static_cast<bf16*>(dgate_up), rows, F);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_swiglu_il_fwd(const void* gate_up, void* out, long long rows, int F,
+                                 int interleaved, cudaStream_t stream) {
+  if (rows <= 0 || F <= 0 || (F & 7)) return -5;
+  swiglu_fwd_il_kernel<<<grid_for(rows * (F >> 3), 256, 148 * 16), 256, 0, stream>>>(
+      static_cast<const bf16*>(gate_up), static_cast<bf16*>(out), rows, F, interleaved);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ceo_swiglu_il_bwd(const void* dout, const void* gate_up, void* dgate_up,
+                                 long long rows, int F, int interleaved, cudaStream_t stream) {
+  if (rows <= 0 || F <= 0 || (F & 7)) return -5;
+  swiglu_bwd_il_kernel<<<grid_for(rows * (F >> 3), 256, 148 * 16), 256, 0, stream>>>(
+      static_cast<const bf16*>(dout), static_cast<const bf16*>(gate_up),
+      static_cast<bf16*>(dgate_up), rows, F, interleaved);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int ceo_act_fwd(const void* x, void* y, long long n, int mode, cudaStream_t stream) {

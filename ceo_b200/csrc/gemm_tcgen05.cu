@@ -34,8 +34,10 @@ constexpr int PANEL_BYTES = 64 * BK * 2;  // one 64-wide MN-major panel, 8 KB
 constexpr int GEMM_THREADS = 192;
 constexpr int EPI_ROW_BYTES = 144;  // 64 bf16 + 16 B pad: conflict-free 16-byte accesses
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int ACT_ROW_BYTES = 80;  // 32 bf16 + 16 B pad
+constexpr int ACT_WARP_BYTES = 32 * ACT_ROW_BYTES;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
-                          4 * EPI_WARP_BYTES /*reduce-scatter store staging*/;
+                          4 * EPI_WARP_BYTES /*store staging*/ + 4 * ACT_WARP_BYTES /*SwiGLU*/;
 constexpr uint32_t TMEM_COLS = 512;
 
 struct GemmParams {
@@ -90,6 +92,15 @@ struct GemmParams {
   const void* rs_residual; // optional bf16, same shape/ld as rs_out
   long long rs_ldo;
   int rank, world;
+  // SwiGLU fused into the epilogue (bf16 C, K-major or MN-major operands alike):
+  //   1  C holds gate/up in INTERLEAVED columns (2j = gate_j, 2j+1 = up_j); besides C the
+  //      epilogue writes act[:, j] = silu(gate_j) * up_j into aux (M x N/2, ld_aux)
+  //   2  the accumulator is d(act) (M x N); aux is the saved interleaved gate/up (M x 2N,
+  //      ld_aux); C receives the interleaved d(gate/up) (M x 2N, ldc) and d(act) never
+  //      goes to memory
+  int epi_mode;
+  void* aux;
+  long long ld_aux;
 };
 
 enum : int { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_TMEM = 3, ST_EPILOGUE = 4, ST_AG_WAIT = 5,
@@ -545,6 +556,118 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           __syncwarp();
         }
+      } else if (p.epi_mode == 1) {
+        // gate/up projection with SiLU(gate) * up in the epilogue: C (interleaved gate/up,
+        // kept for the backward pass) and act leave together, both as whole 32-byte sectors
+        uint8_t* sb = smem + STAGES * STAGE_BYTES + 256 + quad * EPI_WARP_BYTES;
+        uint8_t* sa = smem + STAGES * STAGE_BYTES + 256 + 4 * EPI_WARP_BYTES + quad * ACT_WARP_BYTES;
+        const int row0 = m0 + quad * 32;
+        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(cbase) +
+                               static_cast<long long>(row0) * p.ldc;
+        __nv_bfloat16* abase = reinterpret_cast<__nv_bfloat16*>(p.aux) +
+                               static_cast<long long>(row0) * p.ld_aux;
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c2 * 64 + hc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q4 * 8 + j]) * alpha;
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16) = o;
+              float a4[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float g = f[2 * j];
+                a4[j] = g / (1.f + __expf(-g)) * f[2 * j + 1];
+              }
+              uint2 ao;
+              __nv_bfloat162* ah = reinterpret_cast<__nv_bfloat162*>(&ao);
+              ah[0] = __floats2bfloat162_rn(a4[0], a4[1]);
+              ah[1] = __floats2bfloat162_rn(a4[2], a4[3]);
+              *reinterpret_cast<uint2*>(sa + lane * ACT_ROW_BYTES + hc * 32 + q4 * 8) = ao;
+            }
+          }
+          __syncwarp();
+          const int ncol = n0 + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            if (row0 + rl < p.M && ncol < p.N)
+              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol) = o;
+          }
+          const int acol = (n0 + c2 * 64) / 2 + (lane & 3) * 8;  // 32 act columns per chunk
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rl = i * 8 + (lane >> 2);
+            const uint4 o = *reinterpret_cast<const uint4*>(sa + rl * ACT_ROW_BYTES + (lane & 3) * 16);
+            if (row0 + rl < p.M && 2 * acol < p.N)
+              *reinterpret_cast<uint4*>(abase + static_cast<long long>(rl) * p.ld_aux + acol) = o;
+          }
+          __syncwarp();
+        }
+      } else if (p.epi_mode == 2) {
+        // down projection's data gradient with the SwiGLU backward in the epilogue: the
+        // accumulator holds d(act) for 256 columns; the matching 512 interleaved gate/up
+        // columns are read, and d(gate), d(up) written, 128 bytes per row at a time
+        uint8_t* sb = smem + STAGES * STAGE_BYTES + 256 + quad * EPI_WARP_BYTES;
+        const int row0 = m0 + quad * 32;
+        const __nv_bfloat16* gubase = reinterpret_cast<const __nv_bfloat16*>(p.aux) +
+                                      static_cast<long long>(row0) * p.ld_aux;
+        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(cbase) +
+                               static_cast<long long>(row0) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int gcol = 2 * (n0 + c * 32) + (lane & 7) * 8;  // 64 gate/up columns per step
+          const bool col_ok = n0 + c * 32 < p.N;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            uint4 o = make_uint4(0, 0, 0, 0);
+            if (row0 + rl < p.M && col_ok)
+              o = *reinterpret_cast<const uint4*>(gubase + static_cast<long long>(rl) * p.ld_aux + gcol);
+            *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = o;
+          }
+          __syncwarp();
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {  // 4 d(act) values <-> 8 interleaved gate/up values
+            uint4* slot = reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + q * 16);
+            const uint4 u4 = *slot;
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u4);
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 gu = __bfloat1622float2(h[j]);  // (gate, up)
+              const float d = __uint_as_float(v[q * 4 + j]) * alpha;
+              const float sg = 1.f / (1.f + __expf(-gu.x));
+              const float silu = gu.x * sg;
+              oh[j] = __floats2bfloat162_rn(d * gu.y * (sg + silu * (1.f - sg)), d * silu);
+            }
+            *slot = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            if (row0 + rl < p.M && col_ok)
+              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + gcol) = o;
+          }
+          __syncwarp();
+        }
       } else if (!p.out_f32 && !p.accumulate && !p.bias && ((p.N | p.ldc) & 7) == 0 &&
                  (!p.residual || (p.ldr & 7) == 0)) {
         // bf16 output (+ bf16 residual): same 64-column transpose through the per-warp tile,
@@ -873,6 +996,13 @@ struct Fp8Desc {
   const float* scale_b = nullptr;
 };
 
+// SwiGLU fused into the epilogue (see GemmParams::epi_mode).
+struct EpiDesc {
+  int mode = 0;
+  void* aux = nullptr;
+  long long ld_aux = 0;
+};
+
 // Host-side description of the collective fused into a GEMM launch (see GemmParams).
 struct FusedDesc {
   int kind = 0;  // 0 plain, 1 all-gather of A, 2 all-gather of B, 3 reduce-scatter of C
@@ -897,7 +1027,7 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
                     int out_f32, int accumulate, float alpha, const float* bias,
                     const void* residual, long long ldr, long long batch_stride_r, int* status,
                     int max_ctas, const FusedDesc& fz, cudaStream_t stream, int split_k_mode = 1,
-                    const Fp8Desc& f8 = Fp8Desc()) {
+                    const Fp8Desc& f8 = Fp8Desc(), const EpiDesc& epi = EpiDesc()) {
   using namespace ceo;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if (f8.on && (a_mn_major || b_mn_major || fz.kind != 0)) return -5;
@@ -956,6 +1086,17 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
   p.status = status;
   p.rank = fz.rank;
   p.world = fz.world;
+  if (epi.mode) {
+    // bf16 output, one matrix, no other epilogue term; whole 64-column groups of gate/up
+    if (epi.mode < 0 || epi.mode > 2 || !epi.aux || out_f32 || accumulate || bias || residual ||
+        batch != 1 || fz.kind != 0 || (epi.ld_aux & 7) || (ldc & 7) ||
+        (reinterpret_cast<uintptr_t>(epi.aux) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
+        (epi.mode == 1 ? (N & 63) : (N & 31)))
+      return -5;
+    p.epi_mode = epi.mode;
+    p.aux = epi.aux;
+    p.ld_aux = epi.ld_aux;
+  }
   // bands of 16 row blocks: a wave of 148 tiles is then ~16 x 9 tiles whose A and B panels
   // both stay in L2 (m-fastest over all rows re-reads A once per ~2 n-blocks)
   p.grp_m = p.num_m > 16 ? 16 : p.num_m;
@@ -1057,6 +1198,24 @@ extern "C" int ceo_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, batch, batch_stride_a,
                   batch_stride_b, batch_stride_c, out_f32, accumulate, alpha, bias, residual, ldr,
                   batch_stride_r, status, max_ctas, fz, stream);
+}
+
+// The bf16 GEMM with SwiGLU in its epilogue.  mode 1: C[M,N] = A B^T holds gate/up in
+// interleaved columns and aux (M x N/2, bf16, ld_aux) receives silu(gate) * up.  mode 2: the
+// product A B^T is d(act) (M x N); aux is the saved interleaved gate/up (M x 2N, ld_aux) and
+// C (M x 2N, ldc) receives the interleaved d(gate/up).
+extern "C" int ceo_gemm_bf16_swiglu(const void* A, const void* B, void* C, int M, int N, int K,
+                                    long long lda, long long ldb, long long ldc, int a_mn_major,
+                                    int b_mn_major, float alpha, int mode, void* aux,
+                                    long long ld_aux, int* status, cudaStream_t stream) {
+  FusedDesc fz;
+  EpiDesc epi;
+  epi.mode = mode;
+  epi.aux = aux;
+  epi.ld_aux = ld_aux;
+  if (mode != 1 && mode != 2) return -5;
+  return gemm_run(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, 1, 0, 0, 0, 0, 0, alpha,
+                  nullptr, nullptr, 0, 0, status, 0, fz, stream, 1, Fp8Desc(), epi);
 }
 
 // C[M,N] = alpha / (scale_a * scale_b) * A[M,K] @ B[N,K]^T (+ bias) (+ residual) with 8-bit

@@ -102,6 +102,13 @@ int ceo_swiglu_fwd(const void* gate_up, void* out, long long rows, int F, cudaSt
 int ceo_swiglu_bwd(const void* dout, const void* gate_up, void* dgate_up, long long rows, int F,
                    cudaStream_t stream);
 /* mode 0 tanh-GELU, 1 erf-GELU, 2 SiLU, 3 ReLU */
+/* SwiGLU on a (rows, 2F) gate/up tensor whose gate and up columns alternate (interleaved = 1:
+ * column 2j = gate_j, 2j+1 = up_j, the layout of the fused GEMM epilogue) or sit in two
+ * halves (interleaved = 0). */
+int ceo_swiglu_il_fwd(const void* gate_up, void* out, long long rows, int F, int interleaved,
+                      cudaStream_t stream);
+int ceo_swiglu_il_bwd(const void* dout, const void* gate_up, void* dgate_up, long long rows, int F,
+                      int interleaved, cudaStream_t stream);
 int ceo_act_fwd(const void* x, void* y, long long n, int mode, cudaStream_t stream);
 int ceo_act_bwd(const void* dy, const void* x, void* dx, long long n, int mode,
                 cudaStream_t stream);
@@ -224,6 +231,14 @@ int ceo_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pi
 int ceo_transpose16(const void* src, void* dst, int rows, int cols, long long lds, long long ldd,
                     cudaStream_t stream);
 int ceo_memset32(void* x, long long n, unsigned int value, cudaStream_t stream);
+
+/* bf16 GEMM with SwiGLU in the epilogue.  mode 1: C (M x N) = A B^T holds gate/up in
+ * interleaved columns (2j gate, 2j+1 up) and aux (M x N/2) receives silu(gate) * up; N a
+ * multiple of 64.  mode 2: A B^T is d(act) (M x N, N a multiple of 32), aux is the saved
+ * interleaved gate/up (M x 2N) and C (M x 2N) receives the interleaved d(gate/up). */
+int ceo_gemm_bf16_swiglu(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                         long long ldb, long long ldc, int a_mn_major, int b_mn_major, float alpha,
+                         int mode, void* aux, long long ld_aux, int* status, cudaStream_t stream);
 
 /* C = alpha / (scale_a * scale_b) * A[M,K] @ B[N,K]^T (+ bias) (+ residual): 8-bit float
  * operands (kind 0 e4m3, 1 e5m2), both K-major, strides multiples of 16; scale_a / scale_b

@@ -26,6 +26,7 @@ import torch.nn as nn
 from ..ops import efla as efla_ops
 from ..ops import nn as K
 from ..ops.fp8 import Fp8Recipe, fp8_linear
+from ..ops import matmul as matmul_ops
 from ..ops.matmul import linear
 from ..utils.config import ModelConfig
 from .prism import PrismLayer
@@ -144,13 +145,27 @@ class MLP(nn.Module):
         D, F = cfg.hidden_dim, cfg.intermediate_dim
         self.F = F
         n_up = 2 * F if self.act == "swiglu" else F
-        self.w_up = _param((n_up, D), std, device, dtype, gen)  # [gate | up] rows when swiglu
+        self.w_up = _param((n_up, D), std, device, dtype, gen)
+        if self.act == "swiglu":
+            # drawn as [gate | up] row blocks, kept INTERLEAVED (row 2j = gate_j, row 2j+1 =
+            # up_j): an output tile of the gate/up GEMM then holds matching (gate, up) pairs
+            # and its epilogue can apply SiLU(gate) * up
+            w = self.w_up.data
+            self.w_up.data = w.view(2, F, D).transpose(0, 1).reshape(n_up, D).contiguous()
         self.w_down = _param((D, F), std, device, dtype, gen)
         self.fp8 = None
 
+    def gate_up_weights(self):
+        """(W_gate, W_up), each (F, D) (strided views of the interleaved parameter)."""
+        return self.w_up[0::2], self.w_up[1::2]
+
     def forward(self, x_norm, residual):
-        u = _lin(self, "up", x_norm, self.w_up)
-        a = K.swiglu(u) if self.act == "swiglu" else K.activation(u, self.act)
+        if self.act == "swiglu":
+            if x_norm.is_cuda and self.fp8 is None and matmul_ops.FUSED_SWIGLU and self.F % 32 == 0:
+                return matmul_ops.swiglu_mlp(x_norm, self.w_up, self.w_down, residual)
+            a = K.swiglu(_lin(self, "up", x_norm, self.w_up), interleaved=True)
+        else:
+            a = K.activation(_lin(self, "up", x_norm, self.w_up), self.act)
         return _lin(self, "down", a, self.w_down, residual)
 
 
@@ -391,9 +406,9 @@ def block_reference_tensors(b: Block, p: str, cfg: ModelConfig, out: dict) -> di
     if b.ln2.bias is not None:
         out[p + "ln2.bias"] = b.ln2.bias.detach()
     if b.mlp.act == "swiglu":
-        g, u = b.mlp.w_up.detach().split(b.mlp.F, dim=0)
-        out[p + "mlp_gate.weight"] = g.t().contiguous()
-        out[p + "mlp_up.weight"] = u.t().contiguous()
+        g, u = b.mlp.gate_up_weights()
+        out[p + "mlp_gate.weight"] = g.detach().t().contiguous()
+        out[p + "mlp_up.weight"] = u.detach().t().contiguous()
     else:
         out[p + "mlp_up.weight"] = b.mlp.w_up.detach().t().contiguous()
     out[p + "mlp_down.weight"] = b.mlp.w_down.detach().t().contiguous()
@@ -423,8 +438,9 @@ def load_block_reference(b: Block, p: str, cfg: ModelConfig, tensors: dict) -> N
     if b.ln2.bias is not None:
         _put(b.ln2.bias, tensors[p + "ln2.bias"])
     if b.mlp.act == "swiglu":
-        _put(b.mlp.w_up[:b.mlp.F], tensors[p + "mlp_gate.weight"].t())
-        _put(b.mlp.w_up[b.mlp.F:], tensors[p + "mlp_up.weight"].t())
+        g, u = b.mlp.gate_up_weights()
+        _put(g, tensors[p + "mlp_gate.weight"].t())
+        _put(u, tensors[p + "mlp_up.weight"].t())
     else:
         _put(b.mlp.w_up, tensors[p + "mlp_up.weight"].t())
     _put(b.mlp.w_down, tensors[p + "mlp_down.weight"].t())

@@ -136,3 +136,86 @@ def linear(x: torch.Tensor, weight: torch.Tensor,
            residual: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T (+ residual)`` with ``weight`` of shape ``(out, in)``."""
     return _LinearFn.apply(x, weight, residual)
+
+
+# ---------------------------------------------------------------- SwiGLU MLP, fused
+# Set to False to run the MLP as three separate ops (gate/up GEMM, SwiGLU kernel, down GEMM).
+FUSED_SWIGLU = True
+
+
+def _gemm_swiglu(a, b, c, M, N, K, b_mn, mode, aux):
+    rc = _lib.lib().ceo_gemm_bf16_swiglu(
+        a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0), c.stride(0),
+        0, int(b_mn), 1.0, mode, aux.data_ptr(), aux.stride(0),
+        _lib.status_word(a.device).data_ptr(), _lib.stream())
+    _lib.check(rc, "ceo_gemm_bf16_swiglu")
+
+
+class _SwiGLUMlpFn(torch.autograd.Function):
+    """``(silu(gate) * up) @ w_down^T (+ residual)`` with ``[gate, up] = x @ w_up^T`` in
+    interleaved columns (row 2j of ``w_up`` is gate_j, row 2j+1 is up_j).
+
+    Forward: the gate/up GEMM applies SiLU(gate) * up in its epilogue and writes gate/up (kept
+    for the backward pass) and the activation together - no separate activation kernel, no
+    re-read of gate/up.  Backward: the down projection's data-gradient GEMM reads gate/up in
+    its epilogue and writes d(gate/up) directly; d(activation) never goes to memory."""
+
+    @staticmethod
+    def forward(ctx, x, w_up, w_down, residual):
+        x2 = _as2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M, K = x2.shape
+        N2 = w_up.shape[0]
+        F = N2 // 2
+        res2 = _as2d(residual) if residual is not None else None
+        fg = getattr(w_up, "fsdp_gather", None)
+        act = torch.empty(M, F, dtype=x2.dtype, device=x2.device)
+        if fg is not None and fg.pending:
+            # FSDP: this GEMM carries the weight all-gather; the activation runs on its own
+            gate_up = fg.gemm(x2)
+            _lib.check(_lib.lib().ceo_swiglu_il_fwd(gate_up.data_ptr(), act.data_ptr(), M, F, 1,
+                                                    _lib.stream()), "ceo_swiglu_il_fwd")
+        else:
+            gate_up = torch.empty(M, N2, dtype=x2.dtype, device=x2.device)
+            _gemm_swiglu(x2, w_up, gate_up, M, N2, K, False, 1, act)
+        y = gemm(act, w_down, residual=res2)
+        ctx.save_for_backward(x2, gate_up, act)
+        ctx.refs = (w_up, w_down)
+        ctx.x_shape = x.shape
+        ctx.has_res = residual is not None
+        return y.view(*x.shape[:-1], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, gate_up, act = ctx.saved_tensors
+        w_up, w_down = ctx.refs
+        M, K = x2.shape
+        N2 = w_up.shape[0]
+        F = N2 // 2
+        D = w_down.shape[0]
+        dy2 = _as2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        # d(gate/up) from the down projection's data gradient: (M, D) x (D, F) -> epilogue
+        dgu = torch.empty_like(gate_up)
+        _gemm_swiglu(dy2, w_down, dgu, M, F, D, True, 2, gate_up)
+        grads = []
+        for w, dyy, xin in ((w_down, dy2, act), (w_up, dgu, x2)):
+            mg = getattr(w, "main_grad", None)
+            if not w.requires_grad:
+                grads.append(None)
+            elif mg is not None:
+                gemm(dyy, xin, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                w.grad_touched = True
+                grads.append(None)
+            else:
+                grads.append(gemm(dyy, xin, a_mn=True, b_mn=True, out_dtype=w.dtype))
+        dx = gemm(dgu, w_up, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        return dx, grads[1], grads[0], (dy if ctx.has_res else None)
+
+
+def swiglu_mlp(x, w_up, w_down, residual=None):
+    """The SwiGLU MLP ``(silu(x W_gate^T) * (x W_up^T)) W_down^T (+ residual)`` with the
+    activation fused into the GEMM epilogues; ``w_up`` holds gate and up rows interleaved."""
+    return _SwiGLUMlpFn.apply(x, w_up, w_down, residual)

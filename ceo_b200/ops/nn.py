@@ -155,14 +155,16 @@ def layernorm(x, weight, bias=None, eps: float = 1e-5):
 # ----------------------------------------------------------------------- activations
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gate_up):
+    def forward(ctx, gate_up, interleaved):
         F = gate_up.shape[-1] // 2
         g2 = gate_up.reshape(-1, 2 * F)
         out = torch.empty(g2.shape[0], F, dtype=gate_up.dtype, device=gate_up.device)
-        _lib.check(_lib.lib().ceo_swiglu_fwd(g2.data_ptr(), out.data_ptr(), g2.shape[0], F,
-                                             _lib.stream()), "ceo_swiglu_fwd")
+        _lib.check(_lib.lib().ceo_swiglu_il_fwd(g2.data_ptr(), out.data_ptr(), g2.shape[0], F,
+                                                int(interleaved), _lib.stream()),
+                   "ceo_swiglu_il_fwd")
         ctx.save_for_backward(g2)
         ctx.shape = gate_up.shape
+        ctx.interleaved = interleaved
         return out.view(*gate_up.shape[:-1], F)
 
     @staticmethod
@@ -173,17 +175,19 @@ class _SwiGLUFn(torch.autograd.Function):
         if not d2.is_contiguous():
             d2 = d2.contiguous()
         dgu = torch.empty_like(g2)
-        _lib.check(_lib.lib().ceo_swiglu_bwd(d2.data_ptr(), g2.data_ptr(), dgu.data_ptr(),
-                                             g2.shape[0], F, _lib.stream()), "ceo_swiglu_bwd")
-        return dgu.view(ctx.shape)
+        _lib.check(_lib.lib().ceo_swiglu_il_bwd(d2.data_ptr(), g2.data_ptr(), dgu.data_ptr(),
+                                                g2.shape[0], F, int(ctx.interleaved),
+                                                _lib.stream()), "ceo_swiglu_il_bwd")
+        return dgu.view(ctx.shape), None
 
 
-def swiglu(gate_up):
-    """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last dimension."""
+def swiglu(gate_up, interleaved: bool = False):
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last dimension, or, with
+    ``interleaved``, for gate and up in alternating columns (2j = gate_j, 2j+1 = up_j)."""
     if not gate_up.is_cuda:
-        return ref.swiglu(gate_up)
+        return ref.swiglu(gate_up, interleaved)
     assert gate_up.is_contiguous()
-    return _SwiGLUFn.apply(gate_up)
+    return _SwiGLUFn.apply(gate_up, interleaved)
 
 
 class _ActFn(torch.autograd.Function):

@@ -33,8 +33,11 @@ def layernorm(x, weight, bias=None, eps=1e-5):
     return y.to(x.dtype)
 
 
-def swiglu(gate_up):
-    g, u = gate_up.float().chunk(2, dim=-1)
+def swiglu(gate_up, interleaved: bool = False):
+    """silu(gate) * up; gate / up are the two halves of the last dimension, or (interleaved)
+    its even / odd columns."""
+    gf = gate_up.float()
+    g, u = (gf[..., 0::2], gf[..., 1::2]) if interleaved else gf.chunk(2, dim=-1)
     return (F.silu(g) * u).to(gate_up.dtype)
 
 

@@ -148,6 +148,14 @@ def test_swiglu_and_activations():
     want = torch.nn.functional.silu(g) * u
     want.backward(d.float())
     assert _rel(out, want) < 6e-3 and _rel(gu.grad, gr.grad) < 8e-3
+    # interleaved layout (column 2j = gate_j, 2j+1 = up_j)
+    gi = _rand(130, 2 * 352).requires_grad_()
+    oi = nn_ops.swiglu(gi, interleaved=True)
+    oi.backward(d)
+    gr2 = gi.detach().float().requires_grad_()
+    want2 = torch.nn.functional.silu(gr2[:, 0::2]) * gr2[:, 1::2]
+    want2.backward(d.float())
+    assert _rel(oi, want2) < 6e-3 and _rel(gi.grad, gr2.grad) < 8e-3
     for kind in ("gelu", "gelu_erf", "silu", "relu"):
         x = _rand(64, 512).requires_grad_()
         y = nn_ops.activation(x, kind)
@@ -192,3 +200,33 @@ def test_embedding():
     torch.nn.functional.embedding(ids, tr).backward(dy.float())
     assert torch.equal(out, table.detach()[ids])
     assert _rel(table.grad, tr.grad) < 8e-3
+
+
+@pytest.mark.parametrize("M,D,F", [(300, 256, 352), (256, 512, 1024), (64, 128, 96)])
+def test_swiglu_mlp_fused_epilogues_match_fp32(M, D, F):
+    """The MLP with SiLU(gate) * up in the gate/up GEMM's epilogue and the SwiGLU backward in
+    the down projection's data-gradient epilogue, against the same math in fp32."""
+    from ceo_b200.ops.matmul import swiglu_mlp
+    torch.manual_seed(9)
+    x = _rand(M, D).requires_grad_()
+    w_up = (_rand(2 * F, D) * 0.2).requires_grad_()     # interleaved rows
+    w_down = (_rand(D, F) * 0.2).requires_grad_()
+    res = _rand(M, D).requires_grad_()
+    y = swiglu_mlp(x, w_up, w_down, res)
+    dy = _rand(M, D)
+    y.backward(dy)
+    xr, wur, wdr, rr = (t.detach().float().requires_grad_() for t in (x, w_up, w_down, res))
+    gu = xr @ wur.t()
+    act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+    yr = act @ wdr.t() + rr
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 8e-3
+    for a, b, name in ((x, xr, "dx"), (w_up, wur, "dw_up"), (w_down, wdr, "dw_down"),
+                       (res, rr, "dres")):
+        assert _rel(a.grad, b.grad) < 1.5e-2, name
+    # the unfused path (three ops) gives the same function
+    from ceo_b200.ops.matmul import linear
+    y2 = linear(nn_ops.swiglu(linear(x.detach(), w_up.detach()), interleaved=True),
+                w_down.detach(), res.detach())
+    assert _rel(y2, y) < 8e-3
+    assert _lib.read_status() == 0
