@@ -21,9 +21,12 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "common/check.cuh"
 #include "common/ptx.cuh"
 #include "common/util.cuh"
 #include "include/ceo_kernels.h"
+
+CEO_BOUNDS_TU(comm)
 
 namespace cg = cooperative_groups;
 
@@ -222,6 +225,7 @@ zero_step_kernel(const ZeroStepArgs a) {
     float4* ms = reinterpret_cast<float4*>(a.master + rg.loff);
     const long long n4 = rg.len >> 2;
     for (long long i = tid; i < n4; i += nth) {
+      (void)CEO_IDX(base + 4 * i, a.total - 3, 501);  // the slice stays inside the flat buffers
       const float4 g4 = reinterpret_cast<const float4*>(gl)[i];
       reinterpret_cast<float4*>(gl)[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // consumed: zero it
       if (skip) continue;
@@ -272,7 +276,8 @@ zero_step_kernel(const ZeroStepArgs a) {
     const long long s4 = rg.goff >> 2, n4 = (rg.len * a.world) >> 2;
     const long long o4 = (a.rank * rg.len) >> 2, l4 = rg.len >> 2;
     for (long long i = tid; i < n4; i += nth)
-      if (i < o4 || i >= o4 + l4) gz[s4 + i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < o4 || i >= o4 + l4)
+        gz[CEO_IDX(s4 + i, a.total >> 2, 502)] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 
   // ---- barrier 2: all parameter slices have landed everywhere -------------------------

@@ -18,8 +18,11 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "common/check.cuh"
 #include "common/ptx.cuh"
 #include "include/ceo_kernels.h"
+
+CEO_BOUNDS_TU(gemm)
 
 namespace ceo {
 
@@ -175,8 +178,9 @@ __device__ __forceinline__ void rs_reduce(const GemmParams& p, int warp, int lan
         for (int src = 0; src < W; ++src)
           if (src < p.world)
             part[q][src] = __ldcg(reinterpret_cast<const uint4*>(
-                stage + (static_cast<long long>(src) * p.rs_rows_per_rank + row0 + q) * p.ldc +
-                nb * BN + c));
+                stage + CEO_IDX((static_cast<long long>(src) * p.rs_rows_per_rank + row0 + q) * p.ldc +
+                                    nb * BN + c,
+                                static_cast<long long>(p.world) * p.rs_rows_per_rank * p.ldc - 7, 406)));
         if (resid)
           resv[q] = *reinterpret_cast<const uint4*>(resid + (row0 + q) * p.rs_ldo + nb * BN + c);
       }
@@ -207,7 +211,9 @@ __device__ __forceinline__ void rs_reduce(const GemmParams& p, int warp, int lan
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc8[2 * j], acc8[2 * j + 1]);
-        *reinterpret_cast<uint4*>(outp + (row0 + q) * p.rs_ldo + nb * BN + c) = o;
+        *reinterpret_cast<uint4*>(
+            outp + CEO_IDX((row0 + q) * p.rs_ldo + nb * BN + c,
+                           static_cast<long long>(p.rs_rows_per_rank - 1) * p.rs_ldo + p.N - 7, 407)) = o;
       }
     }
   }
@@ -542,7 +548,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               for (int j = 0; j < 4; ++j)
                 oh[j] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * j]) * alpha,
                                               __uint_as_float(v[q4 * 8 + 2 * j + 1]) * alpha);
-              *reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16) = o;
+              *reinterpret_cast<uint4*>(
+                  sb + CEO_IDX(lane * EPI_ROW_BYTES + hc * 64 + q4 * 16, EPI_WARP_BYTES - 15, 401)) = o;
             }
           }
           __syncwarp();
@@ -550,9 +557,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rl = i * 4 + (lane >> 3);
-            const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
+            const uint4 o = *reinterpret_cast<const uint4*>(
+                sb + CEO_IDX(rl * EPI_ROW_BYTES + (lane & 7) * 16, EPI_WARP_BYTES - 15, 402));
             if (m0 + quad * 32 + rl < p.M && ncol < p.N)
-              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol) = o;
+              *reinterpret_cast<uint4*>(
+                  gbase + CEO_IDX(static_cast<long long>(rl) * p.ldc + ncol,
+                                  static_cast<long long>(p.world) * p.rs_rows_per_rank * p.ldc -
+                                      (coff - static_cast<long long>(lane) * p.ldc) - 7, 403)) = o;
           }
           __syncwarp();
         }
@@ -704,7 +715,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             tmem_ld_wait();
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
-              uint4* slot = reinterpret_cast<uint4*>(sb + lane * EPI_ROW_BYTES + hc * 64 + q4 * 16);
+              uint4* slot = reinterpret_cast<uint4*>(
+                  sb + CEO_IDX(lane * EPI_ROW_BYTES + hc * 64 + q4 * 16, EPI_WARP_BYTES - 15, 404));
               float f[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q4 * 8 + j]) * alpha;
@@ -731,7 +743,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             const int rl = i * 4 + (lane >> 3);
             const uint4 o = *reinterpret_cast<const uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16);
             if (row0 + rl < p.M && ncol < p.N)
-              *reinterpret_cast<uint4*>(gbase + static_cast<long long>(rl) * p.ldc + ncol) = o;
+              *reinterpret_cast<uint4*>(
+                  gbase + CEO_IDX(static_cast<long long>(rl) * p.ldc + ncol,
+                                  static_cast<long long>(p.M - row0 - 1) * p.ldc + p.N - 7, 405)) = o;
           }
           __syncwarp();
         }

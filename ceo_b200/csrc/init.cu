@@ -182,17 +182,21 @@ using namespace ceo;
 extern "C" int ceo_bounds_collect_scan(unsigned long long*, int);
 extern "C" int ceo_bounds_collect_act(unsigned long long*, int);
 extern "C" int ceo_bounds_collect_embed(unsigned long long*, int);
+extern "C" int ceo_bounds_collect_gemm(unsigned long long*, int);
+extern "C" int ceo_bounds_collect_comm(unsigned long long*, int);
 #endif
 // Checked build: synchronises the device, then out[0..3] = {violations, site, index, extent} of
 // the first recorded violation (sites: 1xx scan / gather / scatter / transpose, 2xx
-// activations, 3xx embedding) and returns 0; `reset` clears the records.  Normal build:
+// activations, 3xx embedding, 4xx GEMM epilogue staging and the reduce-scatter reduction, 5xx
+// the fused optimizer step) and returns 0; `reset` clears the records.  Normal build:
 // returns -1 (no checks compiled in).
 extern "C" int ceo_bounds_status(long long* out, int reset) {
 #ifdef CEO_BOUNDS_CHECK
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return static_cast<int>(e);
   int (*const fns[])(unsigned long long*, int) = {ceo_bounds_collect_scan, ceo_bounds_collect_act,
-                                                  ceo_bounds_collect_embed};
+                                                  ceo_bounds_collect_embed, ceo_bounds_collect_gemm,
+                                                  ceo_bounds_collect_comm};
   unsigned long long total = 0, first[4] = {0, 0, 0, 0};
   for (auto fn : fns) {
     unsigned long long rec[4];

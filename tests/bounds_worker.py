@@ -38,6 +38,44 @@ def main():
     gu = torch.randn(37, 2 * 264, device=dev).bfloat16()
     g, u = gu[:, :264].float(), gu[:, 264:].float()
     assert (K.swiglu(gu).float() - g * torch.sigmoid(g) * u).abs().max() < 0.05
+    # GEMM epilogue staging at tile edges (bf16 store path), the reduce-scatter reduction and
+    # the fused optimizer step in loopback (peer pointers aimed at local memory)
+    from ceo_b200.ops.matmul import gemm
+    from ceo_b200.parallel.loopback import LoopbackPeers, table
+    a = torch.randn(200, 136, device=dev).bfloat16()
+    b = torch.randn(328, 136, device=dev).bfloat16()
+    r = torch.randn(200, 328, device=dev).bfloat16()
+    c = gemm(a, b, residual=r)
+    assert (c.float() - (a.float() @ b.float().t() + r.float())).abs().max() < 0.5
+    L = _lib.lib()
+    st = _lib.status_word(torch.device("cuda", 0))
+    M, N, Kd = 512, 328, 64
+    x = torch.randn(M, Kd, device=dev).bfloat16()
+    w = torch.randn(N, Kd, device=dev).bfloat16()
+    stage = [torch.zeros(2, M // 2, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    cnt = [torch.zeros(2, M // 2 // 128, dtype=torch.int32, device=dev) for _ in range(2)]
+    target = 4 * ((N + 255) // 256)
+    cnt[0][1] = target
+    o = torch.empty(M // 2, N, dtype=torch.bfloat16, device=dev)
+    _lib.check(L.ceo_gemm_rs_bf16(x.data_ptr(), w.data_ptr(), M, N, Kd, Kd, Kd, 0, 0, 1.0,
+                                  table(stage), table(cnt), target, o.data_ptr(), None, N, 0, 2, 4,
+                                  st.data_ptr(), _lib.stream()), "ceo_gemm_rs_bf16")
+    assert (o.float() - (x.float() @ w.float().t())[:M // 2]).abs().max() < 0.5
+    peers = LoopbackPeers(2)
+    peers.signal(0)
+    total = 4096
+    gr = [torch.randn(total, device=dev) * 0.01 for _ in range(2)]
+    pr = [torch.zeros(total, device=dev).bfloat16() for _ in range(2)]
+    master, m1, v1 = (torch.zeros(1536, device=dev) for _ in range(3))
+    rng = torch.tensor([[0, 1024, 0, 1], [2048, 512, 1024, 0]], dtype=torch.int64, device=dev)
+    acc, nrm, clp = torch.zeros(2, device=dev), torch.zeros(1, device=dev), torch.ones(1, device=dev)
+    _lib.check(L.ceo_zero_step(table(gr), table(pr), peers.flags(), peers.slots(), master.data_ptr(),
+                               m1.data_ptr(), v1.data_ptr(), acc.data_ptr(), nrm.data_ptr(),
+                               clp.data_ptr(), st.data_ptr(), rng.data_ptr(), 2, total, 2048, 0, 2,
+                               peers.next_epoch(), 0, 1, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 0.5, 1.0, 0,
+                               _lib.stream()), "ceo_zero_step")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and float(master.abs().sum()) > 0
     out["clean"] = _lib.bounds_status()
     # the recorder itself: 5 indices past the end of a 100-element buffer, redirected to 0
     buf = torch.ones(101, device=dev)
