@@ -71,10 +71,14 @@ static inline int set_wait_limit_override(unsigned iterations) {
       cudaMemcpyToSymbol(ceo_wait_limit_override, &iterations, sizeof(unsigned)));
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t limit = wait_limit(CEO_WAIT_LIMIT);
-  for (uint32_t it = 0; it < limit; ++it) {
+  // fast path first: the run-time limit lives in global memory, and a load of it in front of
+  // every wait would sit on the critical path of the single MMA-issuing thread
+  for (uint32_t it = 0; it < 64; ++it)
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(32);
+  const uint32_t limit = wait_limit(CEO_WAIT_LIMIT);
+  for (uint32_t it = 64; it < limit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(32);
   }
   return false;
 }
@@ -175,11 +179,15 @@ __device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
 // Bounded wait until *p (monotonic counter, wrap-tolerant) reaches `target`.
 template <bool SYS>
 __device__ __forceinline__ bool flag_wait_ge(const unsigned* p, unsigned target) {
+  {
+    const unsigned v = SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu(p);
+    if (static_cast<int>(v - target) >= 0) return true;  // already there: no limit lookup
+  }
   const unsigned limit = wait_limit(CEO_FLAG_WAIT_LIMIT);
-  for (unsigned it = 0; it < limit; ++it) {
+  for (unsigned it = 1; it < limit; ++it) {
+    __nanosleep(100);
     const unsigned v = SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu(p);
     if (static_cast<int>(v - target) >= 0) return true;
-    __nanosleep(100);
   }
   return false;
 }

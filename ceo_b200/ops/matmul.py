@@ -14,6 +14,8 @@ gemm_backward_cuda of the reference (kernels/cuda/gemm.cu:303, 400).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -139,8 +141,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor,
 
 
 # ---------------------------------------------------------------- SwiGLU MLP, fused
-# Set to False to run the MLP as three separate ops (gate/up GEMM, SwiGLU kernel, down GEMM).
-FUSED_SWIGLU = True
+# False (or CEO_FUSED_SWIGLU=0 in the environment) runs the MLP as three separate ops
+# (gate/up GEMM, SwiGLU kernel, down GEMM).
+FUSED_SWIGLU = os.environ.get("CEO_FUSED_SWIGLU", "1") not in ("0", "")
 
 
 def _gemm_swiglu(a, b, c, M, N, K, b_mn, mode, aux):

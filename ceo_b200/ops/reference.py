@@ -143,12 +143,38 @@ def delta_rule_chunked(q, k, v, alpha, s0=None, chunk=64, resets=None):
     return o.permute(0, 2, 3, 1, 4).reshape(B, T, H, dv), S
 
 
-def efla_reference_form(k, v, beta: float, s0=None):
-    """The reference's own special case: q = k, one scalar beta, c_t from ||k_t||^2
-    (kernels/cuda/efla.cu:181-232)."""
+def efla_reference_form(k, v, beta: float, s0=None, readout: str = "model"):
+    """The reference's special case of the recurrence: q = k, one scalar beta, c_t from
+    ||k_t||^2 (kernels/cuda/efla.cu:181-221) - the STATE recurrence is the reference's exactly.
+
+    ``readout`` selects how the output is read from the state S (d_k x d_v, row = key index):
+
+    * ``"model"`` (default): ``o_t = S_t^T k_t``, the contraction over the KEY index that this
+      framework's model and kernels use (with a separate q in general);
+    * ``"reference"``: ``o_t[row] = sum_col S_t[row][col] k_t[col]``, i.e. ``S_t k_t``, the
+      contraction over the VALUE index that the reference's kernel and its CPU routine
+      perform (kernels/cuda/efla.cu:222-231, ``eflaComputeOutput`` in
+      src/kernels/efla_kernels.zig); it needs d_k = d_v.  The CUDA kernels of this framework
+      do not implement this read-out: it exists here so that the difference is pinned by a
+      test rather than by a docstring."""
     lam = k.float().pow(2).sum(-1)
     alpha = efla_coefficient(torch.full_like(lam, beta), lam)
-    return delta_rule_sequential(k, k, v, alpha, s0)
+    if readout == "model":
+        return delta_rule_sequential(k, k, v, alpha, s0)
+    if readout != "reference":
+        raise ValueError(readout)
+    B, T, H, d = k.shape
+    assert v.shape[-1] == d, "the reference's read-out contracts keys with the value index"
+    S = torch.zeros(B, H, d, d, dtype=torch.float32, device=k.device) if s0 is None \
+        else s0.float().clone()
+    kf, vf = k.float(), v.float()
+    outs = []
+    for t in range(T):
+        kt, vt, a = kf[:, t], vf[:, t], alpha[:, t]
+        u = torch.einsum("bhkv,bhk->bhv", S, kt)                      # S^T k
+        S = S + a[..., None, None] * kt[..., :, None] * (vt - u)[..., None, :]
+        outs.append(torch.einsum("bhrc,bhc->bhr", S, kt))              # S k (over columns)
+    return torch.stack(outs, dim=1).to(k.dtype), S
 
 
 # ---------------------------------------------------------------------- ShortConv / PRISM

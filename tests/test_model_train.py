@@ -46,6 +46,21 @@ def test_efla_coefficient_and_oracles_agree():
     ob, sb = ref.efla_reference_form(k[:, 64:], v[:, 64:], 1.0, sa)
     assert torch.allclose(torch.cat([oa, ob], 1), o_full, atol=1e-5)
     assert torch.allclose(sb, s_full, atol=1e-5)
+    # the reference's own read-out (S k over the value index, kernels/cuda/efla.cu:222-231):
+    # the same state, a different output - checked against a literal per-token transcription
+    # of the reference's CPU routines (eflaStateUpdate / eflaComputeOutput)
+    o_ref, s_ref = ref.efla_reference_form(k, v, 1.0, readout="reference")
+    assert torch.allclose(s_ref, s_full, atol=1e-5) and not torch.allclose(o_ref, o_full, atol=1e-3)
+    S = torch.zeros(d, d, dtype=torch.float64)
+    for t in range(6):
+        kt, vt = k[0, t, 0].double(), v[0, t, 0].double()
+        lam = float(kt @ kt)
+        c = (1.0 - math.exp(-lam)) / lam
+        u = S.t() @ kt
+        S = S + c * torch.outer(kt, vt - u)
+        assert torch.allclose(o_ref[0, t, 0].double(), S @ kt, atol=1e-5)
+    with pytest.raises(ValueError):
+        ref.efla_reference_form(k, v, 1.0, readout="nope")
     # decode step == one step of the sequential recurrence
     st = torch.zeros(B, H, d, d)
     outs = [efla.delta_rule_decode_step(q[:, t], k[:, t], v[:, t], a[:, t], st) for t in range(8)]
