@@ -636,19 +636,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                       static_cast<long long>(row0) * p.ld_aux;
         __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(cbase) +
                                static_cast<long long>(row0) * p.ldc;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        // the gate/up rows of step c + 1 are requested while step c is being computed, so the
+        // latency of those global loads stays off the epilogue's critical path
+        uint4 pre[8];
+        auto fetch = [&](int c) {
           const int gcol = 2 * (n0 + c * 32) + (lane & 7) * 8;  // 64 gate/up columns per step
           const bool col_ok = n0 + c * 32 < p.N;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rl = i * 4 + (lane >> 3);
-            uint4 o = make_uint4(0, 0, 0, 0);
+            pre[i] = make_uint4(0, 0, 0, 0);
             if (row0 + rl < p.M && col_ok)
-              o = *reinterpret_cast<const uint4*>(gubase + static_cast<long long>(rl) * p.ld_aux + gcol);
-            *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = o;
+              pre[i] = *reinterpret_cast<const uint4*>(gubase + static_cast<long long>(rl) * p.ld_aux + gcol);
+          }
+        };
+        fetch(0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int gcol = 2 * (n0 + c * 32) + (lane & 7) * 8;
+          const bool col_ok = n0 + c * 32 < p.N;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = pre[i];
           }
           __syncwarp();
+          if (c + 1 < BN / 32) fetch(c + 1);
           uint32_t v[32];
           tmem_ld_32x32(taddr + c * 32, v);
           tmem_ld_wait();
@@ -694,6 +707,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                              static_cast<long long>(b) * p.batch_stride_r +
                              static_cast<long long>(row0) * p.ldr
                        : nullptr;
+        // the residual rows of chunk c2 + 1 are requested while chunk c2 is converted and
+        // stored: their global-load latency stays off the epilogue's critical path
+        uint4 pre[8];
+        auto fetch_res = [&](int c2) {
+          const int ncol = n0 + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3);
+            pre[i] = make_uint4(0, 0, 0, 0);
+            if (row0 + rl < p.M && ncol < p.N)
+              pre[i] = *reinterpret_cast<const uint4*>(rbase + static_cast<long long>(rl) * p.ldr + ncol);
+          }
+        };
+        if (rbase) fetch_res(0);
 #pragma unroll 1
         for (int c2 = 0; c2 < BN / 64; ++c2) {
           const int ncol = n0 + c2 * 64 + (lane & 7) * 8;
@@ -701,12 +728,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int rl = i * 4 + (lane >> 3);
-              uint4 o = make_uint4(0, 0, 0, 0);
-              if (row0 + rl < p.M && ncol < p.N)
-                o = *reinterpret_cast<const uint4*>(rbase + static_cast<long long>(rl) * p.ldr + ncol);
-              *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = o;
+              *reinterpret_cast<uint4*>(sb + rl * EPI_ROW_BYTES + (lane & 7) * 16) = pre[i];
             }
             __syncwarp();
+            if (c2 + 1 < BN / 64) fetch_res(c2 + 1);
           }
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {
