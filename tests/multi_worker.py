@@ -26,13 +26,13 @@ def small_cfg(world):
     return cfg
 
 
-def run_engine(comm, cfg, rank, steps=3):
+def run_engine(comm, cfg, rank, steps=3, n_micro=1):
     eng = TrainEngine(cfg, torch.device("cuda", torch.cuda.current_device()), comm, seed=0)
     data = SyntheticTokens(cfg.model.vocab_size, "zipf", 1.1, 0, rank)
     losses = []
     for _ in range(steps):
-        tok, tgt = data.batch(2, 256)
-        loss, gn = eng.train_step([(tok.cuda(), tgt.cuda())], lr=1e-3)
+        mbs = [tuple(t.cuda() for t in data.batch(2, 256)) for _ in range(n_micro)]
+        loss, gn = eng.train_step(mbs, lr=1e-3)
         losses.append((float(loss), float(gn)))
     torch.cuda.synchronize()
     return eng, losses
@@ -79,11 +79,13 @@ def main():
         for opt_kind in ("adamw", "lion"):
             cfg = small_cfg(world)
             cfg.training.optimizer = opt_kind
-            e_ref, l_ref = run_engine(Comm(), cfg, rank)
+            # two micro-batches per step: gradients accumulate, the buckets leave during the
+            # backward pass of the second one, the weight gather rides in the first forward
+            e_ref, l_ref = run_engine(Comm(), cfg, rank, n_micro=2)
             assert e_ref.zero_stage == 1 and e_ref.flat.layout == "contiguous"
             for stage in ((1, 2, 3) if opt_kind == "adamw" else (2,)):
                 cfg.runtime.zero_stage = stage
-                eng, losses = run_engine(fc, cfg, rank)
+                eng, losses = run_engine(fc, cfg, rank, n_micro=2)
                 assert eng.zero_stage == stage and eng.flat.layout == "segment"
                 assert (len(eng.gathers) > 0) == (stage == 3)
                 for (a, ga), (b, gb) in zip(l_ref, losses):

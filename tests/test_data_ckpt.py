@@ -321,3 +321,40 @@ def test_aligned_packing_and_state_resets_match_separate_documents():
     assert abs(float(packed) - num / den) < 2e-5
     # without the resets the documents leak into each other
     assert abs(float(model(tokens, targets)) - num / den) > 1e-4
+
+
+def test_bucket_plan_covers_every_ownership_range_once():
+    """ZeRO stage 2 / 3: one bucket per transformer block (its matrices, contiguous in the
+    ownership map), everything else in the runs reduced after the backward pass."""
+    import os
+
+    from ceo_b200.models.model import EflaLM
+    from ceo_b200.optim.flat import FlatParams
+    from ceo_b200.parallel.fsdp import BucketReducer
+    from ceo_b200.utils.config import Config
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = Config.parse_from_file(os.path.join(root, "configs", "smoke_cpu.yaml"))
+    cfg.model.num_layers = 3
+    model = EflaLM(cfg.model, "cpu", seed=0)
+    flat = FlatParams(model, 2, 1, layout="segment")
+
+    class _NoStream:
+        pass
+    import torch as _t
+    orig = _t.cuda.Stream
+    _t.cuda.Stream = lambda *a, **k: _NoStream()     # the planner needs no GPU
+    try:
+        red = BucketReducer(None, flat, [f"blocks.{i}." for i in range(3)])
+    finally:
+        _t.cuda.Stream = orig
+    seen = []
+    for b in red.buckets + red.rest:
+        assert b is not None
+        seen += list(range(*b))
+    assert sorted(seen) == list(range(len(flat.ranges)))
+    for i, (r0, r1) in enumerate(red.buckets):
+        names = [n for rg in flat.ranges[r0:r1] for n in rg.names]
+        assert names and all(n.startswith(f"blocks.{i}.") for n in names)
+        assert {n.rsplit(".", 1)[-1] for n in names} >= {"w_qkv", "w_o", "w_up", "w_down"}
+    rest_names = [n for r0, r1 in red.rest for rg in flat.ranges[r0:r1] for n in rg.names]
+    assert "embed_tokens" in rest_names and any(n.endswith("ln1.weight") for n in rest_names)
