@@ -146,6 +146,21 @@ def main(argv=None):
         do = torch.randn_like(o)
         rec("swiglu_bwd", time_ms(lambda: torch.autograd.grad(o, gu, do, retain_graph=True)), 0,
             5.0 * M * Fh * 2)
+    if want("swiglu"):
+        # the same two ops inside the GEMM epilogues (what the MLP runs): compare the pair
+        # (plain GEMM + SwiGLU kernel) with the one fused launch
+        w_up = (torch.randn(2 * Fh, D, device=dev) * 0.02).bfloat16()
+        w_dn = (torch.randn(D, Fh, device=dev) * 0.02).bfloat16()
+        gu_b = torch.empty(M, 2 * Fh, device=dev, dtype=torch.bfloat16)
+        act_b = torch.empty(M, Fh, device=dev, dtype=torch.bfloat16)
+        dy_b = torch.randn(M, D, device=dev).bfloat16()
+        dgu_b = torch.empty_like(gu_b)
+        rec(f"gemm_fwd_gate_up + SwiGLU epilogue {M}x{2 * Fh}x{D}",
+            time_ms(lambda: G._gemm_swiglu(x, w_up, gu_b, M, 2 * Fh, D, False, 1, act_b)),
+            2.0 * M * 2 * Fh * D)
+        rec(f"gemm_dgrad_down + SwiGLU backward epilogue {M}x{Fh}x{D}",
+            time_ms(lambda: G._gemm_swiglu(dy_b, w_dn, dgu_b, M, Fh, D, True, 2, gu_b)),
+            2.0 * M * Fh * D)
     if want("efla"):
         from ..ops import efla as E
         from ..parallel.cp import efla_flops
