@@ -96,6 +96,58 @@ def main(argv=None):
         out[-1]["local_gemm_ms"] = round(loc, 4)
         if rank == 0:
             print(json.dumps({"local_gemm_ms": round(loc, 4)}), flush=True)
+    # ---- FSDP: the weight all-gather inside the GEMM that consumes it (ZeRO stage 3) --------
+    # 1.3B shapes: x (M, 2048) against w_qkv (6208, 2048) gathered from row shards, with w_o
+    # (2048, 2048) gathered by the same launch; the library composition all-gathers both
+    # weights and then multiplies.
+    import math
+
+    from ..ops import _lib
+    from .symm import SymmetricBuffer
+    Dm = 2048
+    for name, n_w, n_x in (("fsdp qkv (+w_o)", 6208, Dm * Dm), ("fsdp gate_up (+w_down)", 11264,
+                                                               Dm * 5632)):
+        if n_w % world or n_x % (8 * world):
+            continue
+        wbuf = SymmetricBuffer(n_w * Dm * 2, fc.group)
+        xbuf = SymmetricBuffer(n_x * 2, fc.group)
+        w_full = wbuf.view(torch.bfloat16, n_w * Dm).view(n_w, Dm)
+        w_full.normal_(0, 0.02, generator=g)
+        e_full = xbuf.view(torch.bfloat16, n_x)
+        xin = torch.randn(M, Dm, device="cuda", generator=g).bfloat16()
+        rows_w = n_w // world
+        blk = math.gcd(rows_w, 64)
+        flags = torch.zeros(n_w // blk, dtype=torch.int32, device="cuda")
+        outw = torch.empty(M, n_w, dtype=torch.bfloat16, device="cuda")
+        calls = [0]
+        st = _lib.status_word(torch.device("cuda", torch.cuda.current_device()))
+
+        def fused():
+            calls[0] += 1
+            fc.device_barrier()   # every rank's shard is final (the optimizer's last barrier)
+            _lib.check(_lib.lib().ceo_ag_gemm_bf16(
+                wbuf.table(), 2, xin.data_ptr(), outw.data_ptr(), M, n_w, Dm, Dm, n_w, 0, 0, 0, 1.0,
+                None, 0, flags.data_ptr(), calls[0], rank, world, 8, blk, xbuf.table(),
+                n_x * 2 // world, st.data_ptr(), _lib.stream()), "ceo_ag_gemm_bf16")
+
+        def nccl():
+            sw = w_full[rank * rows_w:(rank + 1) * rows_w]
+            dist.all_gather_into_tensor(w_full, sw)
+            ne = n_x // world
+            dist.all_gather_into_tensor(e_full, e_full[rank * ne:(rank + 1) * ne])
+            plain_gemm(xin, w_full)
+        f = timed(fused, fc)
+        n = timed(nccl, fc)
+        loc = timed(lambda: plain_gemm(xin, w_full), fc)
+        rec(f"{name} {M}x{n_w}x{Dm}", f, n, 2.0 * M * n_w * Dm,
+            (world - 1) / world * (n_w * Dm + n_x) * 2)
+        out[-1]["local_gemm_ms"] = round(loc, 4)
+        if rank == 0:
+            print(json.dumps({"local_gemm_ms": round(loc, 4)}), flush=True)
+        torch.cuda.synchronize()
+        fc.barrier()
+        wbuf.close()
+        xbuf.close()
     tp.close()
     fc.close()
     if a.json and rank == 0:
