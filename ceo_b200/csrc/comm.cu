@@ -86,6 +86,8 @@ struct ZRange {
   int gather, pad;
 };
 
+constexpr int ZT = 512;  // threads per CTA of the zero-step and bucket-reduce kernels
+
 struct ZeroStepArgs {
   PeerPtrs grads;    // float*  full gradient buffers (one per rank)
   PeerPtrs params;   // bf16*   full parameter buffers
@@ -110,25 +112,27 @@ struct ZeroStepArgs {
 
 // Sum of every rank's gradients over this rank's slice of ranges [r0, r1), left in this rank's
 // own gradient buffer; returns the thread's share of the squared norm of the sums.
-// WU = the world size rounded up to 2, 4 or 8.  A thread handles 8 / WU float4 positions per
-// iteration and issues all of their loads (8 in flight) before it consumes any: with one load
+// WU = the world size rounded up to 2, 4 or 8.  A thread handles LOADS / WU float4 positions
+// per iteration and issues all of their loads (LOADS in flight) before it consumes any: with one load
 // in flight per thread the links and HBM idle.  The sum runs in rank order (reproducible).
-template <int WU>
+template <int WU, int LOADS>
 __device__ __forceinline__ float reduce_ranges_t(const PeerPtrs& grads, const ZRange* ranges,
                                                  int r0, int r1, int rank, int world,
                                                  long long tid, long long nth) {
-  constexpr int NB = 8 / WU;
+  constexpr int NB = LOADS / WU;
   float ss = 0.f;
   for (int ri = r0; ri < r1; ++ri) {
     const ZRange rg = ranges[ri];
     const long long base = rg.goff + rank * rg.len;
     float* gl = reinterpret_cast<float*>(grads.p[rank]) + base;
     const long long n4 = rg.len >> 2;
-    for (long long i0 = tid; i0 < n4; i0 += nth * NB) {
+    // a CTA takes NB * blockDim consecutive positions per iteration: the positions of one
+    // thread sit at constant offsets from one another (one address register per stream)
+    for (long long i0 = (tid - threadIdx.x) * NB + threadIdx.x; i0 < n4; i0 += nth * NB) {
       float4 g[NB][WU];
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        const long long i = i0 + b * nth;
+        const long long i = i0 + b * ZT;
 #pragma unroll
         for (int r = 0; r < WU; ++r)
           if (r < world && i < n4)  // L2-only load: never a stale L1 line of peer data
@@ -137,7 +141,7 @@ __device__ __forceinline__ float reduce_ranges_t(const PeerPtrs& grads, const ZR
       }
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        const long long i = i0 + b * nth;
+        const long long i = i0 + b * ZT;
         if (i >= n4) break;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -150,15 +154,92 @@ __device__ __forceinline__ float reduce_ranges_t(const PeerPtrs& grads, const ZR
   }
   return ss;
 }
+template <int LOADS>
 __device__ __forceinline__ float reduce_ranges(const PeerPtrs& grads, const ZRange* ranges, int r0,
                                                int r1, int rank, int world, long long tid,
                                                long long nth) {
-  if (world <= 2) return reduce_ranges_t<2>(grads, ranges, r0, r1, rank, world, tid, nth);
-  if (world <= 4) return reduce_ranges_t<4>(grads, ranges, r0, r1, rank, world, tid, nth);
-  return reduce_ranges_t<8>(grads, ranges, r0, r1, rank, world, tid, nth);
+  if (world <= 2) return reduce_ranges_t<2, LOADS>(grads, ranges, r0, r1, rank, world, tid, nth);
+  if (world <= 4) return reduce_ranges_t<4, LOADS>(grads, ranges, r0, r1, rank, world, tid, nth);
+  return reduce_ranges_t<8, LOADS>(grads, ranges, r0, r1, rank, world, tid, nth);
 }
 
-__global__ void __launch_bounds__(512)
+// The optimizer update of this rank's slice of one range (KIND 0 AdamW, 1 Lion).  A thread
+// handles two float4 positions per iteration and issues the loads of all four streams of
+// both (8 in flight) before it computes; the gradient slice is zeroed as it is consumed.
+template <int KIND>
+__device__ __forceinline__ void update_range(const ZeroStepArgs& a, const ZRange rg, float gs,
+                                             long long tid, long long nth) {
+  constexpr int U = 2;
+  const long long base = rg.goff + a.rank * rg.len;
+  float4* __restrict__ gl = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.grads.p[a.rank]) + base);
+  float4* __restrict__ mm = reinterpret_cast<float4*>(a.m + rg.loff);
+  float4* __restrict__ vv = reinterpret_cast<float4*>(KIND == 0 ? a.v + rg.loff : nullptr);
+  float4* __restrict__ ms = reinterpret_cast<float4*>(a.master + rg.loff);
+  const long long n4 = rg.len >> 2;
+  const float lr = a.lr, b1 = a.b1, b2 = a.b2;
+  // a CTA takes U * ZT consecutive positions per iteration (see reduce_ranges_t)
+  for (long long i0 = (tid - threadIdx.x) * U + threadIdx.x; i0 < n4; i0 += nth * U) {
+    float4 g4[U], m4[U], v4[U], p4[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * ZT;
+      if (i < n4) {
+        (void)CEO_IDX(base + 4 * i, a.total - 3, 501);  // the slice stays inside the flat buffers
+        g4[u] = gl[i];
+        m4[u] = mm[i];
+        p4[u] = ms[i];
+        if (KIND == 0) v4[u] = vv[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * ZT;
+      if (i >= n4) break;
+      const float decay = 1.f - lr * ((base + 4 * i < a.decay_end) ? a.wd : 0.f);
+      const float* gp = reinterpret_cast<const float*>(&g4[u]);
+      float* mp = reinterpret_cast<float*>(&m4[u]);
+      float* vp = reinterpret_cast<float*>(&v4[u]);
+      float* pp = reinterpret_cast<float*>(&p4[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float g = gp[j] * gs;
+        if (KIND == 0) {
+          mp[j] = b1 * mp[j] + (1.f - b1) * g;
+          vp[j] = b2 * vp[j] + (1.f - b2) * g * g;
+          pp[j] = pp[j] * decay - lr * (mp[j] * a.bc1_inv) / (sqrtf(vp[j] * a.bc2_inv) + a.eps);
+        } else {
+          const float uu = b1 * mp[j] + (1.f - b1) * g;
+          pp[j] = pp[j] * decay - lr * (uu > 0.f ? 1.f : (uu < 0.f ? -1.f : 0.f));
+          mp[j] = b2 * mp[j] + (1.f - b2) * g;
+        }
+      }
+      gl[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // consumed
+      mm[i] = m4[u];
+      if (KIND == 0) vv[i] = v4[u];
+      ms[i] = p4[u];
+      uint2 packed;
+      bf162* h = reinterpret_cast<bf162*>(&packed);
+      h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
+      h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
+      if (rg.gather) {
+        for (int r = 0; r < a.world; ++r)
+          reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[r]) + base)[i] = packed;
+      } else {
+        reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[a.rank]) + base)[i] = packed;
+      }
+    }
+  }
+}
+
+// A skipped step (non-finite norm): the owned gradient slices are dropped, nothing else moves.
+__device__ __forceinline__ void zero_owned(const ZeroStepArgs& a, const ZRange rg, long long tid,
+                                           long long nth) {
+  float4* gl = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.grads.p[a.rank]) + rg.goff +
+                                         a.rank * rg.len);
+  for (long long i = tid; i < (rg.len >> 2); i += nth) gl[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__global__ void __launch_bounds__(ZT, 1)
 zero_step_kernel(const ZeroStepArgs a) {
   cg::grid_group grid = cg::this_grid();
   __shared__ float red[33];
@@ -183,7 +264,7 @@ zero_step_kernel(const ZeroStepArgs a) {
 
   // ---- phase 1: reduce this rank's slices over all ranks, keep the sums locally ---------
   if (a.do_reduce) {
-    float ss = reduce_ranges(a.grads, a.ranges, 0, a.nranges, a.rank, a.world, tid, nth);
+    float ss = reduce_ranges<8>(a.grads, a.ranges, 0, a.nranges, a.rank, a.world, tid, nth);
     ss = block_reduce_sum(ss, red);
     if (threadIdx.x == 0) atomicAdd(a.local_acc, ss);
   }
@@ -217,56 +298,9 @@ zero_step_kernel(const ZeroStepArgs a) {
 
   // ---- phase 2: update the slices; bf16 results stored into the parameter buffers --------
   for (int ri = 0; ri < a.nranges; ++ri) {
-    const ZRange rg = a.ranges[ri];
-    const long long base = rg.goff + a.rank * rg.len;
-    float* gl = reinterpret_cast<float*>(a.grads.p[a.rank]) + base;
-    float4* mm = reinterpret_cast<float4*>(a.m + rg.loff);
-    float4* vv = reinterpret_cast<float4*>(a.v ? a.v + rg.loff : nullptr);
-    float4* ms = reinterpret_cast<float4*>(a.master + rg.loff);
-    const long long n4 = rg.len >> 2;
-    for (long long i = tid; i < n4; i += nth) {
-      (void)CEO_IDX(base + 4 * i, a.total - 3, 501);  // the slice stays inside the flat buffers
-      const float4 g4 = reinterpret_cast<const float4*>(gl)[i];
-      reinterpret_cast<float4*>(gl)[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // consumed: zero it
-      if (skip) continue;
-      float4 m4 = mm[i];
-      float4 p4 = ms[i];
-      const float wd = (base + 4 * i < a.decay_end) ? a.wd : 0.f;
-      const float gg[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
-      float* mp = reinterpret_cast<float*>(&m4);
-      float* pp = reinterpret_cast<float*>(&p4);
-      if (a.kind == 0) {
-        float4 v4 = vv[i];
-        float* vp = reinterpret_cast<float*>(&v4);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mp[j] = a.b1 * mp[j] + (1.f - a.b1) * gg[j];
-          vp[j] = a.b2 * vp[j] + (1.f - a.b2) * gg[j] * gg[j];
-          pp[j] = pp[j] * (1.f - a.lr * wd) -
-                  a.lr * (mp[j] * a.bc1_inv) / (sqrtf(vp[j] * a.bc2_inv) + a.eps);
-        }
-        vv[i] = v4;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float u = a.b1 * mp[j] + (1.f - a.b1) * gg[j];
-          pp[j] = pp[j] * (1.f - a.lr * wd) - a.lr * (u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f));
-          mp[j] = a.b2 * mp[j] + (1.f - a.b2) * gg[j];
-        }
-      }
-      mm[i] = m4;
-      ms[i] = p4;
-      uint2 packed;
-      bf162* h = reinterpret_cast<bf162*>(&packed);
-      h[0] = __floats2bfloat162_rn(pp[0], pp[1]);
-      h[1] = __floats2bfloat162_rn(pp[2], pp[3]);
-      if (rg.gather) {
-        for (int r = 0; r < a.world; ++r)
-          reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[r]) + base)[i] = packed;
-      } else {
-        reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.params.p[a.rank]) + base)[i] = packed;
-      }
-    }
+    if (skip) zero_owned(a, a.ranges[ri], tid, nth);
+    else if (a.kind == 0) update_range<0>(a, a.ranges[ri], gs, tid, nth);
+    else update_range<1>(a, a.ranges[ri], gs, tid, nth);
   }
   // every rank is past barrier 1, so nobody reads this rank's gradients any more: zero the
   // parts other ranks own (the owned slices were zeroed above by the threads that read them)
@@ -291,14 +325,14 @@ zero_step_kernel(const ZeroStepArgs a) {
 // squared norm is added to local_acc[0].  The launch is preceded by a flag barrier (its own
 // kernel on the same stream) that tells every rank the bucket's gradients are final
 // everywhere; when that barrier's wait ran out the status word is set and nothing is reduced.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(ZT)
 zero_bucket_reduce_kernel(PeerPtrs grads, const ZRange* ranges, int r0, int r1, int rank,
                           int world, float* local_acc, const int* status) {
   __shared__ float red[33];
   if (*reinterpret_cast<const volatile int*>(status) != 0) return;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
-  float ss = reduce_ranges(grads, ranges, r0, r1, rank, world, tid, nth);
+  float ss = reduce_ranges<8>(grads, ranges, r0, r1, rank, world, tid, nth);
   ss = block_reduce_sum(ss, red);
   if (threadIdx.x == 0) atomicAdd(local_acc, ss);
 }
@@ -407,7 +441,7 @@ extern "C" int ceo_zero_step(void* const* grads, void* const* params, void* cons
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, zero_step_kernel, 512, 0);
     if (occ < 1) return -5;
-    full_grid = sms * (occ > 2 ? 2 : occ);
+    full_grid = sms * (occ > 2 ? 2 : occ);  // one CTA of 16 warps per SM at 128 registers
   }
   int grid = full_grid;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;

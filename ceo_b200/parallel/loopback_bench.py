@@ -49,6 +49,8 @@ def main(argv=None):
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--no-reduce", action="store_true",
+                    help="zero_step: skip the reduce-scatter phase (as after bucket reductions)")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
     L = _lib.lib()
@@ -76,12 +78,13 @@ def main(argv=None):
                                        master.data_ptr(), m.data_ptr(), v.data_ptr(),
                                        acc.data_ptr(), norm.data_ptr(), clip.data_ptr(),
                                        st.data_ptr(), ranges.data_ptr(), 1, total, total, 0, W,
-                                       peers.next_epoch(), 0, 1, 1e-3, 0.9, 0.95, 1e-8, 0.1,
+                                       peers.next_epoch(), 0, 0 if a.no_reduce else 1, 1e-3, 0.9,
+                                       0.95, 1e-8, 0.1,
                                        step[0], 1.0 / W, 1.0, 0, _lib.stream()), "ceo_zero_step")
         ms = _time(run, a.iters)
         # per launch: W fp32 gradient slices read, the rank's fp32 master / m / v read + written,
         # bf16 slice stored W times, the whole local gradient buffer zeroed
-        nbytes = shard * (4 * W + 24 + 2 * W) + total * 4
+        nbytes = shard * ((0 if a.no_reduce else 4 * W) + 24 + 2 * W) + total * 4
         rec.update(ms=ms, flat_elements=total, bytes=nbytes, tb_per_s=nbytes / ms / 1e9)
     elif a.op in ("ag_gemm", "ag_gemm_w"):
         M, K, N = a.tokens, a.d_model, a.n

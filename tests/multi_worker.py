@@ -96,7 +96,7 @@ def main():
                                               eng.model.named_parameters()):
                     if p1.numel() > 1:
                         rel = ((p1.float() - p2.float()).norm() / (p1.float().norm() + 1e-9)).item()
-                        assert rel < (2e-3 if opt_kind == "adamw" else 2e-2), (opt_kind, stage, n1, rel)
+                        assert rel < (4e-3 if opt_kind == "adamw" else 2e-2), (opt_kind, stage, n1, rel)
                 # identical parameters on every rank, gradients consumed
                 chk = torch.stack([p.float().sum() for p in eng.model.parameters()]).sum().reshape(1)
                 allc = cmp.all_gather_cat(chk)
