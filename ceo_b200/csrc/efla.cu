@@ -1165,6 +1165,10 @@ __device__ __forceinline__ float group_reduce_sum(float v) {
   return v;
 }
 
+// A warp takes U * RPW consecutive (token, head) rows per iteration and requests all of their
+// 16-byte pieces before it uses any (2 U loads in flight per lane forward, 4 U backward): with
+// one row group in flight per warp these kernels ran at half the memory bandwidth.
+// rows * H < 2^31 (checked on the host), so row ids divide as 32-bit integers.
 template <int D>
 __global__ void __launch_bounds__(256)
 efla_prep_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
@@ -1172,42 +1176,51 @@ efla_prep_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                      bf16* __restrict__ kn, float* __restrict__ rq, float* __restrict__ rk,
                      float* __restrict__ alpha, long long rows, int H, long long qs, long long ks,
                      int normalize) {
-  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  constexpr int LPR = D / 8, RPW = 32 / LPR, U = 4;
   const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
-  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const long long total = rows * H;
-  for (long long id0 = wid * RPW; id0 < total; id0 += nw * RPW) {
-    const long long id = id0 + rw;
-    const bool live = id < total;
-    const long long tok = live ? id / H : 0;
-    const int h = live ? static_cast<int>(id - tok * H) : 0;
-    float qv[8], kv[8];
-    unpack8(*reinterpret_cast<const uint4*>(q + tok * qs + h * D + sub * 8), qv);
-    unpack8(*reinterpret_cast<const uint4*>(k + tok * ks + h * D + sub * 8), kv);
-    float sq = 0.f, sk = 0.f;
+  const unsigned wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned nw = (gridDim.x * blockDim.x) >> 5;
+  const unsigned total = static_cast<unsigned>(rows * H);
+  for (unsigned id0 = wid * (RPW * U); id0 < total; id0 += nw * (RPW * U)) {
+    uint4 qp[U], kp[U];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      sq += qv[e] * qv[e];
-      sk += kv[e] * kv[e];
+    for (int u = 0; u < U; ++u) {
+      const unsigned id = id0 + u * RPW + rw;
+      const unsigned idc = id < total ? id : 0;
+      const unsigned tok = idc / static_cast<unsigned>(H), h = idc - tok * H;
+      qp[u] = *reinterpret_cast<const uint4*>(q + tok * qs + h * D + sub * 8);
+      kp[u] = *reinterpret_cast<const uint4*>(k + tok * ks + h * D + sub * 8);
     }
-    sq = group_reduce_sum<LPR>(sq);
-    sk = group_reduce_sum<LPR>(sk);
-    const float iq = normalize ? rsqrtf(sq + 1e-6f) : 1.f;
-    const float ik = normalize ? rsqrtf(sk + 1e-6f) : 1.f;
-    if (!live) continue;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      qv[e] *= iq;
-      kv[e] *= ik;
-    }
-    *reinterpret_cast<uint4*>(qn + id * D + sub * 8) = pack8(qv);
-    *reinterpret_cast<uint4*>(kn + id * D + sub * 8) = pack8(kv);
-    if (sub == 0) {
-      const float b = beta_scalar ? beta[0] : beta[id];
-      rq[id] = iq;
-      rk[id] = ik;
-      alpha[id] = normalize ? -expm1f(-b) : efla_coeff(b, sk);
+    for (int u = 0; u < U; ++u) {
+      const unsigned id = id0 + u * RPW + rw;
+      float qv[8], kv[8];
+      unpack8(qp[u], qv);
+      unpack8(kp[u], kv);
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sq += qv[e] * qv[e];
+        sk += kv[e] * kv[e];
+      }
+      sq = group_reduce_sum<LPR>(sq);
+      sk = group_reduce_sum<LPR>(sk);
+      const float iq = normalize ? rsqrtf(sq + 1e-6f) : 1.f;
+      const float ik = normalize ? rsqrtf(sk + 1e-6f) : 1.f;
+      if (id >= total) continue;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        qv[e] *= iq;
+        kv[e] *= ik;
+      }
+      *reinterpret_cast<uint4*>(qn + static_cast<long long>(id) * D + sub * 8) = pack8(qv);
+      *reinterpret_cast<uint4*>(kn + static_cast<long long>(id) * D + sub * 8) = pack8(kv);
+      if (sub == 0) {
+        const float b = beta_scalar ? beta[0] : beta[id];
+        rq[id] = iq;
+        rk[id] = ik;
+        alpha[id] = normalize ? -expm1f(-b) : efla_coeff(b, sk);
+      }
     }
   }
 }
@@ -1223,63 +1236,77 @@ efla_prep_bwd_kernel(const bf16* __restrict__ dqn, const bf16* __restrict__ dkn,
                      const float* __restrict__ dalpha, bf16* __restrict__ dq,
                      bf16* __restrict__ dk, float* __restrict__ dbeta, long long rows, int H,
                      long long dqs, long long dks, int normalize) {
-  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  constexpr int LPR = D / 8, RPW = 32 / LPR, U = 2;
   const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
-  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const long long total = rows * H;
-  for (long long id0 = wid * RPW; id0 < total; id0 += nw * RPW) {
-    const long long id = id0 + rw;
-    const bool live = id < total;
-    const long long idc = live ? id : 0;
-    const long long tok = idc / H;
-    const int h = static_cast<int>(idc - tok * H);
-    float qv[8], kv[8], gq[8], gk[8];
-    const long long o = idc * D + sub * 8;
-    unpack8(*reinterpret_cast<const uint4*>(qn + o), qv);
-    unpack8(*reinterpret_cast<const uint4*>(kn + o), kv);
-    unpack8(*reinterpret_cast<const uint4*>(dqn + o), gq);
-    unpack8(*reinterpret_cast<const uint4*>(dkn + o), gk);
-    float dq_dot = 0.f, dk_dot = 0.f, sk = 0.f;
+  const unsigned wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned nw = (gridDim.x * blockDim.x) >> 5;
+  const unsigned total = static_cast<unsigned>(rows * H);
+  for (unsigned id0 = wid * (RPW * U); id0 < total; id0 += nw * (RPW * U)) {
+    uint4 qp[U], kp[U], gqp[U], gkp[U];
+    float bb[U], daa[U], iqq[U], ikk[U];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      dq_dot += qv[e] * gq[e];
-      dk_dot += kv[e] * gk[e];
-      sk += kv[e] * kv[e];
+    for (int u = 0; u < U; ++u) {
+      const unsigned id = id0 + u * RPW + rw;
+      const unsigned idc = id < total ? id : 0;
+      const long long o = static_cast<long long>(idc) * D + sub * 8;
+      qp[u] = *reinterpret_cast<const uint4*>(qn + o);
+      kp[u] = *reinterpret_cast<const uint4*>(kn + o);
+      gqp[u] = *reinterpret_cast<const uint4*>(dqn + o);
+      gkp[u] = *reinterpret_cast<const uint4*>(dkn + o);
+      bb[u] = beta_scalar ? beta[0] : beta[idc];
+      daa[u] = dalpha[idc];
+      iqq[u] = rq[idc];
+      ikk[u] = rk[idc];
     }
-    dq_dot = group_reduce_sum<LPR>(dq_dot);
-    dk_dot = group_reduce_sum<LPR>(dk_dot);
-    sk = group_reduce_sum<LPR>(sk);
-    if (!live) continue;
-    const float b = beta_scalar ? beta[0] : beta[id];
-    const float da = dalpha[id];
-    float kcoef = 0.f, db;
-    if (normalize) {
-      db = da * __expf(-b);
-    } else {
-      const float lam = sk;
-      const float ex = __expf(-b * lam);
-      db = da * ex;
-      float dcdl;
-      if (lam <= 1e-6f) dcdl = -0.5f * b * b + b * b * b * lam * (1.f / 3.f);
-      else dcdl = (b * lam * ex + expm1f(-b * lam)) / (lam * lam);
-      kcoef = 2.f * da * dcdl;
-    }
-    const float iq = rq[id], ik = rk[id];
-    float oq[8], ok[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      if (normalize) {
-        oq[e] = iq * (gq[e] - qv[e] * dq_dot);
-        ok[e] = ik * (gk[e] - kv[e] * dk_dot);
-      } else {
-        oq[e] = gq[e];
-        ok[e] = gk[e] + kcoef * kv[e];
+    for (int u = 0; u < U; ++u) {
+      const unsigned id = id0 + u * RPW + rw;
+      float qv[8], kv[8], gq[8], gk[8];
+      unpack8(qp[u], qv);
+      unpack8(kp[u], kv);
+      unpack8(gqp[u], gq);
+      unpack8(gkp[u], gk);
+      float dq_dot = 0.f, dk_dot = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        dq_dot += qv[e] * gq[e];
+        dk_dot += kv[e] * gk[e];
+        sk += kv[e] * kv[e];
       }
+      dq_dot = group_reduce_sum<LPR>(dq_dot);
+      dk_dot = group_reduce_sum<LPR>(dk_dot);
+      sk = group_reduce_sum<LPR>(sk);
+      if (id >= total) continue;
+      const float b = bb[u], da = daa[u];
+      float kcoef = 0.f, db;
+      if (normalize) {
+        db = da * __expf(-b);
+      } else {
+        const float lam = sk;
+        const float ex = __expf(-b * lam);
+        db = da * ex;
+        float dcdl;
+        if (lam <= 1e-6f) dcdl = -0.5f * b * b + b * b * b * lam * (1.f / 3.f);
+        else dcdl = (b * lam * ex + expm1f(-b * lam)) / (lam * lam);
+        kcoef = 2.f * da * dcdl;
+      }
+      const float iq = iqq[u], ik = ikk[u];
+      float oq[8], ok[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (normalize) {
+          oq[e] = iq * (gq[e] - qv[e] * dq_dot);
+          ok[e] = ik * (gk[e] - kv[e] * dk_dot);
+        } else {
+          oq[e] = gq[e];
+          ok[e] = gk[e] + kcoef * kv[e];
+        }
+      }
+      const unsigned tok = id / static_cast<unsigned>(H), h = id - tok * H;
+      *reinterpret_cast<uint4*>(dq + tok * dqs + h * D + sub * 8) = pack8(oq);
+      *reinterpret_cast<uint4*>(dk + tok * dks + h * D + sub * 8) = pack8(ok);
+      if (sub == 0) dbeta[id] = db;
     }
-    *reinterpret_cast<uint4*>(dq + tok * dqs + h * D + sub * 8) = pack8(oq);
-    *reinterpret_cast<uint4*>(dk + tok * dks + h * D + sub * 8) = pack8(ok);
-    if (sub == 0) dbeta[id] = db;
   }
 }
 
@@ -1508,12 +1535,12 @@ extern "C" int ceo_efla_prep_fwd(const void* q, const void* k, const float* beta
                                  void* qn, void* kn, float* rq, float* rk, float* alpha,
                                  long long rows, int H, int D, long long q_stride,
                                  long long k_stride, int normalize, cudaStream_t stream) {
-  if (rows <= 0 || H <= 0 || (D != 64 && D != 128)) return -5;
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || rows * H >= (1LL << 31)) return -5;
   if (((q_stride | k_stride) & 7) ||
       ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
         reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn)) & 15))
     return -2;  // rows move as 16-byte accesses
-  const int grid = grid_for(rows * H, 8 * (D == 64 ? 4 : 2), 148 * 16);
+  const int grid = grid_for(rows * H, 8 * 4 * (D == 64 ? 4 : 2), 148 * 4);  // one resident wave
   if (D == 64)
     efla_prep_fwd_kernel<64><<<grid, 256, 0, stream>>>(
         static_cast<const bf16*>(q), static_cast<const bf16*>(k), beta, beta_scalar,
@@ -1532,13 +1559,13 @@ extern "C" int ceo_efla_prep_bwd(const void* dqn, const void* dkn, const void* q
                                  int beta_scalar, const float* dalpha, void* dq, void* dk,
                                  float* dbeta, long long rows, int H, int D, long long dq_stride,
                                  long long dk_stride, int normalize, cudaStream_t stream) {
-  if (rows <= 0 || H <= 0 || (D != 64 && D != 128)) return -5;
+  if (rows <= 0 || H <= 0 || (D != 64 && D != 128) || rows * H >= (1LL << 31)) return -5;
   if (((dq_stride | dk_stride) & 7) ||
       ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
         reinterpret_cast<uintptr_t>(dqn) | reinterpret_cast<uintptr_t>(dkn) |
         reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn)) & 15))
     return -2;  // rows move as 16-byte accesses
-  const int grid = grid_for(rows * H, 8 * (D == 64 ? 4 : 2), 148 * 16);
+  const int grid = grid_for(rows * H, 8 * 2 * (D == 64 ? 4 : 2), 148 * 3);  // one resident wave
   if (D == 64)
     efla_prep_bwd_kernel<64><<<grid, 256, 0, stream>>>(
         static_cast<const bf16*>(dqn), static_cast<const bf16*>(dkn), static_cast<const bf16*>(qn),

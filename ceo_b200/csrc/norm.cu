@@ -222,15 +222,18 @@ rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res
   for (int i = 0; i < NVT; ++i) wp[i] = reinterpret_cast<const uint4*>(w)[threadIdx.x + i * NORM_THREADS];
   int it = 0;
   for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, it ^= 1) {
-    uint4 xv[R][NVT];
+    uint4 xv[R][NVT], rv[R][NVT];
     float ss[R];
+    // every load of the iteration (x and the residual, R rows) is issued before any is used
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const bool okr = row0 + r < rows;
       const size_t off = static_cast<size_t>(okr ? row0 + r : row0) * D;
 #pragma unroll
-      for (int i = 0; i < NVT; ++i)
+      for (int i = 0; i < NVT; ++i) {
         xv[r][i] = reinterpret_cast<const uint4*>(x + off)[threadIdx.x + i * NORM_THREADS];
+        if (res) rv[r][i] = reinterpret_cast<const uint4*>(res + off)[threadIdx.x + i * NORM_THREADS];
+      }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -243,7 +246,7 @@ rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res
         unpack8(xv[r][i], v);
         if (res) {
           float t[8];
-          unpack8(reinterpret_cast<const uint4*>(res + off)[threadIdx.x + i * NORM_THREADS], t);
+          unpack8(rv[r][i], t);
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] += t[j];
           xv[r][i] = pack8(v);  // normalise exactly what is stored as h
@@ -299,8 +302,10 @@ rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   }
   int it = 0;
   for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, it ^= 1) {
-    uint4 xv[R][NVT], gv[R][NVT];
+    uint4 xv[R][NVT], gv[R][NVT], dv[R][NVT];
     float rs[R];
+    // x, dy and the residual stream's gradient of all R rows are requested together: the
+    // second round trip a late dres load would add is as long as the first
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const bool okr = row0 + r < rows;
@@ -310,6 +315,7 @@ rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
       for (int i = 0; i < NVT; ++i) {
         xv[r][i] = reinterpret_cast<const uint4*>(x + off)[threadIdx.x + i * NORM_THREADS];
         gv[r][i] = reinterpret_cast<const uint4*>(dy + off)[threadIdx.x + i * NORM_THREADS];
+        if (dres) dv[r][i] = reinterpret_cast<const uint4*>(dres + off)[threadIdx.x + i * NORM_THREADS];
       }
     }
 #pragma unroll
@@ -347,7 +353,7 @@ rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
         for (int j = 0; j < 8; ++j) o[j] = gf[j] * wv[i][j] * rs[r] - xf[j] * coef;
         if (dres) {
           float t[8];
-          unpack8(reinterpret_cast<const uint4*>(dres + off)[threadIdx.x + i * NORM_THREADS], t);
+          unpack8(dv[r][i], t);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += t[j];
         }
@@ -521,6 +527,18 @@ static bool norm_shape_ok(int rows, int D) {
 
 using namespace ceo;
 
+// CTAs of NORM_THREADS threads of `kernel` that the device holds at once.
+template <typename K>
+static int resident_ctas(K kernel) {
+  int dev = 0, sms = 148, occ = 1;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, NORM_THREADS, 0) != cudaSuccess ||
+      occ < 1)
+    occ = 1;
+  return sms * occ;
+}
+
 extern "C" int ceo_norm_bwd_blocks(int rows) {
   int g = rows < CEO_NORM_BWD_MAX_BLOCKS ? rows : CEO_NORM_BWD_MAX_BLOCKS;
   return g < 1 ? 1 : g;
@@ -533,7 +551,14 @@ extern "C" int ceo_rmsnorm_fwd(const void* x, const void* residual, const void* 
   if (D == 2048 || D == 4096) {
     constexpr int R = 4;
     int g = (rows + R - 1) / R;
-    if (g > 148 * 4) g = 148 * 4;
+    // one wave: a grid larger than what is resident at once adds a partly filled second wave
+    static int cap1 = 0, cap2 = 0;
+    if (cap1 == 0) {
+      cap1 = resident_ctas(rmsnorm_fwd_rows_kernel<1, R>);
+      cap2 = resident_ctas(rmsnorm_fwd_rows_kernel<2, R>);
+    }
+    const int cap = D == 2048 ? cap1 : cap2;
+    if (g > cap) g = cap;
     if (D == 2048)
       rmsnorm_fwd_rows_kernel<1, R><<<g, NORM_THREADS, 0, stream>>>(
           static_cast<const bf16*>(x), static_cast<const bf16*>(residual),

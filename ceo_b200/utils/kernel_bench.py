@@ -139,6 +139,16 @@ def main(argv=None):
         dy = torch.randn_like(y)
         rec("rmsnorm_bwd", time_ms(lambda: torch.autograd.grad(y, (xr, w), dy, retain_graph=True)),
             0, 3.0 * M * D * 2)
+        # the forms the transformer block uses: residual add fused into the forward kernel
+        # (x, residual in; h, y out), residual stream's gradient added in the backward kernel
+        r2 = torch.randn_like(x)
+        rec("rmsnorm_fwd (+ residual)", time_ms(lambda: N.rmsnorm(x, w, residual=r2)), 0,
+            4.0 * M * D * 2)
+        y2, h2 = N.rmsnorm(xr, w, skip=True)
+        dh = torch.randn_like(y)
+        rec("rmsnorm_bwd (+ residual gradient)",
+            time_ms(lambda: torch.autograd.grad((y2, h2), (xr, w), (dy, dh), retain_graph=True)),
+            0, 4.0 * M * D * 2)
     if want("swiglu"):
         gu = torch.randn(M, 2 * Fh, device=dev).bfloat16().requires_grad_()
         rec("swiglu_fwd", time_ms(lambda: N.swiglu(gu)), 0, 3.0 * M * Fh * 2)
