@@ -42,6 +42,9 @@ constexpr int ACT_WARP_BYTES = 32 * ACT_ROW_BYTES;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
                           4 * EPI_WARP_BYTES /*store staging*/ + 4 * ACT_WARP_BYTES /*SwiGLU*/;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t AG_CHUNK = 32768;                             // bytes per bulk copy
+constexpr int AG_RING = (STAGES * STAGE_BYTES) / AG_CHUNK;       // 6 buffers of 32 KB
+constexpr int AG_RING_BAR = 16;  // mbarriers of the copy-first mode (the pipeline's stay untouched)
 
 struct GemmParams {
   void* C;
@@ -71,6 +74,7 @@ struct GemmParams {
   // of BM (A) or BN (B) rows; the TMA producer waits for a block's flag before loading it.
   int ag_operand;          // 0 none, 1 A, 2 B
   int ag_ctas;
+  int ag_all;  // 1: every CTA copies its share of the peers' shards first, then computes
   int ag_rows_per_shard;   // rows of the gathered operand owned by each rank
   int ag_blk_rows;         // rows per flag (a divisor of ag_rows_per_shard)
   long long ag_row_bytes;  // bytes per row (dense rows)
@@ -221,6 +225,73 @@ __device__ __forceinline__ void rs_reduce(const GemmParams& p, int warp, int lan
 
 // FP8 = 1: both operands are K-major 8-bit floats; a stage row is still 128 bytes, i.e. 128
 // elements of K, and one MMA covers 32 of them.
+// Copy-first all-gather (one thread per CTA): the peers' shards of the gathered operand and of
+// the extra tensor are cut into 32 KB chunks, interleaved over the peers and dealt round-robin
+// to ALL CTAs of the grid; each CTA moves its few chunks peer -> shared memory -> local buffer
+// through the (still empty) pipeline stages with bulk async copies, then adds 1 to the launch's
+// counter.  With ~150 CTAs x 6 chunks in flight the gather runs at link rate and is over
+// within the first tiles, which are the local shard's; a producer waits for the counter once,
+// before its first tile with remote rows.
+__device__ __forceinline__ bool ag_copy_all(const GemmParams& p, uint8_t* smem, uint64_t* rbar) {
+  const int cn = static_cast<int>(gridDim.x), ci = static_cast<int>(blockIdx.x);
+  const long long shard_bytes = p.ag_rows_per_shard * p.ag_row_bytes;
+  const int cpp = static_cast<int>((shard_bytes + AG_CHUNK - 1) / AG_CHUNK);
+  const int xpp = static_cast<int>((p.ag_extra_bytes + AG_CHUNK - 1) / AG_CHUNK);
+  const int peers = p.world - 1;
+  const int nchunks = peers * (cpp + xpp);
+  const int mine = ci < nchunks ? (nchunks - ci + cn - 1) / cn : 0;
+  auto locate = [&](int i, const uint8_t*& src, uint8_t*& dst, uint32_t& nb) {
+    const int g = ci + i * cn;
+    const int peer = (p.rank + 1 + g % peers) % p.world;
+    int c = g / peers;
+    long long off, left;
+    if (c < cpp) {
+      off = static_cast<long long>(c) * AG_CHUNK;
+      left = shard_bytes - off;
+      src = reinterpret_cast<const uint8_t*>(p.ag_src[peer]) + off;
+      dst = reinterpret_cast<uint8_t*>(p.ag_dst) + peer * shard_bytes + off;
+    } else {
+      off = static_cast<long long>(c - cpp) * AG_CHUNK;
+      left = p.ag_extra_bytes - off;
+      src = reinterpret_cast<const uint8_t*>(p.ag_extra_src[peer]) + off;
+      dst = reinterpret_cast<uint8_t*>(p.ag_extra_dst) + peer * p.ag_extra_bytes + off;
+    }
+    nb = static_cast<uint32_t>(left < AG_CHUNK ? left : AG_CHUNK);
+  };
+  uint32_t ring_ph = 0;
+  int issued = 0;
+  bool ok = true;
+  for (int done = 0; done < mine && ok; ++done) {
+    while (issued < mine && issued < done + AG_RING) {
+      if (issued >= AG_RING) bulk_wait_read<0>();  // the ring slot's last store has read it
+      const uint8_t* src; uint8_t* dst; uint32_t nb;
+      locate(issued, src, dst, nb);
+      const int slot = issued % AG_RING;
+      mbar_arrive_expect_tx(&rbar[slot], nb);
+      bulk_load(smem + slot * AG_CHUNK, src, nb, &rbar[slot]);
+      ++issued;
+    }
+    const uint8_t* src; uint8_t* dst; uint32_t nb;
+    locate(done, src, dst, nb);
+    const int slot = done % AG_RING;
+    if (!mbar_wait(&rbar[slot], (ring_ph >> slot) & 1)) {
+      atomicCAS(p.status, 0, ST_COPY);
+      ok = false;
+      break;
+    }
+    ring_ph ^= 1u << slot;
+    fence_proxy_async_smem();
+    bulk_store(dst, smem + slot * AG_CHUNK, nb);
+    bulk_commit();
+  }
+  if (!ok) for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  bulk_wait<0>();  // every byte is in local memory, and the stages are free for the pipeline
+  fence_proxy_async_all();
+  __threadfence();
+  if (ok) atomicAdd(p.ag_flags, 1u);
+  return ok;
+}
+
 template <int A_MN, int B_MN, int FP8 = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -248,6 +319,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
     }
+    if (p.ag_all)
+      for (int i = 0; i < AG_RING; ++i) mbar_init(&bars[AG_RING_BAR + i], 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -287,6 +360,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      bool all_ready = false;
+      if (p.ag_all) ok = ag_copy_all(p, smem, bars + AG_RING_BAR);
       for (int t = first_tile; t < total_units && ok; t += tile_step) {
         const int ks = t / total_tiles, tt = t - ks * total_tiles;
         const int kb0 = ks * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
@@ -302,6 +377,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           const int row1 = min(rows, row0 + (p.ag_operand == 1 ? BM : BN));
           const int bps = p.ag_rows_per_shard / p.ag_blk_rows;
           bool waited = false;
+          if (p.ag_all) {
+            // copy-first mode: one counter says every CTA has landed its share
+            const int own0 = p.rank * p.ag_rows_per_shard;
+            if (!all_ready && (row0 < own0 || row1 > own0 + p.ag_rows_per_shard)) {
+              if (!flag_wait_ge<false>(p.ag_flags, gridDim.x)) {
+                atomicCAS(p.status, 0, ST_AG_WAIT);
+                ok = false;
+              }
+              all_ready = waited = true;
+            }
+          } else
           for (int blk = row0 / p.ag_blk_rows; blk * p.ag_blk_rows < row1 && ok; ++blk) {
             if (blk / bps == p.rank) continue;
             waited = true;
@@ -1152,8 +1238,16 @@ static int gemm_run(const void* A, const void* B, void* C, int M, int N, int K, 
         (fz.extra_shard_bytes & 15) || (fz.extra_shard_bytes > 0 && !fz.extra))
       return -5;
     p.ag_operand = fz.kind;
-    p.ag_ctas = fz.copy_ctas > 0 ? fz.copy_ctas : 8;
-    if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
+    if (fz.copy_ctas < 0) {
+      // copy-first mode (see ag_copy_all): flags[0] is the launch's counter, zeroed in stream
+      p.ag_all = 1;
+      p.ag_ctas = 0;
+      const cudaError_t ez = cudaMemsetAsync(fz.flags, 0, sizeof(unsigned), stream);
+      if (ez != cudaSuccess) return static_cast<int>(ez);
+    } else {
+      p.ag_ctas = fz.copy_ctas > 0 ? fz.copy_ctas : 8;
+      if (p.ag_ctas > cap / 4) p.ag_ctas = cap / 4;
+    }
     p.ag_rows_per_shard = rows / fz.world;
     p.ag_blk_rows = blk;
     p.ag_row_bytes = static_cast<long long>(K) * 2;

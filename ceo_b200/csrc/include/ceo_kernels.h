@@ -272,6 +272,10 @@ int ceo_symm_allreduce(void* const* bufs, void* const* flags, float* out, int n,
  * flag, a divisor of rows / world (0 = 128 for A, 256 for B).  extra (optional): per-rank
  * buffers of a second tensor sharded into extra_shard_bytes per rank that the copy CTAs
  * gather after the operand (complete when the kernel ends).
+ * copy_ctas: number of copy CTAs (0 = 8); -1 = copy-first mode: every CTA of the grid first
+ * moves its round-robin share of 32 KB chunks of the peers' shards (operand and extra tensor),
+ * then computes; flags[0] is then the launch's counter (zeroed in stream by the call) and
+ * blk_rows / target are not used.  Right for weights (a gather much shorter than the GEMM).
  * Call ceo_symm_barrier first so every rank's shard is complete. */
 int ceo_ag_gemm_bf16(void* const* gathered, int operand, const void* other, void* C, int M, int N,
                      int K, long long ld_other, long long ldc, int other_mn_major, int out_f32,

@@ -127,7 +127,7 @@ def main(argv=None):
             fc.device_barrier()   # every rank's shard is final (the optimizer's last barrier)
             _lib.check(_lib.lib().ceo_ag_gemm_bf16(
                 wbuf.table(), 2, xin.data_ptr(), outw.data_ptr(), M, n_w, Dm, Dm, n_w, 0, 0, 0, 1.0,
-                None, 0, flags.data_ptr(), calls[0], rank, world, 8, blk, xbuf.table(),
+                None, 0, flags.data_ptr(), calls[0], rank, world, -1, blk, xbuf.table(),
                 n_x * 2 // world, st.data_ptr(), _lib.stream()), "ceo_ag_gemm_bf16")
 
         def nccl():

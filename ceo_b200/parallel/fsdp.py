@@ -13,8 +13,9 @@ reference consults) selects how much of a data-parallel replica's state is parti
   parameter all-gather remain.
 * stage 3: parameters too (FSDP).  The update leaves the block matrices as row shards; the
   all-gather of ``w_qkv`` (+ ``w_o``) and ``w_up`` (+ ``w_down``) happens inside the first
-  GEMM that consumes them after the step (``WeightGather``: copy CTAs of the GEMM kernel pull
-  the peers' row shards over NVLink while the other CTAs already multiply the local rows).
+  GEMM that consumes them after the step (``WeightGather``: every CTA of the GEMM kernel first
+  pulls its few 32 KB chunks of the peers' row shards over NVLink, then multiplies, local rows
+  first; the gather runs at link rate and is over while the local tiles are being computed).
   The gathered copy is kept for the remaining micro-batches and the backward pass of the step.
 """
 from __future__ import annotations
@@ -91,7 +92,7 @@ class WeightGather:
     second tensor that a later GEMM of the block needs), fused into the GEMM that first
     consumes the weight after an optimizer step."""
 
-    def __init__(self, comm, flat, name: str, extra_name: str | None = None, copy_ctas: int = 8):
+    def __init__(self, comm, flat, name: str, extra_name: str | None = None, copy_ctas: int = -1):
         self.comm, self.flat = comm, flat
         seg = flat.segment(name)
         self.N, self.K = seg.shape

@@ -49,6 +49,9 @@ def main(argv=None):
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--copy-ctas", type=int, default=0,
+                    help="ag_gemm*: copy CTAs (0: 8 for activations, copy-first mode for weights; "
+                         "-1: every CTA copies its share first)")
     ap.add_argument("--no-reduce", action="store_true",
                     help="zero_step: skip the reduce-scatter phase (as after bucket reductions)")
     a = ap.parse_args(argv)
@@ -104,7 +107,8 @@ def main(argv=None):
             calls[0] += 1
             _lib.check(L.ceo_ag_gemm_bf16(table(bufs), operand, other.data_ptr(), out.data_ptr(),
                                           M, N, K, K, N, 0, 0, 0, 1.0, None, 0, flags.data_ptr(),
-                                          calls[0], 0, W, 8, blk if operand == 2 else 0, None, 0,
+                                          calls[0], 0, W, a.copy_ctas or (8 if operand == 1 else -1),
+                                          blk if operand == 2 else 0, None, 0,
                                           st.data_ptr(), _lib.stream()), "ceo_ag_gemm_bf16")
         ms = _time(run, a.iters)
         rec.update(ms=ms, M=M, N=N, K=K, tflops=2.0 * M * N * K / ms / 1e9,

@@ -116,6 +116,10 @@ class ParallelEngine:
         if self.cp_size == 1:
             return tokens
         T = tokens.shape[1] // self.cp_size
+        if tokens.shape[1] % self.cp_size or T % 64:
+            # the state crosses ranks at chunk boundaries: every span is whole 64-token chunks
+            raise ValueError(f"sequence length {tokens.shape[1]} does not split into "
+                             f"{self.cp_size} context-parallel spans of whole 64-token chunks")
         return tokens[:, self.cp_rank * T:(self.cp_rank + 1) * T].contiguous()
 
     def train_step(self, batches, lr: float | None = None):

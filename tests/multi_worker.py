@@ -189,12 +189,14 @@ def main():
         cfg = small_cfg(world)
         cfg.model.num_heads = 4
         cfg.model.head_dim = 128
-        cfg.data.seq_len = 256
+        # context parallel: every rank's span is at least one 64-token chunk
+        seq = 256 if what == "tp_model" else max(256, 64 * world)
+        cfg.data.seq_len = seq
         cfg.training.micro_batch_size = 2
         cfg.runtime.tensor_parallel_size = world if what == "tp_model" else 1
         cfg.runtime.context_parallel_size = world if what == "cp_model" else 1
         data = SyntheticTokens(cfg.model.vocab_size, "zipf", 1.1, 0, 0)   # same data on all ranks
-        batches = [data.batch(2, 256) for _ in range(3)]
+        batches = [data.batch(2, seq) for _ in range(3)]
         par = ParallelEngine(cfg, torch.device("cuda", torch.cuda.current_device()))
         lp = [tuple(float(x) for x in par.train_step([b], lr=1e-3)) for b in batches]
         cfg1 = small_cfg(1)

@@ -178,3 +178,15 @@ def test_engine_trains_with_fp8_forward_on_gpu():
     assert all(l == l for l in a) and a[-1] < a[0]
     assert abs(a[0] - b[0]) < 0.02 * b[0]      # same weights: fp8 forward ~ bf16 forward
     assert _lib.read_status() == 0
+
+
+def test_fp8_convergence_tool_runs_both_arms(capsys):
+    # the bf16 / FP8 comparison a user runs before switching fp8_training on
+    from ceo_b200.utils import fp8_convergence
+    cfg = os.path.join(ROOT, "configs", "smoke.yaml")
+    assert fp8_convergence.main(["--config", cfg, "--steps", "6", "--global-batch", "2",
+                                 "--seq-len", "128", "--every", "0"]) == 0
+    import json
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["steps"] == 6 and abs(rec["loss_first"][0] - rec["loss_first"][1]) < 0.2
+    assert abs(rec["rel_gap"]) < 0.05
