@@ -46,6 +46,8 @@ def main(argv=None):
     ap.add_argument("--d-model", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=11008)
     ap.add_argument("--json", default="")
+    ap.add_argument("--only", default="", choices=["", "tp", "fsdp"],
+                    help="tp: the tensor-parallel rows; fsdp: the weight-gather rows")
     a = ap.parse_args(argv)
     rank, world, local = init_distributed()
     torch.cuda.set_device(local)
@@ -67,26 +69,33 @@ def main(argv=None):
 
     ncol = max(3 * D // world, 256)
     ffn_loc = (a.ffn // world + 255) // 256 * 256
-    tp = TPContext(fc, M, max(D, ncol, ffn_loc, 2 * ffn_loc), copy_ctas=8)
+    tp = TPContext(fc, M, max(D, ncol, ffn_loc, 2 * ffn_loc))
     g = torch.Generator(device="cuda").manual_seed(rank)
     xs = torch.randn(rows, D, device="cuda", generator=g).bfloat16()
     from ..ops.matmul import gemm as plain_gemm
+    tp_rows = a.only in ("", "tp")
     t_bar = timed(lambda: fc.device_barrier(), fc)
     if rank == 0:
         print(json.dumps({"op": "device barrier (flag kernel)", "world": world,
                           "ms": round(t_bar, 4)}), flush=True)
-    for name, n_loc in (("ag_gemm qkv", ncol), ("ag_gemm gate_up", 2 * ffn_loc)):
+    for name, n_loc in (("ag_gemm qkv", ncol), ("ag_gemm gate_up", 2 * ffn_loc)) if tp_rows else ():
         w = (torch.randn(n_loc, D, device="cuda", generator=g) * 0.02).bfloat16()
-        f = timed(lambda: tp.ag_gemm(xs, w), fc)
+        f = timed(lambda: tp.ag_gemm(xs, w), fc)          # copy-first (the default)
+        tp.copy_ctas = 8
+        f_cc = timed(lambda: tp.ag_gemm(xs, w), fc)       # dedicated copy CTAs
+        tp.copy_ctas = -1
         n = timed(lambda: tp.ag_gemm_nccl(xs, w), fc)
         xf = torch.randn(M, D, device="cuda", generator=g).bfloat16()
         loc = timed(lambda: plain_gemm(xf, w), fc)
         rec(f"{name} {M}x{n_loc}x{D}", f, n, 2.0 * M * n_loc * D,
             (world - 1) / world * M * D * 2)
         out[-1]["local_gemm_ms"] = round(loc, 4)
+        out[-1]["fused_copy_ctas_ms"] = round(f_cc, 4)
         if rank == 0:
-            print(json.dumps({"local_gemm_ms": round(loc, 4)}), flush=True)
-    for name, k_loc in (("gemm_rs out", max(D // world, 256)), ("gemm_rs down", ffn_loc)):
+            print(json.dumps({"local_gemm_ms": round(loc, 4), "fused_copy_ctas_ms": round(f_cc, 4)}),
+                  flush=True)
+    for name, k_loc in (("gemm_rs out", max(D // world, 256)),
+                        ("gemm_rs down", ffn_loc)) if tp_rows else ():
         x = torch.randn(M, k_loc, device="cuda", generator=g).bfloat16()
         w = (torch.randn(D, k_loc, device="cuda", generator=g) * 0.02).bfloat16()
         f = timed(lambda: tp.gemm_rs(x, w), fc)
@@ -107,7 +116,7 @@ def main(argv=None):
     Dm = 2048
     for name, n_w, n_x in (("fsdp qkv (+w_o)", 6208, Dm * Dm), ("fsdp gate_up (+w_down)", 11264,
                                                                Dm * 5632)):
-        if n_w % world or n_x % (8 * world):
+        if n_w % world or n_x % (8 * world) or a.only == "tp":
             continue
         wbuf = SymmetricBuffer(n_w * Dm * 2, fc.group)
         xbuf = SymmetricBuffer(n_x * 2, fc.group)

@@ -28,7 +28,7 @@ class TPContext:
     """Symmetric workspaces of one tensor-parallel group for activations of up to
     ``max_rows`` (gathered) rows by ``max_cols`` columns."""
 
-    def __init__(self, comm, max_rows: int, max_cols: int, copy_ctas: int = 8):
+    def __init__(self, comm, max_rows: int, max_cols: int, copy_ctas: int = -1):
         self.comm, self.group = comm, comm.group
         self.rank, self.world = comm.rank, comm.world
         self.max_rows, self.max_cols = max_rows, max_cols
@@ -50,6 +50,7 @@ class TPContext:
         nblk = (max_rows + 127) // 128
         self.counters = SymmetricBuffer(self.world * nblk * 4, self.group)
         self.ag_flags = torch.zeros(nblk, dtype=torch.int32, device=dev)
+        self.ag_counter = torch.zeros(1, dtype=torch.int32, device=dev)  # copy-first mode
         self.ag_calls = 0
         self.rs_target = 0
         self.nblk = nblk
@@ -74,17 +75,24 @@ class TPContext:
         # which used this half of the buffer
         self.barrier()
         out = torch.empty(M, N, dtype=out_dtype, device=self.dev)
-        # enough copy CTAs to keep NVLink busy when the transfer, not the math, is the bound:
-        # one copy CTA sustains roughly 40 GB/s (six 32 KB bulk copies in flight)
-        comm_s = (self.world - 1) / self.world * M * K * 2 / 770e9
-        math_s = 2.0 * M * N * K / 1.4e15
-        ratio = comm_s / max(math_s, 1e-9)
-        copy_ctas = self.copy_ctas if ratio < 0.3 else (16 if ratio < 0.6 else 24)
+        if self.copy_ctas < 0:
+            # copy-first: every CTA moves its share of the peers' shards at link rate, then
+            # computes (local rows first); one counter instead of per-block flags
+            copy_ctas, flags = -1, self.ag_counter
+        else:
+            # dedicated copy CTAs, enough of them to keep NVLink busy when the transfer, not
+            # the math, is the bound (one copy CTA sustains a few tens of GB/s: six 32 KB bulk
+            # copies in flight)
+            comm_s = (self.world - 1) / self.world * M * K * 2 / 770e9
+            math_s = 2.0 * M * N * K / 1.4e15
+            ratio = comm_s / max(math_s, 1e-9)
+            copy_ctas = self.copy_ctas if ratio < 0.3 else (16 if ratio < 0.6 else 24)
+            flags = self.ag_flags
         L = _lib.lib()
         _lib.check(L.ceo_ag_gemm_bf16(self.gather.table(half), 1, w.data_ptr(), out.data_ptr(), M, N, K,
                                       w.stride(0), out.stride(0), int(w_mn),
                                       int(out_dtype == torch.float32), 0, 1.0, None, 0,
-                                      self.ag_flags.data_ptr(), self.ag_calls, self.rank,
+                                      flags.data_ptr(), self.ag_calls, self.rank,
                                       self.world, copy_ctas, 0, None, 0,
                                       _lib.status_word(self.dev).data_ptr(), _lib.stream()),
                    "ceo_ag_gemm_bf16")
