@@ -80,7 +80,7 @@ def main(argv=None):
                           "ms": round(t_bar, 4)}), flush=True)
     for name, n_loc in (("ag_gemm qkv", ncol), ("ag_gemm gate_up", 2 * ffn_loc)) if tp_rows else ():
         w = (torch.randn(n_loc, D, device="cuda", generator=g) * 0.02).bfloat16()
-        f = timed(lambda: tp.ag_gemm(xs, w), fc)          # copy-first (the default)
+        f = timed(lambda: tp.ag_gemm(xs, w), fc)          # the default choice of mode
         tp.copy_ctas = 8
         f_cc = timed(lambda: tp.ag_gemm(xs, w), fc)       # dedicated copy CTAs
         tp.copy_ctas = -1

@@ -75,9 +75,13 @@ class TPContext:
         # which used this half of the buffer
         self.barrier()
         out = torch.empty(M, N, dtype=out_dtype, device=self.dev)
-        if self.copy_ctas < 0:
-            # copy-first: every CTA moves its share of the peers' shards at link rate, then
-            # computes (local rows first); one counter instead of per-block flags
+        remote = (self.world - 1) / self.world * M * K * 2
+        if self.copy_ctas < 0 and remote <= 24e6:
+            # copy-first: every CTA moves its share of the peers' shards, then computes (local
+            # rows first); one counter instead of per-block flags.  Pays while a CTA's share
+            # fits its ring of six 32 KB buffers (one NVLink round trip for the whole gather):
+            # measured at 2 ranks, 17 MB of weights arrive in 23 us, but 67 MB of activations
+            # take 135 us of copy-only time where 8 copy CTAs hide them behind the GEMM
             copy_ctas, flags = -1, self.ag_counter
         else:
             # dedicated copy CTAs, enough of them to keep NVLink busy when the transfer, not
@@ -86,7 +90,8 @@ class TPContext:
             comm_s = (self.world - 1) / self.world * M * K * 2 / 770e9
             math_s = 2.0 * M * N * K / 1.4e15
             ratio = comm_s / max(math_s, 1e-9)
-            copy_ctas = self.copy_ctas if ratio < 0.3 else (16 if ratio < 0.6 else 24)
+            base = self.copy_ctas if self.copy_ctas > 0 else 8
+            copy_ctas = base if ratio < 0.3 else (16 if ratio < 0.6 else 24)
             flags = self.ag_flags
         L = _lib.lib()
         _lib.check(L.ceo_ag_gemm_bf16(self.gather.table(half), 1, w.data_ptr(), out.data_ptr(), M, N, K,
