@@ -34,6 +34,9 @@ namespace ceo {
 constexpr int CH = 64;    // chunk length
 constexpr int GLD = 68;   // leading dimension of the fp32 64x64 Gram tile
 constexpr int BV = 64;    // value columns per CTA in the serial kernels
+// column groups of warps in efla_bwd_final_kernel (4 x BF_CG warps): 16 warps at 125 registers
+// measured 1-3 % slower than 8 warps at 198 (the kernel is not short of warps to hide latency)
+constexpr int BF_CG = 2;
 
 template <int NT>
 __device__ __forceinline__ void frag_store_bf16(bf16* base, long long ld, float (*acc)[4]) {
@@ -933,8 +936,10 @@ efla_state_bwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 }
 
 // ================================================= backward: dK, dV, d(alpha)
-template <int D>
-__global__ void __launch_bounds__(256, 1)
+// CG column groups of warps: a CTA has 4 x CG warps, warp (r, cg) owns the 16 rows 16 r of a
+// product and the columns [cg * W / CG, (cg + 1) * W / CG) of its W-wide result.
+template <int D, int CG>
+__global__ void __launch_bounds__(128 * CG, 1)
 efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_up,
@@ -946,7 +951,8 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_v, const float* __restrict__ alpha,
                       bf16* __restrict__ dk, bf16* __restrict__ dv, float* __restrict__ dalpha,
                       int T, int H, long long dks, long long dvs, int* status) {
-  constexpr int NT = D / 16, TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
+  constexpr int NT = D / (8 * CG), CW = CH / CG, CN = CW / 8;  // per warp: NT tiles of D, CN of CH
+  constexpr int TILE = (D / 64) * PANEL, STILE = (D / 64) * D * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* Qs = smem;
@@ -1025,8 +1031,8 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
-  const int r = warp & 3, half = warp >> 2;
-  const int c0 = (D / 2) * half;
+  const int r = warp & 3, cg = warp >> 2;
+  const int c0 = (D / CG) * cg;
   const SwzTile Qt = swz_tile(Qs, CH), Kt = swz_tile(Ks, CH), Upt = swz_tile(Ups, CH),
                 dOt = swz_tile(dOs, CH), Zt = swz_tile(Zs, CH), St = swz_tile(Sb, D),
                 dSt = swz_tile(dSb, D), Xt = swz_tile(Xs, CH), dGt = swz_tile(dGs, CH),
@@ -1034,14 +1040,14 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   // 1. G = K K^T, strictly lower part, fp32 (step 4 needs it for d(alpha))
   {
-    float acc[4][4];
-    zero_acc<4>(acc);
-    wg<4, D, false, false>(acc, Kt, 16 * r, Kt, 32 * half);
+    float acc[CN][4];
+    zero_acc<CN>(acc);
+    wg<CN, D, false, false>(acc, Kt, 16 * r, Kt, CW * cg);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < CN; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int row = 16 * r + g + (e >> 1) * 8, col = 32 * half + nt * 8 + 2 * tg + (e & 1);
+        const int row = 16 * r + g + (e >> 1) * 8, col = CW * cg + nt * 8 + 2 * tg + (e & 1);
         Gs[row * GLD + col] = col < row ? acc[nt][e] : 0.f;
       }
   }
@@ -1091,15 +1097,15 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   // 4. dA = -strict_tril(Z U'^T) ; d(alpha) += dA . G ; dG = a dA ;  dP = tril(dO U'^T)
   {
-    float acc[4][4];
-    zero_acc<4>(acc);
-    wg<4, D, false, false>(acc, Zt, 16 * r, Upt, 32 * half);
+    float acc[CN][4];
+    zero_acc<CN>(acc);
+    wg<CN, D, false, false>(acc, Zt, 16 * r, Upt, CW * cg);
     float p[2] = {0.f, 0.f};
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < CN; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
+        const int row = 16 * r + g + hf * 8, col = CW * cg + nt * 8 + 2 * tg;
         const float a = al[row];
         const float d0 = col < row ? -acc[nt][2 * hf] : 0.f;
         const float d1 = col + 1 < row ? -acc[nt][2 * hf + 1] : 0.f;
@@ -1113,13 +1119,13 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       if (tg == 0) atomicAdd(&dal[16 * r + g + hf * 8], s);
     }
-    zero_acc<4>(acc);
-    wg<4, D, false, false>(acc, dOt, 16 * r, Upt, 32 * half);
+    zero_acc<CN>(acc);
+    wg<CN, D, false, false>(acc, dOt, 16 * r, Upt, CW * cg);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < CN; ++nt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int row = 16 * r + g + hf * 8, col = 32 * half + nt * 8 + 2 * tg;
+        const int row = 16 * r + g + hf * 8, col = CW * cg + nt * 8 + 2 * tg;
         sts_bf162(dPt.at(row, col), col <= row ? acc[nt][2 * hf] : 0.f,
                   col + 1 <= row ? acc[nt][2 * hf + 1] : 0.f);
       }
@@ -1336,7 +1342,7 @@ static cudaError_t efla_configure() {
   if (D == 128 && (e = set_smem(efla_out_tc_kernel, OUT_TC_SMEM)) != cudaSuccess) return e;
   if ((e = set_smem(efla_bwd_local_kernel<D>, smem_bwd_local<D>())) != cudaSuccess) return e;
   if ((e = set_smem(efla_state_bwd_kernel<D>, smem_state_bwd<D>())) != cudaSuccess) return e;
-  if ((e = set_smem(efla_bwd_final_kernel<D>, smem_bwd_final<D>())) != cudaSuccess) return e;
+  if ((e = set_smem(efla_bwd_final_kernel<D, BF_CG>, smem_bwd_final<D>())) != cudaSuccess) return e;
   cfg = true;
   return cudaSuccess;
 }
@@ -1456,7 +1462,7 @@ static int efla_run_stage(int stage, const EflaTensors& t, int B, int T, int H, 
       MAP(encode_tmap_2d_bf16(&m[7], t.p[I_XINV], CH, static_cast<uint64_t>(B) * H * n * CH, CH, CH)
               ? -3 : 0);
       MAP(tokp(&m[8], I_V, t.stride[2]));
-      efla_bwd_final_kernel<D><<<gpar, 256, smem_bwd_final<D>(), st>>>(
+      efla_bwd_final_kernel<D, BF_CG><<<gpar, 128 * BF_CG, smem_bwd_final<D>(), st>>>(
           m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], f32(I_ALPHA), b16(I_DK), b16(I_DV),
           f32(I_DALPHA), T, H, t.stride[4], t.stride[5], status);
       break;
