@@ -88,7 +88,12 @@ __device__ __forceinline__ void tma_state_tile_2d(uint8_t* dst, const CUtensorMa
 }
 // Wait for a tile group that is loaded once per CTA (phase 0).  Bounded: when a wait anywhere
 // in the grid has run out, the status word is set and every later wait returns at once.
+// The status word lives in global memory: it is read only once the barrier has not flipped
+// after a few polls (a tile that has already landed costs no global round trip).
 __device__ __forceinline__ void tile_wait(uint64_t* bar, int* status) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, 0)) return;
   if (status && *reinterpret_cast<volatile int*>(status)) return;
   if (!mbar_wait(bar, 0) && status) atomicExch(status, EFLA_WAIT_STATUS);
 }
@@ -562,6 +567,9 @@ efla_out_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int warp = threadIdx.x >> 5;
   // bounded wait that gives up at once when any wait of the grid has already run out
   auto waitb = [&](uint64_t* bar) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, 0)) return true;
     if (status && *reinterpret_cast<volatile int*>(status)) return false;
     return mbar_wait(bar, 0);
   };
