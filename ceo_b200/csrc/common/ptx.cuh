@@ -104,6 +104,20 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// L2 prefetch of the box a tma_load_2d / tma_load_3d with the same coordinates would fetch
+// (no shared-memory destination, no completion tracking).
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 // 2-D tiled store, this CTA's shared memory -> global, tracked by bulk groups (bulk_commit /
 // bulk_wait_read / bulk_wait).  Coordinates must not be negative; x as for loads.
 __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x,

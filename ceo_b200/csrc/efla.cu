@@ -37,6 +37,10 @@ constexpr int BV = 64;    // value columns per CTA in the serial kernels
 // column groups of warps in efla_bwd_final_kernel (4 x BF_CG warps): 16 warps at 125 registers
 // measured 1-3 % slower than 8 warps at 198 (the kernel is not short of warps to hide latency)
 constexpr int BF_CG = 2;
+#ifndef CEO_BF_PREFETCH
+#define CEO_BF_PREFETCH 1
+#endif
+constexpr int BF_AHEAD = 148;  // CTAs of efla_bwd_final_kernel in flight (one per SM)
 
 template <int NT>
 __device__ __forceinline__ void frag_store_bf16(bf16* base, long long ld, float (*acc)[4]) {
@@ -1036,6 +1040,31 @@ efla_bwd_final_kernel(const __grid_constant__ CUtensorMap tm_q,
   // alpha is requested now, parked in shared memory after the Gram product (first use: step 3)
   const float my_al =
       threadIdx.x < CH ? alpha[(static_cast<long long>(tok0) + threadIdx.x) * H + h] : 0.f;
+#if CEO_BF_PREFETCH
+  // One CTA fits an SM, so nothing overlaps the arrival of a CTA's first tiles.  CTAs are
+  // handed out in linear order: the one that follows this one on this SM is about gridDim
+  // CTAs-in-flight further on; its tiles are pulled into L2 now.
+  {
+    const long long lin = static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x + BF_AHEAD;
+    if (lin < static_cast<long long>(gridDim.x) * gridDim.y) {
+      const int nx = static_cast<int>(lin % gridDim.x), nbh = static_cast<int>(lin / gridDim.x);
+      const int nb = nbh / H, nh = nbh - nb * H;
+      const int ntok0 = nb * T + nx * CH, nsrow = (nbh * n + nx) * D;
+      switch (threadIdx.x) {
+        case 1: tma_prefetch_3d(&tm_k, 0, ntok0, (nh * D) >> 6); break;
+        case 33: tma_prefetch_2d(&tm_xinv, 0, (nbh * n + nx) * CH); break;
+        case 65: tma_prefetch_3d(&tm_dup, 0, ntok0, (nh * D) >> 6); break;
+        case 97: tma_prefetch_3d(&tm_states, 0, nsrow, 0); break;
+        case 129: tma_prefetch_3d(&tm_up, 0, ntok0, (nh * D) >> 6); break;
+        case 161: tma_prefetch_3d(&tm_dO, 0, ntok0, (nh * D) >> 6); break;
+        case 193: tma_prefetch_3d(&tm_q, 0, ntok0, (nh * D) >> 6); break;
+        case 225: tma_prefetch_3d(&tm_dstates, 0, nsrow, 0); break;
+        case 17: tma_prefetch_3d(&tm_v, 0, ntok0, (nh * D) >> 6); break;
+        default: break;
+      }
+    }
+  }
+#endif
   tile_wait(&bars[0], status);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
