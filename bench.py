@@ -275,6 +275,20 @@ def main(argv=None):
     shard = {0: f"dp{dp}", 1: f"zero1-dp{dp}", 2: f"zero2-dp{dp}", 3: f"fsdp{dp}"}[zero_stage]
     parallelism = shard if tp * cp == 1 else f"tp{tp}xcp{cp}x{shard}"
     peak_mem = torch.cuda.max_memory_allocated(dev)
+    if comm is None:
+        collectives = "none"
+    elif not getattr(comm, "fused", False):
+        collectives = "library collectives (NCCL)"
+    else:
+        collectives = "own kernels over NVLink peer memory: " + {
+            1: "reduce-scatter + clip + AdamW + all-gather in one kernel after backward",
+            2: "bucket reduce-scatter during backward, then norm + AdamW + all-gather in one kernel",
+            3: "bucket reduce-scatter during backward, norm + AdamW in one kernel, weight "
+               "all-gather inside the QKV and gate/up GEMMs"}.get(zero_stage, "fused optimizer step")
+        if tp > 1:
+            collectives += "; tensor parallel: all-gather -> GEMM and GEMM -> reduce-scatter kernels"
+        if cp > 1:
+            collectives += "; context parallel: in-kernel state exchange"
     if rank == 0:
         value = tokens_per_step * a.steps / (ms * 1e-3)
         flops = eng.model.flops_per_token(seq) * value
@@ -293,7 +307,7 @@ def main(argv=None):
                        "parallelism": parallelism,
                        "zero_stage": zero_stage,
                        "optimizer": cfg.training.optimizer,
-                       "collectives": type(comm).__name__ if comm else "none",
+                       "collectives": collectives,
                        "l2": "inputs larger than L2 (each micro-batch streams >1 GB)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "model_tflops_per_gpu": flops / world / 1e12, "final_loss": last_loss,
