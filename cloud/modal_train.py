@@ -12,6 +12,7 @@ import subprocess
 import sys
 
 APP_NAME = "efla-trainer"
+REMOTE_ROOT = "/workspace/ceo_b200"   # where the image holds this repository
 GPU_TRAIN = "B200:8"
 GPU_SMOKE = "B200"
 DATA_DIR = "/data"
@@ -61,7 +62,7 @@ def build_app():
     import modal
 
     image = (modal.Image.from_registry("nvidia/cuda:12.9.0-devel-ubuntu24.04", add_python="3.12")
-             .pip_install("torch", "numpy").add_local_dir(".", "/root/repo"))
+             .pip_install("torch", "numpy").add_local_dir(".", REMOTE_ROOT))
     app = modal.App(APP_NAME, image=image)
     data = modal.Volume.from_name("efla-data", create_if_missing=True)
     ckpt = modal.Volume.from_name("efla-checkpoints", create_if_missing=True)
@@ -69,24 +70,24 @@ def build_app():
 
     @app.function(gpu=GPU_TRAIN, volumes=vols, timeout=24 * 3600, retries=0)
     def train(config: str = "configs/efla_1p3b.yaml", resume: str = ""):
-        os.chdir("/root/repo")
+        os.chdir(REMOTE_ROOT)
         subprocess.check_call([sys.executable, "-m", "ceo_b200.build"])
         return run_action("train", config=config, resume=resume or None)
 
     @app.function(gpu=GPU_SMOKE, volumes=vols, timeout=1800)
     def smoke_test():
-        os.chdir("/root/repo")
+        os.chdir(REMOTE_ROOT)
         subprocess.check_call([sys.executable, "-m", "ceo_b200.build"])
         return run_action("smoke_test")
 
     @app.function(gpu=GPU_SMOKE, volumes=vols, timeout=3600)
     def evaluate(checkpoint: str, data: str):
-        os.chdir("/root/repo")
+        os.chdir(REMOTE_ROOT)
         return run_action("evaluate", checkpoint=checkpoint, data=data)
 
     @app.function(gpu=GPU_SMOKE, volumes=vols, timeout=3600)
     def generate(checkpoint: str, prompt: str = "", max_tokens: int = 64):
-        os.chdir("/root/repo")
+        os.chdir(REMOTE_ROOT)
         return run_action("generate", checkpoint=checkpoint, prompt=prompt, max_tokens=max_tokens)
 
     @app.function(volumes=vols)
