@@ -82,6 +82,13 @@ def test_shipped_configs_parse():
             c.model.intermediate_dim, c.model.vocab_size, c.data.seq_len) == \
         (2048, 24, 16, 128, 5632, 32000, 4096)
     assert c.training.global_batch_size * c.data.seq_len == 1 << 20
+    # the accumulation count written in the file is the one the batch sizes imply on 8 GPUs,
+    # and every GPU count of the scaling run divides the global batch into whole micro-batches
+    t = c.training
+    assert t.gradient_accumulation_steps * t.micro_batch_size * c.runtime.world_size == \
+        t.global_batch_size
+    for n in (1, 2, 4, 8):
+        assert t.global_batch_size % (t.micro_batch_size * n) == 0
 
 
 def test_hashing():
