@@ -516,3 +516,43 @@ def test_prism_gate_state_and_recurrent_decode():
     assert torch.allclose(cache["state"], st, atol=1e-5)
     with pytest.raises(ValueError):
         model.decode_step(tok[:, 0], [s for s in model.new_states(2)])
+
+
+def test_layer_properties_like_the_reference_unit_tests():
+    # the property assertions of the reference's layer tests (src/nn/layers.zig:689-744,
+    # src/kernels/nn_kernels.zig:250-284): unit mean square after RMSNorm, zero mean / unit
+    # variance after LayerNorm, SwiGLU = silu(gate) * up, softmax rows sum to one, the
+    # cross-entropy of uniform logits is log(V), embedding rows are table rows
+    from ceo_b200.ops import nn as K
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, 32, generator=g) * 3 + 1
+    y, h = K.rmsnorm(x, torch.ones(32))
+    assert h is None and torch.allclose(y.pow(2).mean(-1), torch.ones(6), atol=1e-4)
+    r = torch.randn(6, 32, generator=g)
+    y2, h2 = K.rmsnorm(x, torch.ones(32), residual=r)
+    assert torch.allclose(h2, x + r) and torch.allclose(y2.pow(2).mean(-1), torch.ones(6), atol=1e-4)
+    z = K.layernorm(x, torch.ones(32), torch.zeros(32))
+    assert torch.allclose(z.mean(-1), torch.zeros(6), atol=1e-5)
+    assert torch.allclose(z.var(-1, unbiased=False), torch.ones(6), atol=1e-3)
+    gu = torch.randn(4, 16, generator=g)
+    want = torch.nn.functional.silu(gu[:, :8]) * gu[:, 8:]
+    assert torch.allclose(K.swiglu(gu), want, atol=1e-6)
+    il = torch.stack([gu[:, :8], gu[:, 8:]], dim=-1).reshape(4, 16)     # gate/up interleaved
+    assert torch.allclose(K.swiglu(il, interleaved=True), want, atol=1e-6)
+    assert torch.allclose(K.activation(torch.zeros(3), "gelu"), torch.zeros(3))
+    assert abs(float(K.activation(torch.tensor([1.0]), "silu")) - 0.7310586) < 1e-6
+    assert torch.allclose(K.softmax(x).sum(-1), torch.ones(6), atol=1e-6)
+    V = 50
+    rows = K.cross_entropy_rows(torch.zeros(5, V), torch.arange(5))
+    assert torch.allclose(rows, torch.full((5,), math.log(V)), atol=1e-6)
+    # label smoothing leaves the loss of uniform logits unchanged; an ignored row scores zero
+    rows = K.cross_entropy_rows(torch.zeros(5, V), torch.tensor([0, 1, -100, 3, 4]), 0.1)
+    assert rows[2] == 0 and torch.allclose(rows[[0, 1, 3, 4]], torch.full((4,), math.log(V)), atol=1e-6)
+    table = torch.randn(10, 4, generator=g)
+    ids = torch.tensor([[1, 9], [0, 1]])
+    assert torch.equal(K.embedding(ids, table), table[ids])
+    w = torch.randn(V, 8, generator=g)
+    xx = torch.randn(7, 8, generator=g)
+    t = torch.randint(0, V, (7,), generator=g)
+    assert abs(float(K.linear_cross_entropy(xx, w, t)) -
+               float(torch.nn.functional.cross_entropy(xx @ w.t(), t))) < 1e-5
